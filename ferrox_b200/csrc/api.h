@@ -1,0 +1,46 @@
+// C entry points of the kernel library (libferrox_b200.so).  Every function
+// enqueues work on `stream` (a cudaStream_t passed as void*) and returns 0, a
+// cudaError_t (> 0) from the launch, or one of the negative FX_ERR_* codes of
+// common.cuh when it refuses its arguments.  Nothing here allocates or synchronises.
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int fx_gemm(const void* A, int a_dtype, long lda, const int* a_rows, const void* W, int w_dtype, long ldw,
+            const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K,
+            const int* group_offsets, int n_groups, long w_group_stride, void* stream);
+
+int fx_embed(const void* table, int dtype, const int* ids, float* out, int n_tokens, int hidden, int vocab,
+             int* status, void* stream);
+int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, float eps, void* out, int out_dtype,
+               int n_rows, int hidden, void* stream);
+int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev, int rows, int n,
+                void* stream);
+int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const int* token_seq, const int* seq_slot,
+                     const float* inv_freq, int rotary_dim, void* k_pages, void* v_pages, const int* block_table,
+                     int table_width, int page_size, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                     int write_cache, int* status, void* stream);
+int fx_moe_combine(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w, int top_k,
+                   const void* shared, const float* shared_gate_logit, int n_tokens, int hidden, void* stream);
+int fx_residual_add(float* h, const void* y, int dtype, long n, void* stream);
+
+int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
+                       const int* block_table, int table_width, int page_size, const int* positions,
+                       const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens, int n_heads,
+                       int n_kv_heads, int head_dim, int window, float scale, void* stream);
+
+int fx_router_topk(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
+                   void* stream);
+int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets, int* src_token,
+                 int* inv_perm, void* stream);
+
+int fx_argmax(const float* logits, long ld, int n_rows, int vocab, int* out, void* stream);
+int fx_repetition_penalty(float* work, long ld, int n_rows, int vocab, const int* history, const int* hist_offsets,
+                          const float* penalty, void* stream);
+int fx_sample(float* work, long ld, int n_rows, int vocab, const float* temperature, const int* top_k,
+              const float* top_p, const float* draw, int* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

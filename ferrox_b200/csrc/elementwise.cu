@@ -1,0 +1,243 @@
+// Memory-bound kernels around the matrix products: embedding rows, RMSNorm,
+// rotary encoding fused with the write of K and V into cache pages, SiLU*up.
+// All arithmetic is 32-bit; only loads and stores use the tensor's element type.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// Embedding: out[t, :] = table[ids[t], :] widened to 32-bit (the residual stream
+// is 32-bit in both engines).  Reference: decoder.rs:1279, 3032-3035.
+// A token id outside [0, vocab) writes zeros and raises *status.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                             int hidden, int vocab, int* __restrict__ status)
+{
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
+    const T* row = table + (long)(ok ? id : 0) * hidden;
+    float* o = out + (long)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm: out = x * (1/sqrt(mean(x^2) + eps)) * w, multiplied in that order
+// (reference: crates/ferrox-core/src/matmul.rs:62-69,121-123).  x is the 32-bit
+// residual stream; `rows` (optional) picks the rows to normalise, which is how the
+// final norm runs only at the positions whose logits are wanted.
+template <typename OT>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                               const void* __restrict__ w, int w_dtype, float eps,
+                               OT* __restrict__ out, int hidden)
+{
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (long)(rows ? rows[r] : r) * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    OT* o = out + (long)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        o[i] = from_f32<OT>(xr[i] * scale * load_any(w, w_dtype, i));
+}
+
+// ---------------------------------------------------------------------------
+// SiLU(gate) * up over rows of [gate | up] (two halves of width n side by side).
+// silu(x) = x / (1 + exp(-x)) (reference: matmul.rs:268-280).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, long ld_in, T* __restrict__ out, long ld_out,
+                                const int* __restrict__ n_rows_dev, int rows, int n)
+{
+    const long total = (long)(n_rows_dev ? *n_rows_dev : rows) * n;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / n; const int c = (int)(i - r * n);
+        const float g = to_f32(gu[r * ld_in + c]);
+        const float u = to_f32(gu[r * ld_in + n + c]);
+        out[r * ld_out + c] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Rotary encoding (split-half pairing) of q and k, and the write of k and v into
+// their cache pages, in one pass over the fused q|k|v rows.
+//   angle = pos * inv_freq[i];  (x_i, x_{i+r/2}) <- (x_i cos - x_{i+r/2} sin, x_i sin + x_{i+r/2} cos)
+// (reference: crates/ferrox-core/src/attention.rs:20-32; applied per head at the
+// token's absolute position, decoder.rs:2106-2111, 3489-3507; K/V append
+// decoder.rs:2123-2125, paged cache.rs:382-404).  Elements beyond `rotary_dim`
+// pass through.  `inv_freq == nullptr` means no rotation (position encoding none).
+// Page layout: [page][kv_head][token_in_page][head_dim].
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __restrict__ positions,
+                                     const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                     const float* __restrict__ inv_freq, int rotary_dim,
+                                     T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                     const int* __restrict__ block_table, int table_width, int page_size,
+                                     int n_heads, int n_kv_heads, int head_dim, int write_cache,
+                                     int* __restrict__ status)
+{
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    T* row = qkv + (long)t * ld;
+    const int half = rotary_dim >> 1;
+    long page_base = -1;
+    if (write_cache) {
+        const int slot = seq_slot[token_seq[t]];
+        const int page = block_table[(long)slot * table_width + pos / page_size];
+        if (page < 0) { if (threadIdx.x == 0 && status) atomicExch(status, 2); }
+        else page_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * head_dim;
+    }
+    const int n_rot_heads = n_heads + n_kv_heads;
+    // rotate q and k heads in place
+    if (inv_freq) {
+        for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
+            const int h = idx / half, i = idx - h * half;
+            const float angle = (float)pos * inv_freq[i];
+            float s, c;
+            sincosf(angle, &s, &c);
+            T* x = row + (long)h * head_dim;
+            const float a = to_f32(x[i]), b = to_f32(x[i + half]);
+            x[i] = from_f32<T>(a * c - b * s);
+            x[i + half] = from_f32<T>(a * s + b * c);
+        }
+    }
+    if (page_base < 0) return;
+    __syncthreads();
+    const T* k = row + (long)n_heads * head_dim;
+    const T* v = k + (long)n_kv_heads * head_dim;
+    for (int idx = threadIdx.x; idx < n_kv_heads * head_dim; idx += blockDim.x) {
+        const int h = idx / head_dim, i = idx - h * head_dim;
+        const long dst = page_base + (long)h * page_size * head_dim + i;
+        k_pages[dst] = k[idx];
+        v_pages[dst] = v[idx];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// h[t,:] += sum_k w[t,k] * y[inv_perm[t*K+k], :]  (rank order k = 0..K-1)
+//          + (gate ? sigmoid(gate[t]) : 1) * shared[t,:]
+// (reference: crates/ferrox-moe/src/lib.rs:735-752; sigmoid gate on the shared
+// expert decoder.rs:2660-2681).  The sum per token has a fixed order, so it does
+// not depend on what else is in the batch.
+template <typename T>
+__global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ y, const int* __restrict__ inv_perm,
+                                   const float* __restrict__ topk_w, int top_k,
+                                   const T* __restrict__ shared, const float* __restrict__ shared_gate_logit,
+                                   int hidden)
+{
+    const int t = blockIdx.x;
+    float g = 1.f;
+    if (shared && shared_gate_logit) g = 1.0f / (1.0f + expf(-shared_gate_logit[t]));
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top_k; ++k) {
+            const long r = inv_perm[(long)t * top_k + k];
+            acc = fmaf(topk_w[(long)t * top_k + k], to_f32(y[r * hidden + i]), acc);
+        }
+        if (shared) acc = fmaf(g, to_f32(shared[(long)t * hidden + i]), acc);
+        h[(long)t * hidden + i] += acc;
+    }
+}
+
+// h[t,:] += y[t,:]
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ y, long n)
+{
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+        h[i] += to_f32(y[i]);
+}
+
+inline int threads_for(int n) { int t = 32; while (t < n && t < 1024) t <<= 1; return t; }
+
+}  // namespace
+
+extern "C" int fx_embed(const void* table, int dtype, const int* ids, float* out, int n_tokens, int hidden,
+                        int vocab, int* status, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nt = threads_for(hidden > 256 ? 256 : hidden);
+    if (dtype == FX_F32) embed_kernel<float><<<n_tokens, nt, 0, s>>>((const float*)table, ids, out, hidden, vocab, status);
+    else if (dtype == FX_BF16) embed_kernel<bf16><<<n_tokens, nt, 0, s>>>((const bf16*)table, ids, out, hidden, vocab, status);
+    else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+extern "C" int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, float eps, void* out,
+                          int out_dtype, int n_rows, int hidden, void* stream)
+{
+    if (n_rows <= 0) return FX_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nt = threads_for(hidden / 4 > 32 ? hidden / 4 : 32);
+    if (out_dtype == FX_F32) rmsnorm_kernel<float><<<n_rows, nt, 0, s>>>(x, rows, w, w_dtype, eps, (float*)out, hidden);
+    else if (out_dtype == FX_BF16) rmsnorm_kernel<bf16><<<n_rows, nt, 0, s>>>(x, rows, w, w_dtype, eps, (bf16*)out, hidden);
+    else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+extern "C" int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev,
+                           int rows, int n, void* stream)
+{
+    if (rows <= 0 || n <= 0) return FX_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    long blocks = fx_cdiv((long)rows * n, 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == FX_F32) silu_mul_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)gu, ld_in, (float*)out, ld_out, n_rows_dev, rows, n);
+    else if (dtype == FX_BF16) silu_mul_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((const bf16*)gu, ld_in, (bf16*)out, ld_out, n_rows_dev, rows, n);
+    else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+extern "C" int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const int* token_seq,
+                                const int* seq_slot, const float* inv_freq, int rotary_dim, void* k_pages,
+                                void* v_pages, const int* block_table, int table_width, int page_size, int n_tokens,
+                                int n_heads, int n_kv_heads, int head_dim, int write_cache, int* status, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (rotary_dim % 2 || rotary_dim > head_dim || page_size <= 0) return FX_ERR_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int work = (n_heads + n_kv_heads) * (head_dim / 2);
+    const int nt = threads_for(work > 256 ? 256 : work);
+    if (dtype == FX_F32)
+        rope_kv_write_kernel<float><<<n_tokens, nt, 0, s>>>((float*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
+            rotary_dim, (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
+            head_dim, write_cache, status);
+    else if (dtype == FX_BF16)
+        rope_kv_write_kernel<bf16><<<n_tokens, nt, 0, s>>>((bf16*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
+            rotary_dim, (bf16*)k_pages, (bf16*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
+            head_dim, write_cache, status);
+    else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+extern "C" int fx_moe_combine(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w, int top_k,
+                              const void* shared, const float* shared_gate_logit, int n_tokens, int hidden,
+                              void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int nt = threads_for(hidden > 256 ? 256 : hidden);
+    if (dtype == FX_F32)
+        moe_combine_kernel<float><<<n_tokens, nt, 0, s>>>(h, (const float*)y, inv_perm, topk_w, top_k,
+                                                          (const float*)shared, shared_gate_logit, hidden);
+    else if (dtype == FX_BF16)
+        moe_combine_kernel<bf16><<<n_tokens, nt, 0, s>>>(h, (const bf16*)y, inv_perm, topk_w, top_k,
+                                                         (const bf16*)shared, shared_gate_logit, hidden);
+    else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+extern "C" int fx_residual_add(float* h, const void* y, int dtype, long n, void* stream)
+{
+    if (n <= 0) return FX_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    long blocks = fx_cdiv(n, 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == FX_F32) residual_add_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(h, (const float*)y, n);
+    else if (dtype == FX_BF16) residual_add_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>(h, (const bf16*)y, n);
+    else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}

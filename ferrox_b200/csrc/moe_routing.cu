@@ -1,0 +1,122 @@
+// Routing of tokens to experts: softmax over all experts, top-k, optional
+// renormalisation; then the bookkeeping that sorts (token, rank) pairs by expert so
+// that each expert's rows are contiguous for the grouped matrix products.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+// One warp per token.  p = softmax(logits) over ALL experts (max-subtracted), the k
+// largest p are kept in descending order, on equal p the lowest expert index wins,
+// and the weights are the kept p, divided by their sum when `renorm` is set
+// (reference: crates/ferrox-moe/src/lib.rs:333-355; lowest-index tie-break as in
+// its GPU kernel, crates/ferrox-metal/src/gpu.rs:686-699).
+__global__ void router_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, int renorm,
+                                   int* __restrict__ ids, float* __restrict__ weights)
+{
+    extern __shared__ float smem[];  // [warps][n_experts]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    float* p = smem + (long)warp * n_experts;
+    const float* lg = logits + (long)t * n_experts;
+    float mx = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n_experts; e += 32) { const float v = expf(lg[e] - mx); p[e] = v; sum += v; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    float kept = 0.f;
+    for (int k = 0; k < top_k; ++k) {
+        float best = -1.f; int best_e = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = p[e];
+            if (v > best) { best = v; best_e = e; }  // ascending e: the first maximum stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        const float w = best / sum;
+        if (lane == 0) { ids[(long)t * top_k + k] = best_e; weights[(long)t * top_k + k] = w; p[best_e] = -2.f; }
+        kept += w;
+        __syncwarp();
+    }
+    if (renorm) {
+        __syncwarp();
+        for (int k = lane; k < top_k; k += 32) weights[(long)t * top_k + k] /= kept;
+    }
+}
+
+// counts[e] = number of (token, rank) pairs routed to e.
+__global__ void count_kernel(const int* __restrict__ ids, int n, int n_experts, int* __restrict__ counts)
+{
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+    }
+}
+
+// offsets = exclusive prefix sum of counts ([E+1]); cursors reset to 0.
+__global__ void scan_kernel(const int* __restrict__ counts, int n_experts, int* __restrict__ offsets,
+                            int* __restrict__ cursors)
+{
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_experts; ++e) { offsets[e] = run; run += counts[e]; cursors[e] = 0; }
+        offsets[n_experts] = run;
+    }
+}
+
+// Place pair i in its expert's segment.  The place inside the segment follows the
+// order in which threads arrive; every row is computed alone and read back through
+// inv_perm, so results do not depend on it.
+__global__ void place_kernel(const int* __restrict__ ids, int n, int n_experts, int top_k,
+                             const int* __restrict__ offsets, int* __restrict__ cursors,
+                             int* __restrict__ src_token, int* __restrict__ inv_perm)
+{
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int e = ids[i];
+        if (e < 0 || e >= n_experts) { inv_perm[i] = 0; continue; }
+        const int r = offsets[e] + atomicAdd(&cursors[e], 1);
+        src_token[r] = i / top_k;
+        inv_perm[i] = r;
+    }
+}
+
+}  // namespace
+
+extern "C" int fx_router_topk(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
+                              float* weights, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (top_k <= 0 || top_k > n_experts || n_experts > 4096) return FX_ERR_SIZE;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * n_experts * sizeof(float);
+    if (smem > 48 * 1024) return FX_ERR_SIZE;
+    router_topk_kernel<<<(unsigned)fx_cdiv(n_tokens, warps), warps * 32, smem, (cudaStream_t)stream>>>(
+        logits, n_tokens, n_experts, top_k, renorm, ids, weights);
+    return fx_launch_status();
+}
+
+// scratch: 2 * n_experts ints (counts, cursors).  Outputs: offsets [E+1],
+// src_token [n_tokens * top_k] (row of the sorted order -> token it reads),
+// inv_perm [n_tokens * top_k] (pair -> its row in the sorted order).
+extern "C" int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets,
+                            int* src_token, int* inv_perm, void* stream)
+{
+    const int n = n_tokens * top_k;
+    if (n <= 0) return FX_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(int) * 2 * n_experts, s);
+    if (e != cudaSuccess) return (int)e;
+    int blocks = (int)fx_cdiv(n, 256);
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    count_kernel<<<blocks, 256, 0, s>>>(ids, n, n_experts, scratch);
+    scan_kernel<<<1, 32, 0, s>>>(scratch, n_experts, offsets, scratch + n_experts);
+    place_kernel<<<blocks, 256, 0, s>>>(ids, n, n_experts, top_k, offsets, scratch + n_experts, src_token, inv_perm);
+    return fx_launch_status();
+}

@@ -1,0 +1,210 @@
+"""Thin Python entry to the kernels: torch tensors in, pointers out.
+
+Each function checks what the C side cannot (device, contiguity, dtype), passes
+pointers, sizes and the current CUDA stream to ``libferrox_b200.so`` and raises
+:class:`KernelError` on a non-zero status.  Nothing here computes: there is no
+torch fallback, and a CPU tensor is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+from . import lib as _libmod
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+_ERRORS = {
+    -1: "combination of element types not built",
+    -2: "a size outside what the kernel handles",
+    -3: "pointer or stride not aligned as the kernel requires",
+    -4: "a bounded wait inside a kernel ran out",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_P, _I, _L, _F = c_void_p, c_int, c_long, c_float
+_SIGNATURES = {
+    "fx_gemm": [_P, _I, _L, _P, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P, _I, _L, _P],
+    "fx_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "fx_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
+    "fx_silu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _P],
+    "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _P],
+    "fx_residual_add": [_P, _P, _I, _L, _P],
+    "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
+    "fx_router_topk": [_P, _I, _I, _I, _I, _P, _P, _P],
+    "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "fx_argmax": [_P, _L, _I, _I, _P, _P],
+    "fx_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
+    "fx_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
+}
+
+_fn = {}
+
+
+def _get(name: str):
+    f = _fn.get(name)
+    if f is None:
+        lib = _libmod.load()
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[name]
+        f.restype = c_int
+        _fn[name] = f
+    return f
+
+
+def register_signature(name: str, argtypes) -> None:
+    """Lets further source files of the library declare their entry points."""
+    _SIGNATURES[name] = list(argtypes)
+
+
+def call(name: str, *args) -> None:
+    rc = _get(name)(*args)
+    if rc != 0:
+        if rc > 0:
+            raise KernelError(f"{name}: CUDA error {rc} at launch ({torch.cuda.get_device_name()})")
+        raise KernelError(f"{name}: refused: {_ERRORS.get(rc, rc)}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not handled by the kernels") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernels take CUDA tensors only (there is no CPU path)")
+    return t.data_ptr()
+
+
+def _rows(t: torch.Tensor) -> int:
+    """Row stride of a 2-D tensor whose rows are contiguous."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"expected a 2-D tensor with contiguous rows, found shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+# ---------------------------------------------------------------------------
+def gemm(a, w, out, *, bias=None, accumulate=False, a_rows=None, group_offsets=None, stream=None):
+    """out[M,N] (+)= a[M,K] . w[N,K]^T (+ bias).  With ``group_offsets`` ([G+1],
+    int32) ``w`` is [G,N,K] and rows off[g]..off[g+1] use matrix g; ``a_rows``
+    gathers rows of ``a``."""
+    M, N = out.shape
+    if group_offsets is not None:
+        G, Nw, K = w.shape
+        wstride = w.stride(0)
+        ldw = w.stride(1)
+        if w.stride(2) != 1:
+            raise KernelError("grouped weights must have contiguous rows")
+    else:
+        G, wstride = 1, 0
+        Nw, K = w.shape
+        ldw = _rows(w)
+    if Nw != N or a.shape[1] != K or (a_rows is None and a.shape[0] != M):
+        raise KernelError(f"gemm shapes do not agree: a {tuple(a.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    call(
+        "fx_gemm", _ptr(a), code(a), _rows(a), _ptr(a_rows), _ptr(w), code(w), ldw,
+        _ptr(bias), code(bias) if bias is not None else 0, _ptr(out), code(out), _rows(out), int(accumulate),
+        M, N, K, _ptr(group_offsets), G, wstride, stream if stream is not None else stream_ptr(),
+    )
+    return out
+
+
+def embed(table, ids, out, status=None, stream=None):
+    T = ids.numel()
+    call("fx_embed", _ptr(table), code(table), _ptr(ids), _ptr(out), T, table.shape[1], table.shape[0], _ptr(status),
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def rmsnorm(x, weight, eps, out, rows=None, stream=None):
+    if x.dtype != torch.float32:
+        raise KernelError("rmsnorm reads the 32-bit residual stream")
+    n = out.shape[0]
+    call("fx_rmsnorm", _ptr(x), _ptr(rows), _ptr(weight), code(weight), float(eps), _ptr(out), code(out), n, x.shape[1],
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def silu_mul(gu, out, stream=None):
+    rows, n = out.shape
+    if gu.shape[1] != 2 * n:
+        raise KernelError("silu_mul expects [gate | up] rows of twice the output width")
+    call("fx_silu_mul", _ptr(gu), _rows(gu), _ptr(out), _rows(out), code(gu), None, rows, n,
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def rope_kv_write(qkv, positions, token_seq, seq_slot, inv_freq, rotary_dim, k_pages, v_pages, block_table, page_size,
+                  n_heads, n_kv_heads, head_dim, write_cache=True, status=None, stream=None):
+    T = qkv.shape[0]
+    call("fx_rope_kv_write", _ptr(qkv), code(qkv), _rows(qkv), _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
+         _ptr(inv_freq), rotary_dim, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
+         T, n_heads, n_kv_heads, head_dim, int(write_cache), _ptr(status), stream if stream is not None else stream_ptr())
+
+
+def paged_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,
+                    n_kv_heads, head_dim, window, scale, stream=None):
+    """``q`` is a [T, >= n_heads*head_dim] view whose rows start with the query heads."""
+    T = q.shape[0]
+    call("fx_paged_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), code(q), _ptr(block_table),
+         block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out), _rows(out), T,
+         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), stream if stream is not None else stream_ptr())
+    return out
+
+
+def router_topk(logits, top_k, renorm, ids, weights, stream=None):
+    T, E = logits.shape
+    call("fx_router_topk", _ptr(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights),
+         stream if stream is not None else stream_ptr())
+
+
+def moe_align(ids, n_experts, scratch, offsets, src_token, inv_perm, stream=None):
+    T, K = ids.shape
+    call("fx_moe_align", _ptr(ids), T, K, n_experts, _ptr(scratch), _ptr(offsets), _ptr(src_token), _ptr(inv_perm),
+         stream if stream is not None else stream_ptr())
+
+
+def moe_combine(h, y, inv_perm, topk_w, shared=None, shared_gate_logit=None, stream=None):
+    T, H = h.shape
+    call("fx_moe_combine", _ptr(h), _ptr(y), code(y), _ptr(inv_perm), _ptr(topk_w), topk_w.shape[1], _ptr(shared),
+         _ptr(shared_gate_logit), T, H, stream if stream is not None else stream_ptr())
+
+
+def residual_add(h, y, stream=None):
+    call("fx_residual_add", _ptr(h), _ptr(y), code(y), h.numel(), stream if stream is not None else stream_ptr())
+
+
+def argmax(logits, out, stream=None):
+    n, V = logits.shape
+    call("fx_argmax", _ptr(logits), _rows(logits), n, V, _ptr(out), stream if stream is not None else stream_ptr())
+    return out
+
+
+def repetition_penalty(work, history, hist_offsets, penalty, stream=None):
+    n, V = work.shape
+    call("fx_repetition_penalty", _ptr(work), _rows(work), n, V, _ptr(history), _ptr(hist_offsets), _ptr(penalty),
+         stream if stream is not None else stream_ptr())
+
+
+def sample(work, temperature, top_k, top_p, draw, out, stream=None):
+    n, V = work.shape
+    call("fx_sample", _ptr(work), _rows(work), n, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(draw), _ptr(out),
+         stream if stream is not None else stream_ptr())
+    return out

@@ -1,0 +1,95 @@
+"""Grouped-query attention over paged keys and values.
+
+    q = Wq x + bq, k = Wk x + bk, v = Wv x + bv     (one fused product, [q|k|v] rows)
+    q, k rotated at the token's absolute position; k, v written to the cache pages
+    head h attends with kv head h / (n_heads / n_kv_heads), scale 1/sqrt(head_dim),
+    over positions max(0, p-W+1)..p of its own request
+    h += Wo . concat(heads)
+
+Reference: crates/ferrox-models/src/decoder.rs:2075-2157 (one token), :3230-3549 (a
+batch), attention in crates/ferrox-core/src/attention.rs:402-524.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.specs import CacheSpec, KvCacheSpec
+from ..kernels import ops
+from ..weights.loader import TensorDecl
+from .base import Mixer, build_part, register_part
+
+
+def _common_dtype(tensors):
+    return torch.float32 if any(t.dtype == torch.float32 for t in tensors) else tensors[0].dtype
+
+
+class GqaAttention(Mixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        s = spec
+        if s.head_dim % 2 or s.head_dim > 256:
+            raise ValueError(f"head_dim={s.head_dim}: must be even and at most 256")
+        if s.n_heads % s.n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        self.position = build_part(s.position) if s.position is not None else None
+        self.q_size = s.n_heads * s.head_dim
+        self.kv_size = s.n_kv_heads * s.head_dim
+        self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
+
+    def cache_spec(self):
+        return CacheSpec(kv=KvCacheSpec(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window))
+
+    def tensor_decls(self):
+        s, p = self.spec, self.spec.prefix
+        d = [
+            TensorDecl(p + "q_proj.weight", (self.q_size, s.hidden)),
+            TensorDecl(p + "k_proj.weight", (self.kv_size, s.hidden)),
+            TensorDecl(p + "v_proj.weight", (self.kv_size, s.hidden)),
+            TensorDecl(p + "o_proj.weight", (s.hidden, self.q_size)),
+        ]
+        if s.qkv_bias:
+            d += [
+                TensorDecl(p + "q_proj.bias", (self.q_size,)),
+                TensorDecl(p + "k_proj.bias", (self.kv_size,)),
+                TensorDecl(p + "v_proj.bias", (self.kv_size,)),
+            ]
+        return d
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        p = self.spec.prefix
+        ws = [src.get(p + f"{n}_proj.weight") for n in "qkv"]
+        dt = _common_dtype(ws)
+        self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
+        self.b_qkv = None
+        if self.spec.qkv_bias:
+            bs = [src.get(p + f"{n}_proj.bias") for n in "qkv"]
+            bdt = _common_dtype(bs)
+            self.b_qkv = torch.cat([b.to(bdt) for b in bs]).contiguous()
+        self.w_o = src.get(p + "o_proj.weight")
+        if self.position is not None:
+            self.position.load(src, rt)
+
+    def forward_add(self, x, h, batch, cache):
+        s = self.spec
+        T = x.shape[0]
+        qkv = self.rt.empty(T, self.q_size + 2 * self.kv_size)
+        ops.gemm(x, self.w_qkv, qkv, bias=self.b_qkv, stream=batch.stream)
+        inv_freq = self.position.inv_freq if self.position is not None else None
+        rotary = self.position.rotary_dim if self.position is not None else 0
+        ops.rope_kv_write(
+            qkv, batch.positions, batch.token_seq, batch.seq_slot, inv_freq, rotary, cache.k, cache.v,
+            cache.block_table, cache.page_size, s.n_heads, s.n_kv_heads, s.head_dim,
+            write_cache=cache.writes, status=batch.status, stream=batch.stream,
+        )
+        attn = self.rt.empty(T, self.q_size)
+        ops.paged_attention(
+            qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
+            batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
+        )
+        ops.gemm(attn, self.w_o, h, accumulate=True, stream=batch.stream)
+
+
+register_part("gqa_attention", GqaAttention, replace=True)

@@ -1,0 +1,37 @@
+"""Arrangement of a layer's parts: pre-norm with two residual additions,
+
+    h += mixer(norm1(h));  h += ffn(norm2(h))
+
+(reference: crates/ferrox-models/src/decoder.rs:2054-2173).  The block asks its
+mixer what cache it needs and passes the step's batch through; it is built from
+whatever norm, mixer and feed-forward its spec names.
+"""
+from __future__ import annotations
+
+from .base import Block, build_part, register_part
+
+
+class PreNormBlock(Block):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.norm1 = build_part(spec.norm1)
+        self.mixer = build_part(spec.mixer)
+        self.norm2 = build_part(spec.norm2)
+        self.ffn = build_part(spec.ffn)
+
+    def tensor_decls(self):
+        return (
+            self.norm1.tensor_decls() + self.mixer.tensor_decls() + self.norm2.tensor_decls() + self.ffn.tensor_decls()
+        )
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        for part in (self.norm1, self.mixer, self.norm2, self.ffn):
+            part.load(src, rt)
+
+    def forward(self, h, batch, cache):
+        self.mixer.forward_add(self.norm1.forward(h), h, batch, cache)
+        self.ffn.forward_add(self.norm2.forward(h), h, batch)
+
+
+register_part("pre_norm", PreNormBlock, replace=True)

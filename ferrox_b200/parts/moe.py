@@ -1,0 +1,105 @@
+"""Mixture-of-experts feed-forward with a softmax router.
+
+    p = softmax(Wr x) over all experts; the top-k p, in descending order, are the
+    weights (divided by their sum if ``norm_topk_prob``);
+    y = sum_k w_k * down_e( silu(gate_e x) * (up_e x) ), summed in rank order;
+    y += sigmoid(w_sg . x) * shared(x)   (the gate only if the checkpoint has it).
+
+Reference: router crates/ferrox-moe/src/lib.rs:333-355, expert :619-659, combine
+:735-752, shared expert and its sigmoid gate crates/ferrox-models/src/decoder.rs:
+2660-2681 and (batched) :1037-1093; tokens bucketed by expert :2792-2890.
+
+Tokens are sorted by expert on the device (no host round trip between the router
+and the experts); each expert's rows form one group of a grouped matrix product.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorDecl
+from .base import FeedForward, register_part
+from .mlp import pack_gate_up
+
+
+class SoftmaxTopkMoe(FeedForward):
+    def tensor_decls(self):
+        s, p = self.spec, self.spec.prefix
+        d = [TensorDecl(p + "gate.weight", (s.n_experts, s.hidden))]
+        for e in range(s.n_experts):
+            d += [
+                TensorDecl(p + f"experts.{e}.gate_proj.weight", (s.expert_intermediate, s.hidden)),
+                TensorDecl(p + f"experts.{e}.up_proj.weight", (s.expert_intermediate, s.hidden)),
+                TensorDecl(p + f"experts.{e}.down_proj.weight", (s.hidden, s.expert_intermediate)),
+            ]
+        if s.shared_intermediate > 0:
+            d += [
+                TensorDecl(p + "shared_expert.gate_proj.weight", (s.shared_intermediate, s.hidden)),
+                TensorDecl(p + "shared_expert.up_proj.weight", (s.shared_intermediate, s.hidden)),
+                TensorDecl(p + "shared_expert.down_proj.weight", (s.hidden, s.shared_intermediate)),
+            ]
+            if s.shared_gate:
+                d.append(TensorDecl(p + "shared_expert_gate.weight", (1, s.hidden), optional=True))
+        return d
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        s, p = self.spec, self.spec.prefix
+        self.w_router = src.get(p + "gate.weight")
+        E, I, H = s.n_experts, s.expert_intermediate, s.hidden
+        # If any expert tensor is stored in 32 bits, the packed buffers are 32-bit.
+        names = [p + f"experts.{e}.{n}_proj.weight" for e in range(E) for n in ("gate", "up", "down")]
+        dt = torch.float32 if any(src.dtype_of(n) == torch.float32 for n in names) else rt.dtype
+        self.w_gu = torch.empty(E, 2 * I, H, dtype=dt, device=rt.device)
+        self.w_down = torch.empty(E, H, I, dtype=dt, device=rt.device)
+        for e in range(E):
+            self.w_gu[e, :I].copy_(src.get(p + f"experts.{e}.gate_proj.weight"))
+            self.w_gu[e, I:].copy_(src.get(p + f"experts.{e}.up_proj.weight"))
+            self.w_down[e].copy_(src.get(p + f"experts.{e}.down_proj.weight"))
+        self.w_shared_gu = self.w_shared_down = self.w_shared_gate = None
+        if s.shared_intermediate > 0:
+            self.w_shared_gu = pack_gate_up(
+                src.get(p + "shared_expert.gate_proj.weight"), src.get(p + "shared_expert.up_proj.weight")
+            )
+            self.w_shared_down = src.get(p + "shared_expert.down_proj.weight")
+            if s.shared_gate and src.has(p + "shared_expert_gate.weight"):
+                self.w_shared_gate = src.get(p + "shared_expert_gate.weight").reshape(1, H).contiguous()
+        self._scratch = torch.zeros(2 * E, dtype=torch.int32, device=rt.device)
+
+    def forward_add(self, x, h, batch):
+        s, rt, st = self.spec, self.rt, batch.stream
+        T, E, K, I, H = x.shape[0], s.n_experts, s.top_k, s.expert_intermediate, s.hidden
+        i32 = torch.int32
+        logits = rt.empty(T, E, dtype=torch.float32)
+        ops.gemm(x, self.w_router, logits, stream=st)
+        ids = rt.empty(T, K, dtype=i32)
+        weights = rt.empty(T, K, dtype=torch.float32)
+        ops.router_topk(logits, K, s.norm_topk_prob, ids, weights, stream=st)
+        offsets = rt.empty(E + 1, dtype=i32)
+        src_token = rt.empty(T * K, dtype=i32)
+        inv_perm = rt.empty(T * K, dtype=i32)
+        ops.moe_align(ids, E, self._scratch, offsets, src_token, inv_perm, stream=st)
+
+        gu = rt.empty(T * K, 2 * I)
+        ops.gemm(x, self.w_gu, gu, a_rows=src_token, group_offsets=offsets, stream=st)
+        act = rt.empty(T * K, I)
+        ops.silu_mul(gu, act, stream=st)
+        y = rt.empty(T * K, H)
+        ops.gemm(act, self.w_down, y, group_offsets=offsets, stream=st)
+
+        shared = gate_logit = None
+        if self.w_shared_gu is not None:
+            Is = s.shared_intermediate
+            sgu = rt.empty(T, 2 * Is)
+            ops.gemm(x, self.w_shared_gu, sgu, stream=st)
+            sact = rt.empty(T, Is)
+            ops.silu_mul(sgu, sact, stream=st)
+            shared = rt.empty(T, H)
+            ops.gemm(sact, self.w_shared_down, shared, stream=st)
+            if self.w_shared_gate is not None:
+                gate_logit = rt.empty(T, 1, dtype=torch.float32)
+                ops.gemm(x, self.w_shared_gate, gate_logit, stream=st)
+        ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st)
+
+
+register_part("softmax_topk_moe", SoftmaxTopkMoe, replace=True)

@@ -1,0 +1,110 @@
+"""The engine against the plain implementation under every way of cutting the work:
+whole prompts, a decoded tail, portions of changing size, mixed batches with pages
+used again; in 32-bit and in bfloat16; on tiny configurations that differ in every
+size and option."""
+import random
+
+import pytest
+import torch
+
+import replay_util as ru
+from tiny_configs import CONFIGS, make_folder
+
+pytestmark = pytest.mark.gpu
+
+# Largest |difference| allowed, relative to the largest |logit| of the request.
+# 32-bit: both sides round 32-bit sums in different orders.  bfloat16: activations
+# between kernels are rounded to 8 bits of mantissa.
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+def prompts_for(name, n=5, lo=1, hi=96, seed=0):
+    cfg = CONFIGS[name][0]
+    rng = random.Random(seed)
+    hi = min(hi, cfg["max_position_embeddings"])
+    lens = [lo, 2, hi] + [rng.randint(lo, hi) for _ in range(max(0, n - 3))]
+    return {f"r{i}": [rng.randrange(cfg["vocab_size"]) for _ in range(L)] for i, L in enumerate(lens)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("models")
+    return {name: make_folder(tmp, name) for name in CONFIGS}
+
+
+@pytest.fixture(scope="module")
+def expected(folders):
+    return {name: ru.plain_logits(folders[name], prompts_for(name)) for name in CONFIGS}
+
+
+def engine(folder, dtype, **kw):
+    from ferrox_b200 import Engine
+
+    return Engine.from_folder(folder, dtype=dtype, **kw)
+
+
+def compare(got, want, tol, what):
+    worst = 0.0
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, (what, rid)
+        assert torch.isfinite(got[rid]).all(), (what, rid)
+        err = ru.max_rel_err(got[rid], want[rid])
+        if err > tol:
+            diff = (got[rid] - want[rid]).abs().max(dim=1).values / want[rid].abs().max()
+            first = int((diff > tol).nonzero()[0])
+            raise AssertionError(f"{what}: request {rid} (length {want[rid].shape[0]}): relative error {err:.3e} > {tol}; "
+                                 f"first wrong position {first}")
+        worst = max(worst, err)
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_prompts(folders, expected, name, dtype):
+    eng = engine(folders[name], dtype, page_size=16, n_pages=16, max_slots=4)
+    got = ru.run_whole(eng, prompts_for(name))
+    compare(got, expected[name], TOL[dtype], f"whole/{name}/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_tail_decoded_one_by_one(folders, expected, name, dtype):
+    eng = engine(folders[name], dtype, page_size=16, n_pages=16, max_slots=4)
+    got = ru.run_tail_decode(eng, prompts_for(name), tail=32)
+    compare(got, expected[name], TOL[dtype], f"tail/{name}/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("page_size", [4, 16, 64])
+def test_portions_of_changing_size(folders, expected, name, dtype, page_size):
+    eng = engine(folders[name], dtype, page_size=page_size, n_pages=max(2, 128 // page_size), max_slots=4)
+    got = ru.run_portions(eng, prompts_for(name))
+    compare(got, expected[name], TOL[dtype], f"portions/{name}/{dtype}/ps{page_size}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("page_size", [4, 16])
+def test_mixed_batches_reuse_pages(folders, name, dtype, page_size):
+    prompts = prompts_for(name, n=9, seed=3)
+    want = ru.plain_logits(folders[name], prompts)
+    # four live requests of at most 96 tokens: exactly enough pages, so that every
+    # page a finished request gives back is taken again by a later one
+    eng = engine(folders[name], dtype, page_size=page_size, n_pages=4 * (96 // page_size), max_slots=4)
+    got = ru.run_mixed(eng, prompts, seed=5)
+    compare(got, want, TOL[dtype], f"mixed/{name}/{dtype}/ps{page_size}")
+    assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_cutting_changes_nothing_beyond_rounding_fp32(folders, name):
+    """The same positions through different cuts agree far more tightly than either
+    agrees with another implementation: the sums run in the same order."""
+    prompts = prompts_for(name)
+    a = ru.run_whole(engine(folders[name], "float32", page_size=16, n_pages=16, max_slots=4), prompts)
+    b = ru.run_portions(engine(folders[name], "float32", page_size=4, n_pages=64, max_slots=4), prompts)
+    c = ru.run_mixed(engine(folders[name], "float32", page_size=16, n_pages=24, max_slots=4), prompts, seed=1)
+    for rid in prompts:
+        assert ru.max_rel_err(b[rid], a[rid]) < 2e-6
+        assert ru.max_rel_err(c[rid], a[rid]) < 2e-6
