@@ -44,6 +44,7 @@ class StepBatch:
     entries: List[StepEntry] = field(default_factory=list)  # host view, for parts written in Python
     max_len: int = 0  # longest request length after this step
     max_new: int = 0  # most tokens any entry brings
+    h2d_bytes: int = 0  # size of the step's host-to-device copy
 
 
 def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: int) -> StepBatch:
@@ -75,4 +76,5 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
         token_ids=dev[:T], positions=dev[T:2 * T], token_seq=dev[2 * T:3 * T],
         seq_slot=dev[3 * T:3 * T + B], want_rows=dev[3 * T + B:],
         status=status, stream=stream, entries=list(entries), max_len=max_len, max_new=max_new,
+        h2d_bytes=buf.nbytes,
     )

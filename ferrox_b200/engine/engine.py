@@ -109,7 +109,7 @@ class Engine:
 
     # ---- generation -------------------------------------------------------------
     def generate(self, prompts, max_new_tokens=128, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
-                 seed=0, ignore_eos=False, eos_token_id=None, max_batch_tokens=2048) -> List[List[int]]:
+                 seed=0, ignore_eos=False, eos_token_id=None, max_batch_tokens=2048, return_stats=False):
         """Greedy (temperature 0) or sampled continuation of each prompt.  ``prompts``
         is a list of token-id lists (a single list of ints is one prompt; strings are
         encoded byte by byte).  Returns the generated ids of each prompt, in order."""
@@ -129,7 +129,16 @@ class Engine:
             ids.append(sched.add_request(p, max_new_tokens, params, eos_ids=() if ignore_eos else eos))
         sched.run()
         outs = [sched.result(i) for i in ids]
-        return outs[0] if single else outs
+        outs = outs[0] if single else outs
+        if return_stats:
+            c = sched.counters
+            n = max(1, c.decode_steps)
+            return outs, {
+                "steps": c.steps, "prefill_tokens": c.prefill_tokens, "decode_tokens": c.decode_step_tokens,
+                "decode_steps": c.decode_steps, "decode_seconds": c.decode_seconds, "preemptions": c.preemptions,
+                "h2d_bytes_per_decode_step": c.decode_h2d_bytes / n, "d2h_bytes_per_decode_step": c.decode_d2h_bytes / n,
+            }
+        return outs
 
 
 def _require_cuda(device) -> None:

@@ -26,7 +26,11 @@ class StepFault(RuntimeError):
     """A kernel met a token id outside the vocabulary or a position without a page."""
 
 
+last_h2d_bytes = 0  # host-to-device bytes of the most recent step (token ids, positions, slots)
+
+
 def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True) -> torch.Tensor:
+    global last_h2d_bytes
     if not entries:
         return model.rt.empty(0, model.spec.vocab_size, dtype=torch.float32)
     seen = set()
@@ -54,6 +58,7 @@ def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True) -> t
 
     status = _status(model.rt.device)
     batch = flatten(entries, model.rt.device, status, ops.stream_ptr())
+    last_h2d_bytes = batch.h2d_bytes
     logits = model.forward(batch, lambda entry: cache.layer_cache(entry.cache, entry.writes_cache))
     for e in entries:
         cache.commit(e.slot, e.start + len(e.tokens))

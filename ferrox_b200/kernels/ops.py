@@ -49,6 +49,15 @@ _SIGNATURES = {
 
 _fn = {}
 
+# kernels launched by one call of an entry point (fx_moe_align: count, scan, place)
+_KERNELS = {"fx_moe_align": 3}
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process."""
+    return _launches
+
 
 def _get(name: str):
     f = _fn.get(name)
@@ -67,6 +76,8 @@ def register_signature(name: str, argtypes) -> None:
 
 
 def call(name: str, *args) -> None:
+    global _launches
+    _launches += _KERNELS.get(name, 1)
     rc = _get(name)(*args)
     if rc != 0:
         if rc > 0:

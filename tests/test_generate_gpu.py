@@ -1,0 +1,192 @@
+"""Generation through the public entry point, sampling, and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen2moe as plain
+from tiny_configs import CONFIGS, make_folder
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("gen")
+    # std 0.2: logits far enough apart that greedy choices survive 32-bit rounding
+    return {name: make_folder(tmp, name, std=0.2) for name in CONFIGS}
+
+
+def engine(folder, dtype="float32", **kw):
+    from ferrox_b200 import Engine
+
+    kw.setdefault("page_size", 16)
+    kw.setdefault("n_pages", 32)
+    kw.setdefault("max_slots", 4)
+    return Engine.from_folder(folder, dtype=dtype, **kw)
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_greedy_generation_matches_plain(folders, name):
+    cfg, w = plain.load_model(folders[name])
+    prompts = [[5, 9, 200, 31], [7], list(range(40, 75))]
+    want = [plain.greedy(cfg, w, p, 12) for p in prompts]
+    eng = engine(folders[name])
+    assert eng.generate(prompts, max_new_tokens=12) == want
+    assert eng.generate(prompts[0], max_new_tokens=12) == want[0]  # a single prompt
+    # small budget: prompts cut into portions, decodes beside them
+    assert eng.generate(prompts, max_new_tokens=12, max_batch_tokens=5) == want
+    eng.cache.check_invariants()
+    assert eng.cache.n_free_slots == 4
+
+
+def test_generation_with_preemption_gives_the_same_tokens(folders):
+    cfg, w = plain.load_model(folders["A"])
+    prompts = [[i + 1, i + 3, i + 7, 99, 4, 8, 15, 16] for i in range(4)]
+    want = [plain.greedy(cfg, w, p, 20) for p in prompts]
+    eng = engine(folders["A"], page_size=4, n_pages=14, max_slots=4)  # 4 x 27 positions do not fit 56
+    outs, stats = eng.generate(prompts, max_new_tokens=20, return_stats=True)
+    assert stats["preemptions"] >= 1
+    assert outs == want
+
+
+def test_long_decoding_stays_on_the_plain_implementation(folders):
+    """One token at a time up to the context's end (pages and, for B, the window roll over many times)."""
+    for name in ("A", "B"):
+        cfg, w = plain.load_model(folders[name])
+        n = cfg["max_position_embeddings"] - 4
+        got = engine(folders[name], page_size=4, n_pages=64).generate([[1, 2, 3]], max_new_tokens=n)[0]
+        seq = [1, 2, 3] + got
+        logits = plain.forward(cfg, w, seq[:-1])
+        # every generated token is the plain implementation's choice given the same history
+        want = logits[2:].argmax(dim=-1).tolist()
+        assert got == want
+
+
+def test_bfloat16_generation_runs_and_starts_alike(folders):
+    cfg, w = plain.load_model(folders["A"])
+    want = plain.greedy(cfg, w, [5, 9, 200, 31], 6)
+    got = engine(folders["A"], "bfloat16").generate([[5, 9, 200, 31]], max_new_tokens=6)[0]
+    assert len(got) == 6 and got[0] == want[0]
+
+
+def test_eos_and_string_prompts(folders):
+    eng = engine(folders["A"])
+    free = eng.generate([[5, 9, 200, 31]], max_new_tokens=10)[0]
+    eos = free[4]
+    stopped = eng.generate([[5, 9, 200, 31]], max_new_tokens=10, eos_token_id=eos)[0]
+    assert stopped == free[:free.index(eos)]
+    assert eng.generate([[5, 9, 200, 31]], max_new_tokens=10, eos_token_id=eos, ignore_eos=True)[0] == free
+    assert eng.generate(["hi"], max_new_tokens=3) == eng.generate([[104, 105]], max_new_tokens=3)
+    with pytest.raises(ValueError, match="vocab"):
+        eng.generate([[5, 999]], max_new_tokens=1)
+
+
+def test_sampling_follows_the_reference_procedure(folders):
+    """Device sampling against a plain restatement of sampling.rs:93-189."""
+    from ferrox_b200.sampling.sampler import Sampler, SamplingParams, XorShift64
+
+    torch.manual_seed(0)
+    V = 331
+    logits = (torch.randn(6, V) * 3).cuda()
+    hist = [[], [1, 2, 2, 5], [7], [], [3, 3, 3], [9]]
+    params = [
+        SamplingParams(temperature=0.0),
+        SamplingParams(temperature=0.0, repetition_penalty=1.5),
+        SamplingParams(temperature=0.7, seed=11),
+        SamplingParams(temperature=1.3, top_k=5, seed=12),
+        SamplingParams(temperature=0.9, top_p=0.6, repetition_penalty=1.2, seed=13),
+        SamplingParams(temperature=1.0, top_k=40, top_p=0.95, seed=14),
+    ]
+
+    def plain_sample(row, p, rng, h):
+        s = row.clone()
+        if p.repetition_penalty != 1.0:
+            for t in h:
+                s[t] = s[t] / p.repetition_penalty if s[t] > 0 else s[t] * p.repetition_penalty
+        if p.temperature <= 0:
+            return int(torch.argmax(s))
+        pr = torch.softmax(s / p.temperature, dim=0)
+        if 0 < p.top_k < V:
+            kth = torch.topk(pr, p.top_k).values[-1]
+            pr = torch.where(pr >= kth, pr, torch.zeros_like(pr))
+        if p.top_p < 1.0:
+            order = torch.argsort(pr, descending=True)
+            c = torch.cumsum(pr[order], 0)
+            cut = int((c >= p.top_p).nonzero()[0]) + 1 if bool((c >= p.top_p).any()) else V
+            keep = torch.zeros(V, dtype=torch.bool)
+            keep[order[:cut]] = True
+            pr = torch.where(keep, pr, torch.zeros_like(pr))
+        pr = pr / pr.sum()
+        draw = rng.next_f32()
+        c = torch.cumsum(pr, 0)
+        idx = (draw < c).nonzero()
+        return int(idx[0]) if len(idx) else int((pr > 0).nonzero()[-1])
+
+    sampler = Sampler("cuda:0")
+    rngs_a = [XorShift64(p.seed) for p in params]
+    rngs_b = [XorShift64(p.seed) for p in params]
+    cpu = logits.cpu()
+    for _ in range(20):
+        got = sampler.sample(logits, params, rngs_a, hist)
+        want = [plain_sample(cpu[i], params[i], rngs_b[i], hist[i]) for i in range(6)]
+        assert got == want
+    # temperature -> 0+ and top_k = 1 both reduce to greedy (sampling.rs:241-380)
+    g = sampler.sample(logits, [SamplingParams()] * 6, rngs_a, hist)
+    k1 = sampler.sample(logits, [SamplingParams(temperature=1.0, top_k=1, seed=3)] * 6, [XorShift64(3) for _ in range(6)], hist)
+    p0 = sampler.sample(logits, [SamplingParams(temperature=1.0, top_p=1e-6, seed=3)] * 6, [XorShift64(3) for _ in range(6)], hist)
+    assert g == k1 == p0 == cpu.argmax(dim=1).tolist()
+
+
+def test_sampled_generation_is_seeded_and_batch_independent(folders):
+    eng = engine(folders["A"])
+    a = eng.generate([[5, 9, 200, 31]], max_new_tokens=16, temperature=0.9, top_k=20, seed=5)[0]
+    b = eng.generate([[5, 9, 200, 31]], max_new_tokens=16, temperature=0.9, top_k=20, seed=5)[0]
+    c = eng.generate([[5, 9, 200, 31]], max_new_tokens=16, temperature=0.9, top_k=20, seed=6)[0]
+    both = eng.generate([[5, 9, 200, 31], [8, 8, 8]], max_new_tokens=16, temperature=0.9, top_k=20, seed=5)
+    assert a == b and a != c and both[0] == a
+
+
+def test_command_line(folders, tmp_path):
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "ferrox"), "-m", folders["A"], "--tokens", "5,9,200,31",
+                        "-n", "6", "--temp", "0", "--dtype", "float32", "--repeat-penalty", "1.0"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr
+    cfg, w = plain.load_model(folders["A"])
+    assert [int(t) for t in r.stdout.split()] == plain.greedy(cfg, w, [5, 9, 200, 31], 6)
+    assert "ferrox: prompt 4 tokens" in r.stderr and "predict 6 tokens" in r.stderr
+    r = subprocess.run([sys.executable, "-m", "ferrox_b200", "run", "-m", folders["A"], "-p", "ab", "-n", "3", "--temp", "0.8",
+                        "-s", "1", "--print-ids"], capture_output=True, text=True, env=env, timeout=600, cwd=ROOT)
+    assert r.returncode == 0 and len(r.stdout.split()) == 3, r.stderr
+
+
+def test_trace_run_tool(folders, tmp_path):
+    cfg, w = plain.load_model(folders["B"])
+    toks = {"a": [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], "b": [2, 7, 1, 8, 2, 8]}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": toks["a"][:5], "want": [4]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": toks["a"][5:7], "want": []},
+                                {"id": "b", "tokens": toks["b"], "want": [0, 5]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": toks["a"][7:], "want": [0, 3]}], "end": ["a"]},
+    ]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folders["B"], "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.split("\n")[:3] == ["done 0", "done 1", "done 2"]
+    import numpy as np
+
+    la, lb = plain.forward(cfg, w, toks["a"]), plain.forward(cfg, w, toks["b"])
+    V = cfg["vocab_size"]
+    s0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, V)
+    s1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(-1, V)
+    s2 = np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, V)
+    assert s0.shape[0] == 1 and s1.shape[0] == 2 and s2.shape[0] == 2
+    for got, want in ((s0[0], la[4]), (s1[0], lb[0]), (s1[1], lb[5]), (s2[0], la[7]), (s2[1], la[10])):
+        assert float(np.abs(got - want.numpy()).max()) < 2e-5 * float(want.abs().max())
