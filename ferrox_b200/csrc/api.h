@@ -33,7 +33,17 @@ int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void*
 int fx_router_topk(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
                    void* stream);
 int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets, int* src_token,
-                 int* inv_perm, void* stream);
+                 int* inv_perm, int* active, int n_slots, void* stream);
+
+int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, long ldw, long w_group_stride,
+                   const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int n_tokens,
+                   int N, int K, int gated, int gate_up_offset, const int* group_offsets, const int* active_groups,
+                   int n_slots, int tokens_hint, void* stream);
+int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
+                        const int* block_table, int table_width, int page_size, const int* positions,
+                        const int* token_seq, const int* seq_slot, void* out, long ldo, float* part_acc,
+                        float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
+                        float scale, int split_len, int n_splits, void* stream);
 
 int fx_argmax(const float* logits, long ld, int n_rows, int vocab, int* out, void* stream);
 int fx_repetition_penalty(float* work, long ld, int n_rows, int vocab, const int* history, const int* hist_offsets,

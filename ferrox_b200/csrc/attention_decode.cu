@@ -1,0 +1,284 @@
+// Attention for steps with few query tokens (decoding, short portions): the keys of
+// each request are split into ranges that separate blocks read, so that one long
+// context keeps many SMs busy; a second kernel merges the ranges.
+//
+//   grid = (kv head [x head chunk], query token, split)
+//   split s covers the absolute key positions [s * split_len, (s+1) * split_len),
+//   clipped to the token's visible range [max(0, p - W + 1), p].
+//
+// A block reads each key and value of its range once for all query heads that
+// share the kv head (up to 8; more are handled by further head chunks).  Threads
+// form groups of LPK lanes; a group takes every (128/LPK)-th key, each lane
+// holding 8 (bfloat16) or 4 (float) consecutive elements of the head dimension,
+// scores it with a group-wide sum and keeps a running (m, l, acc) per query head.
+// The groups are merged in fixed order through shared memory, the block writes
+// (m, l, acc) for its split to scratch memory, and `merge` combines the splits in
+// order.  All sums are 32-bit.  split_len depends on the step's size and the
+// context limit, never on the requests' current lengths.
+//
+// Reference: one warp per head over a contiguous cache
+// (crates/ferrox-cuda/src/attn.rs:22-79); online softmax
+// crates/ferrox-core/src/attention.rs:146-175; window :484-524; pages :572-610.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+constexpr int NTHREADS = 128;
+constexpr int MAXQ = 8;      // query heads per block
+constexpr int MAX_D = 256;
+
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* o) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    }
+};
+template <> struct Vec<bf16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16* p, float* o) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[2 * i] = __uint_as_float(w[i] << 16);
+            o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+// exp in full precision on the 32-bit path, the fast approximation on the bfloat16 path
+template <typename T> __device__ __forceinline__ float fx_exp(float x);
+template <> __device__ __forceinline__ float fx_exp<float>(float x) { return expf(x); }
+template <> __device__ __forceinline__ float fx_exp<bf16>(float x) { return __expf(x); }
+
+// LPK lanes per key; each lane owns VPL vectors of Vec<T>::N elements: element
+// index of vector v of lane ln is (v * LPK + ln) * N.
+template <typename T, int LPK, int VPL, int GQ>
+__global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
+    const T* __restrict__ q, long ldq, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+    const int* __restrict__ block_table, int table_width, int page_size,
+    const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+    float* __restrict__ part_acc, float* __restrict__ part_ml,
+    int n_heads, int n_kv_heads, int head_dim, int window, float scale, int split_len, int n_splits)
+{
+    constexpr int N = Vec<T>::N;
+    constexpr int GROUPS = NTHREADS / LPK;
+    const int group_size = n_heads / n_kv_heads;
+    const int chunks = (group_size + GQ - 1) / GQ;
+    const int kvh = blockIdx.x / chunks;
+    const int h0 = kvh * group_size + (blockIdx.x % chunks) * GQ;   // first query head of this block
+    const int nq = min(GQ, kvh * group_size + group_size - h0);
+    const int tkn = blockIdx.y, split = blockIdx.z;
+    const int pos = positions[tkn];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int k_begin = max(lo, split * split_len);
+    const int k_end = min(pos + 1, (split + 1) * split_len);
+    const int grp = threadIdx.x / LPK, ln = threadIdx.x % LPK;
+
+    float qr[GQ][VPL][N], acc[GQ][VPL][N], m[GQ], l[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; ++h) {
+        m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+            const int e = (v * LPK + ln) * N;
+#pragma unroll
+            for (int i = 0; i < N; ++i) { acc[h][v][i] = 0.f; qr[h][v][i] = 0.f; }
+            if (h < nq && e < head_dim) Vec<T>::load(q + (long)tkn * ldq + (long)(h0 + h) * head_dim + e, qr[h][v]);
+        }
+    }
+
+    if (k_begin < k_end) {
+        const int* table = block_table + (long)seq_slot[token_seq[tkn]] * table_width;
+        const long head_stride = (long)page_size * head_dim;
+        // the loop bounds are the same for every thread, so the group-wide shuffles
+        // below are always executed by whole warps
+        for (int kb = k_begin; kb < k_end; kb += GROUPS) {
+            const int key = kb + grp;
+            bool valid = key < k_end;
+            const int page = valid ? table[key / page_size] : -1;
+            valid = valid && page >= 0;  // a position without a page is skipped, never dereferenced
+            const long base = valid ? ((long)page * n_kv_heads + kvh) * head_stride + (long)(key % page_size) * head_dim : 0;
+            float kv[VPL][N];
+            float s[GQ];
+#pragma unroll
+            for (int h = 0; h < GQ; ++h) s[h] = 0.f;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                const int e = (v * LPK + ln) * N;
+                if (valid && e < head_dim) {
+                    Vec<T>::load(k_pages + base + e, kv[v]);
+#pragma unroll
+                    for (int h = 0; h < GQ; ++h)
+#pragma unroll
+                        for (int i = 0; i < N; ++i) s[h] = fmaf(qr[h][v][i], kv[v][i], s[h]);
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < GQ; ++h)
+#pragma unroll
+                for (int o = LPK / 2; o > 0; o >>= 1) s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);
+            if (!valid) continue;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                const int e = (v * LPK + ln) * N;
+#pragma unroll
+                for (int i = 0; i < N; ++i) kv[v][i] = 0.f;
+                if (e < head_dim) Vec<T>::load(v_pages + base + e, kv[v]);
+            }
+#pragma unroll
+            for (int h = 0; h < GQ; ++h) {
+                const float sc = s[h] * scale;
+                const float m_new = fmaxf(m[h], sc);
+                const float alpha = fx_exp<T>(m[h] - m_new);   // m = -inf at first: exp(-inf) = 0
+                const float p = fx_exp<T>(sc - m_new);
+                l[h] = l[h] * alpha + p;
+#pragma unroll
+                for (int v = 0; v < VPL; ++v)
+#pragma unroll
+                    for (int i = 0; i < N; ++i) acc[h][v][i] = acc[h][v][i] * alpha + p * kv[v][i];
+                m[h] = m_new;
+            }
+        }
+    }
+
+    // merge the groups of this block, in group order
+    __shared__ float sm_m[GROUPS][GQ], sm_l[GROUPS][GQ];
+    extern __shared__ float sm_acc[];   // [GROUPS][GQ][head_dim_padded]
+    const int dpad = VPL * LPK * N;
+    if (ln == 0) {
+#pragma unroll
+        for (int h = 0; h < GQ; ++h) { sm_m[grp][h] = m[h]; sm_l[grp][h] = l[h]; }
+    }
+#pragma unroll
+    for (int h = 0; h < GQ; ++h)
+#pragma unroll
+        for (int v = 0; v < VPL; ++v)
+#pragma unroll
+            for (int i = 0; i < N; ++i)
+                sm_acc[((long)grp * GQ + h) * dpad + (v * LPK + ln) * N + i] = acc[h][v][i];
+    __syncthreads();
+    for (int o = threadIdx.x; o < nq * head_dim; o += NTHREADS) {
+        const int h = o / head_dim, e = o - h * head_dim;
+        float mm = -INFINITY;
+        for (int gI = 0; gI < GROUPS; ++gI) mm = fmaxf(mm, sm_m[gI][h]);
+        float ll = 0.f, a = 0.f;
+        if (mm > -INFINITY) {
+            for (int gI = 0; gI < GROUPS; ++gI) {
+                const float w = fx_exp<T>(sm_m[gI][h] - mm);
+                ll += sm_l[gI][h] * w;
+                a += sm_acc[((long)gI * GQ + h) * dpad + e] * w;
+            }
+        }
+        const long slot = ((long)tkn * n_heads + (h0 + h)) * n_splits + split;
+        part_acc[slot * head_dim + e] = a;
+        if (e == 0) { part_ml[slot * 2] = mm; part_ml[slot * 2 + 1] = ll; }
+    }
+}
+
+template <typename T>
+__global__ void merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                             T* __restrict__ out, long ldo, int n_heads, int head_dim, int n_splits)
+{
+    const int tkn = blockIdx.x, h = blockIdx.y;
+    const long base = ((long)tkn * n_heads + h) * n_splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    for (int e = threadIdx.x; e < head_dim; e += blockDim.x) {
+        float ll = 0.f, a = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            if (ms == -INFINITY) continue;
+            const float w = fx_exp<T>(ms - mm);
+            ll += part_ml[(base + s) * 2 + 1] * w;
+            a += part_acc[(base + s) * head_dim + e] * w;
+        }
+        out[(long)tkn * ldo + (long)h * head_dim + e] = from_f32<T>(ll > 0.f ? a / ll : 0.f);
+    }
+}
+
+template <typename T, int LPK, int VPL, int GQ>
+int launch_one(dim3 grid, cudaStream_t s, const T* q, long ldq, const T* k, const T* v, const int* bt, int tw, int ps,
+               const int* pos, const int* tseq, const int* sslot, float* pa, float* pm, int nh, int nkv, int d,
+               int window, float scale, int split_len, int n_splits)
+{
+    auto kern = decode_split_kernel<T, LPK, VPL, GQ>;
+    const size_t smem = sizeof(float) * (NTHREADS / LPK) * GQ * (VPL * LPK * Vec<T>::N);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<grid, NTHREADS, smem, s>>>(q, ldq, k, v, bt, tw, ps, pos, tseq, sslot, pa, pm, nh, nkv, d, window, scale,
+                                      split_len, n_splits);
+    return fx_launch_status();
+}
+
+template <typename T, int LPK, int VPL, typename... A>
+int launch_split(int gq, A... args)
+{
+    switch (gq) {
+        case 1: return launch_one<T, LPK, VPL, 1>(args...);
+        case 2: return launch_one<T, LPK, VPL, 2>(args...);
+        case 4: return launch_one<T, LPK, VPL, 4>(args...);
+        default: return launch_one<T, LPK, VPL, 8>(args...);
+    }
+}
+
+template <typename T>
+int run(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table, int table_width,
+        int page_size, const int* positions, const int* token_seq, const int* seq_slot, void* out, long ldo,
+        float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
+        float scale, int split_len, int n_splits, cudaStream_t s)
+{
+    constexpr int N = Vec<T>::N;
+    if (head_dim % N || head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
+    if (ldq % N || (uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16) return FX_ERR_ALIGN;
+    const int group = n_heads / n_kv_heads;
+    int gq = 1;
+    while (gq < group && gq < MAXQ) gq <<= 1;
+    const int chunks = (group + gq - 1) / gq;
+    dim3 grid(n_kv_heads * chunks, n_tokens, n_splits);
+    if (grid.y > 65535u || grid.z > 65535u) return FX_ERR_SIZE;
+    const int vecs = head_dim / N;   // vectors per key
+    const T* Q = (const T*)q; const T* K = (const T*)k_pages; const T* V = (const T*)v_pages;
+    int rc;
+#define FX_GO(LPK, VPL)                                                                                       \
+    rc = launch_split<T, LPK, VPL>(gq, grid, s, Q, ldq, K, V, block_table, table_width, page_size, positions, \
+                                   token_seq, seq_slot, part_acc, part_ml, n_heads, n_kv_heads, head_dim,    \
+                                   window, scale, split_len, n_splits)
+    if (vecs <= 4) { FX_GO(4, 1); }
+    else if (vecs <= 8) { FX_GO(8, 1); }
+    else if (vecs <= 16) { FX_GO(16, 1); }
+    else if (vecs <= 32) { FX_GO(16, 2); }
+    else { FX_GO(16, 4); }
+#undef FX_GO
+    if (rc != FX_OK) return rc;
+    merge_kernel<T><<<dim3(n_tokens, n_heads), 64, 0, s>>>(part_acc, part_ml, (T*)out, ldo, n_heads, head_dim, n_splits);
+    return fx_launch_status();
+}
+
+}  // namespace
+
+// Scratch: part_acc [n_tokens, n_heads, n_splits, head_dim] and part_ml [n_tokens, n_heads, n_splits, 2], float32.
+extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
+                                   const int* block_table, int table_width, int page_size, const int* positions,
+                                   const int* token_seq, const int* seq_slot, void* out, long ldo, float* part_acc,
+                                   float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
+                                   float scale, int split_len, int n_splits, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (split_len <= 0 || n_splits <= 0) return FX_ERR_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FX_F32)
+        return run<float>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
+                          out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
+                          split_len, n_splits, s);
+    if (dtype == FX_BF16)
+        return run<bf16>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
+                         out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
+                         split_len, n_splits, s);
+    return FX_ERR_DTYPE;
+}

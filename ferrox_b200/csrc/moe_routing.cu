@@ -61,13 +61,18 @@ __global__ void count_kernel(const int* __restrict__ ids, int n, int n_experts, 
 }
 
 // offsets = exclusive prefix sum of counts ([E+1]); cursors reset to 0.
+// active[slot] lists the experts that got at least one row, then -1 up to n_slots.
 __global__ void scan_kernel(const int* __restrict__ counts, int n_experts, int* __restrict__ offsets,
-                            int* __restrict__ cursors)
+                            int* __restrict__ cursors, int* __restrict__ active, int n_slots)
 {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
-        int run = 0;
-        for (int e = 0; e < n_experts; ++e) { offsets[e] = run; run += counts[e]; cursors[e] = 0; }
+        int run = 0, n_active = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            offsets[e] = run; run += counts[e]; cursors[e] = 0;
+            if (active && counts[e] > 0 && n_active < n_slots) active[n_active++] = e;
+        }
         offsets[n_experts] = run;
+        if (active) for (int i = n_active; i < n_slots; ++i) active[i] = -1;
     }
 }
 
@@ -104,9 +109,10 @@ extern "C" int fx_router_topk(const float* logits, int n_tokens, int n_experts, 
 
 // scratch: 2 * n_experts ints (counts, cursors).  Outputs: offsets [E+1],
 // src_token [n_tokens * top_k] (row of the sorted order -> token it reads),
-// inv_perm [n_tokens * top_k] (pair -> its row in the sorted order).
+// inv_perm [n_tokens * top_k] (pair -> its row in the sorted order); optionally
+// active [n_slots]: the experts with rows, then -1 (n_slots >= min(n_experts, n_tokens * top_k)).
 extern "C" int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets,
-                            int* src_token, int* inv_perm, void* stream)
+                            int* src_token, int* inv_perm, int* active, int n_slots, void* stream)
 {
     const int n = n_tokens * top_k;
     if (n <= 0) return FX_OK;
@@ -116,7 +122,7 @@ extern "C" int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_exper
     int blocks = (int)fx_cdiv(n, 256);
     if (blocks > 148 * 4) blocks = 148 * 4;
     count_kernel<<<blocks, 256, 0, s>>>(ids, n, n_experts, scratch);
-    scan_kernel<<<1, 32, 0, s>>>(scratch, n_experts, offsets, scratch + n_experts);
+    scan_kernel<<<1, 32, 0, s>>>(scratch, n_experts, offsets, scratch + n_experts, active, n_slots);
     place_kernel<<<blocks, 256, 0, s>>>(ids, n, n_experts, top_k, offsets, scratch + n_experts, src_token, inv_perm);
     return fx_launch_status();
 }

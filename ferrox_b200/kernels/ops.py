@@ -41,7 +41,10 @@ _SIGNATURES = {
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "fx_router_topk": [_P, _I, _I, _I, _I, _P, _P, _P],
-    "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
+    "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P],
+    "fx_decode_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
+                            _I, _P],
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
     "fx_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "fx_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
@@ -50,7 +53,7 @@ _SIGNATURES = {
 _fn = {}
 
 # kernels launched by one call of an entry point (fx_moe_align: count, scan, place)
-_KERNELS = {"fx_moe_align": 3}
+_KERNELS = {"fx_moe_align": 3, "fx_decode_attention": 2}
 _launches = 0
 
 
@@ -186,10 +189,71 @@ def router_topk(logits, top_k, renorm, ids, weights, stream=None):
          stream if stream is not None else stream_ptr())
 
 
-def moe_align(ids, n_experts, scratch, offsets, src_token, inv_perm, stream=None):
+def moe_align(ids, n_experts, scratch, offsets, src_token, inv_perm, active=None, stream=None):
+    """``active`` (optional, int32 [n_slots]) receives the experts that got rows, then -1."""
     T, K = ids.shape
     call("fx_moe_align", _ptr(ids), T, K, n_experts, _ptr(scratch), _ptr(offsets), _ptr(src_token), _ptr(inv_perm),
+         _ptr(active), active.numel() if active is not None else 0, stream if stream is not None else stream_ptr())
+
+
+SKINNY_MAX_TOKENS = 64
+
+
+def skinny_ok(x, w) -> bool:
+    """Whether the decode-sized product kernel takes these operands."""
+    K = x.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 32 == 0 and x.stride(0) % 8 == 0
+            and w.stride(-2) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=None, group_offsets=None,
+                active_groups=None, tokens_hint=0, stream=None):
+    """out[rows, N] (+)= x . w^T for few rows: streams ``w`` once.  ``gated``: ``w`` is
+    [gate rows ; up rows] (2N rows) and out = silu(gate) * up.  Grouped: ``w`` is
+    [G, rows, K], ``group_offsets``/``active_groups`` come from :func:`moe_align`."""
+    rows, N = out.shape
+    K = x.shape[1]
+    if group_offsets is not None:
+        wrows, wstride, ldw = w.shape[1], w.stride(0), w.stride(1)
+        n_slots = active_groups.numel()
+    else:
+        wrows, wstride, ldw = w.shape[0], 0, w.stride(0)
+        n_slots = 1
+    if wrows != (2 * N if gated else N) or w.shape[-1] != K:
+        raise KernelError(f"gemm_skinny shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    call("fx_gemm_skinny", _ptr(x), _rows(x), _ptr(x_rows), _ptr(w), ldw, wstride, _ptr(bias),
+         code(bias) if bias is not None else 0, _ptr(out), code(out), _rows(out), int(accumulate), rows, N, K,
+         int(gated), N if gated else 0, _ptr(group_offsets), _ptr(active_groups), n_slots, int(tokens_hint),
          stream if stream is not None else stream_ptr())
+    return out
+
+
+def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int):
+    """(split_len, n_splits) for :func:`decode_attention`: enough blocks to fill the
+    GPU, as a function of the step's size and the context limit only."""
+    target = 148 * 4
+    want = max(1, -(-target // max(1, n_tokens * n_kv_blocks)))
+    split_len = max(64, -(-max_positions // want))
+    split_len = -(-split_len // 64) * 64
+    n_splits = max(1, -(-max_positions // split_len))
+    return split_len, n_splits
+
+
+def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,
+                     n_kv_heads, head_dim, window, scale, split_len, n_splits, part_acc, part_ml, stream=None):
+    T = q.shape[0]
+    call("fx_decode_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), code(q), _ptr(block_table),
+         block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out), _rows(out),
+         _ptr(part_acc), _ptr(part_ml), T, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), split_len,
+         n_splits, stream if stream is not None else stream_ptr())
+    return out
+
+
+def linear(x, w, out, *, bias=None, accumulate=False, stream=None):
+    """out (+)= x . w^T (+ bias): picks the kernel by size and element type."""
+    if x.shape[0] <= SKINNY_MAX_TOKENS and skinny_ok(x, w):
+        return gemm_skinny(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
+    return gemm(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
 
 
 def moe_combine(h, y, inv_perm, topk_w, shared=None, shared_gate_logit=None, stream=None):

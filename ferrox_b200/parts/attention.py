@@ -21,6 +21,9 @@ from ..weights.loader import TensorDecl
 from .base import Mixer, build_part, register_part
 
 
+DECODE_ATTENTION_MAX_TOKENS = 64
+
+
 def _common_dtype(tensors):
     return torch.float32 if any(t.dtype == torch.float32 for t in tensors) else tensors[0].dtype
 
@@ -76,7 +79,7 @@ class GqaAttention(Mixer):
         s = self.spec
         T = x.shape[0]
         qkv = self.rt.empty(T, self.q_size + 2 * self.kv_size)
-        ops.gemm(x, self.w_qkv, qkv, bias=self.b_qkv, stream=batch.stream)
+        ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, stream=batch.stream)
         inv_freq = self.position.inv_freq if self.position is not None else None
         rotary = self.position.rotary_dim if self.position is not None else 0
         ops.rope_kv_write(
@@ -85,11 +88,24 @@ class GqaAttention(Mixer):
             write_cache=cache.writes, status=batch.status, stream=batch.stream,
         )
         attn = self.rt.empty(T, self.q_size)
-        ops.paged_attention(
-            qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
-            batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
-        )
-        ops.gemm(attn, self.w_o, h, accumulate=True, stream=batch.stream)
+        if T <= DECODE_ATTENTION_MAX_TOKENS:
+            # few query tokens: split each request's keys over many blocks
+            group = s.n_heads // s.n_kv_heads
+            kv_blocks = s.n_kv_heads * -(-group // 8)
+            split_len, n_splits = ops.decode_split_plan(T, kv_blocks, cache.block_table.shape[1] * cache.page_size)
+            part_acc = self.rt.empty(T, s.n_heads, n_splits, s.head_dim, dtype=torch.float32)
+            part_ml = self.rt.empty(T, s.n_heads, n_splits, 2, dtype=torch.float32)
+            ops.decode_attention(
+                qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
+                batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, split_len, n_splits,
+                part_acc, part_ml, stream=batch.stream,
+            )
+        else:
+            ops.paged_attention(
+                qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
+                batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
+            )
+        ops.linear(attn, self.w_o, h, accumulate=True, stream=batch.stream)
 
 
 register_part("gqa_attention", GqaAttention, replace=True)

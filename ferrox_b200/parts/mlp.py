@@ -32,11 +32,14 @@ class SwigluMlp(FeedForward):
 
     def forward_add(self, x, h, batch):
         T, I = x.shape[0], self.spec.intermediate
-        gu = self.rt.empty(T, 2 * I)
-        ops.gemm(x, self.w_gu, gu, stream=batch.stream)
         act = self.rt.empty(T, I)
-        ops.silu_mul(gu, act, stream=batch.stream)
-        ops.gemm(act, self.w_down, h, accumulate=True, stream=batch.stream)
+        if T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu):
+            ops.gemm_skinny(x, self.w_gu, act, gated=True, stream=batch.stream)  # silu(gate) * up in the epilogue
+        else:
+            gu = self.rt.empty(T, 2 * I)
+            ops.gemm(x, self.w_gu, gu, stream=batch.stream)
+            ops.silu_mul(gu, act, stream=batch.stream)
+        ops.linear(act, self.w_down, h, accumulate=True, stream=batch.stream)
 
 
 register_part("swiglu_mlp", SwigluMlp, replace=True)

@@ -70,35 +70,46 @@ class SoftmaxTopkMoe(FeedForward):
         s, rt, st = self.spec, self.rt, batch.stream
         T, E, K, I, H = x.shape[0], s.n_experts, s.top_k, s.expert_intermediate, s.hidden
         i32 = torch.int32
+        small = T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
         logits = rt.empty(T, E, dtype=torch.float32)
-        ops.gemm(x, self.w_router, logits, stream=st)
+        ops.linear(x, self.w_router, logits, stream=st)
         ids = rt.empty(T, K, dtype=i32)
         weights = rt.empty(T, K, dtype=torch.float32)
         ops.router_topk(logits, K, s.norm_topk_prob, ids, weights, stream=st)
         offsets = rt.empty(E + 1, dtype=i32)
         src_token = rt.empty(T * K, dtype=i32)
         inv_perm = rt.empty(T * K, dtype=i32)
-        ops.moe_align(ids, E, self._scratch, offsets, src_token, inv_perm, stream=st)
+        active = rt.empty(min(E, T * K), dtype=i32) if small else None
+        ops.moe_align(ids, E, self._scratch, offsets, src_token, inv_perm, active, stream=st)
 
-        gu = rt.empty(T * K, 2 * I)
-        ops.gemm(x, self.w_gu, gu, a_rows=src_token, group_offsets=offsets, stream=st)
         act = rt.empty(T * K, I)
-        ops.silu_mul(gu, act, stream=st)
         y = rt.empty(T * K, H)
-        ops.gemm(act, self.w_down, y, group_offsets=offsets, stream=st)
+        if small:
+            # few tokens: every expert that was chosen is streamed once, gate/up fused with SiLU
+            ops.gemm_skinny(x, self.w_gu, act, gated=True, x_rows=src_token, group_offsets=offsets,
+                            active_groups=active, tokens_hint=T, stream=st)
+            ops.gemm_skinny(act, self.w_down, y, group_offsets=offsets, active_groups=active, tokens_hint=T, stream=st)
+        else:
+            gu = rt.empty(T * K, 2 * I)
+            ops.gemm(x, self.w_gu, gu, a_rows=src_token, group_offsets=offsets, stream=st)
+            ops.silu_mul(gu, act, stream=st)
+            ops.gemm(act, self.w_down, y, group_offsets=offsets, stream=st)
 
         shared = gate_logit = None
         if self.w_shared_gu is not None:
             Is = s.shared_intermediate
-            sgu = rt.empty(T, 2 * Is)
-            ops.gemm(x, self.w_shared_gu, sgu, stream=st)
             sact = rt.empty(T, Is)
-            ops.silu_mul(sgu, sact, stream=st)
+            if T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_shared_gu):
+                ops.gemm_skinny(x, self.w_shared_gu, sact, gated=True, stream=st)
+            else:
+                sgu = rt.empty(T, 2 * Is)
+                ops.gemm(x, self.w_shared_gu, sgu, stream=st)
+                ops.silu_mul(sgu, sact, stream=st)
             shared = rt.empty(T, H)
-            ops.gemm(sact, self.w_shared_down, shared, stream=st)
+            ops.linear(sact, self.w_shared_down, shared, stream=st)
             if self.w_shared_gate is not None:
                 gate_logit = rt.empty(T, 1, dtype=torch.float32)
-                ops.gemm(x, self.w_shared_gate, gate_logit, stream=st)
+                ops.linear(x, self.w_shared_gate, gate_logit, stream=st)
         ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st)
 
 

@@ -1,0 +1,386 @@
+"""Each kernel alone against a plain 32-bit torch statement of the same operation,
+at sizes other than the engine's (odd widths, head sizes in steps of 16, page
+edges, windows)."""
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# error relative to the largest |expected| value
+TOL = {"float32": 3e-6, "bfloat16": 1.2e-2}
+
+
+def ops():
+    from ferrox_b200.kernels import ops as o
+
+    return o
+
+
+def rel(got, want):
+    return float((got.float() - want.float()).abs().max() / want.float().abs().max().clamp_min(1e-30))
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=None):
+    g = torch.Generator().manual_seed(seed if seed is not None else sum(shape) + len(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ------------------------------------------------------------------ matrix products
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 77), (70, 65, 64), (129, 33, 250), (64, 64, 16)])
+def test_gemm_generic(dtype, M, N, K):
+    o, dt = ops(), DT[dtype]
+    a, w, bias = rnd(M, K, dtype=dt), rnd(N, K, dtype=dt), rnd(N, dtype=torch.float32)
+    want = a.float() @ w.float().T + bias
+    out = torch.empty(M, N, dtype=dt, device=DEV)
+    o.gemm(a, w, out, bias=bias)
+    assert rel(out, want) < TOL[dtype]
+    acc = rnd(M, N, dtype=torch.float32, seed=5)
+    base = acc.clone()
+    o.gemm(a, w, acc, accumulate=True)  # 32-bit output, added to what is there
+    assert rel(acc, base + a.float() @ w.float().T) < (3e-6 if dtype == "float32" else 1e-5)
+
+
+def test_gemm_mixed_precision_weights_stay_32_bit():
+    o = ops()
+    a, w = rnd(5, 96, dtype=torch.bfloat16), rnd(40, 96, dtype=torch.float32)
+    out = torch.empty(5, 40, dtype=torch.float32, device=DEV)
+    o.gemm(a, w, out)
+    assert rel(out, a.float() @ w.T) < 3e-6  # no rounding of the 32-bit weights
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_gemm_grouped_with_gather(dtype):
+    o, dt = ops(), DT[dtype]
+    G, N, K, T = 5, 37, 48, 23
+    x, w = rnd(T, K, dtype=dt), rnd(G, N, K, dtype=dt)
+    counts = [0, 9, 1, 0, 13]
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    rows = torch.randint(0, T, (sum(counts),), generator=torch.Generator().manual_seed(1)).to(torch.int32).to(DEV)
+    out = torch.zeros(sum(counts), N, dtype=dt, device=DEV)
+    o.gemm(x, w, out, a_rows=rows, group_offsets=offsets)
+    r = 0
+    for g, c in enumerate(counts):
+        for _ in range(c):
+            want = x[rows[r]].float() @ w[g].float().T
+            assert rel(out[r], want) < TOL[dtype]
+            r += 1
+
+
+@pytest.mark.parametrize("T", [1, 3, 8, 9, 17, 40, 64])
+@pytest.mark.parametrize("N,K", [(16, 32), (60, 64), (1, 96), (200, 2048), (33, 160)])
+def test_gemm_skinny(T, N, K):
+    o = ops()
+    x, w, bias = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1), rnd(N)
+    want = x.float() @ w.float().T + bias
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    o.gemm_skinny(x, w, out, bias=bias)
+    assert rel(out, want) < TOL["bfloat16"]
+    acc = rnd(T, N, seed=3)
+    base = acc.clone()
+    o.gemm_skinny(x, w, acc, accumulate=True)
+    assert rel(acc, base + x.float() @ w.float().T) < 2e-5
+    # gated: silu(gate) * up in the epilogue
+    if N > 1:
+        wg = rnd(2 * N, K, dtype=torch.bfloat16, scale=0.1, seed=9)
+        gate, up = x.float() @ wg[:N].float().T, x.float() @ wg[N:].float().T
+        got = torch.empty(T, N, dtype=torch.float32, device=DEV)
+        o.gemm_skinny(x, wg, got, gated=True)
+        assert rel(got, gate / (1 + torch.exp(-gate)) * up) < 2e-5
+
+
+@pytest.mark.parametrize("T,K_top", [(1, 2), (8, 4), (33, 3)])
+def test_gemm_skinny_grouped_against_routing(T, K_top):
+    o = ops()
+    E, I, H = 7, 64, 96
+    x = rnd(T, H, dtype=torch.bfloat16)
+    w_gu, w_down = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.1), rnd(E, H, I, dtype=torch.bfloat16, scale=0.1)
+    g = torch.Generator().manual_seed(T)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K_top] for _ in range(T)]).to(torch.int32).to(DEV)
+    scratch = torch.zeros(2 * E, dtype=torch.int32, device=DEV)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    src = torch.empty(T * K_top, dtype=torch.int32, device=DEV)
+    inv = torch.empty(T * K_top, dtype=torch.int32, device=DEV)
+    active = torch.empty(min(E, T * K_top), dtype=torch.int32, device=DEV)
+    o.moe_align(ids, E, scratch, offsets, src, inv, active)
+    # bookkeeping: a permutation, rows grouped by expert, active = experts with rows
+    counts = torch.bincount(ids.flatten().long(), minlength=E)
+    assert offsets.tolist() == [0] + counts.cumsum(0).tolist()
+    assert sorted(inv.tolist()) == list(range(T * K_top))
+    for i in range(T * K_top):
+        r = int(inv[i])
+        e = int(ids.flatten()[i])
+        assert int(offsets[e]) <= r < int(offsets[e + 1]) and int(src[r]) == i // K_top
+    act_list = [e for e in active.tolist() if e >= 0]
+    assert act_list == [e for e in range(E) if counts[e] > 0] and all(e == -1 for e in active.tolist()[len(act_list):])
+    act = torch.empty(T * K_top, I, dtype=torch.bfloat16, device=DEV)
+    o.gemm_skinny(x, w_gu, act, gated=True, x_rows=src, group_offsets=offsets, active_groups=active, tokens_hint=T)
+    y = torch.empty(T * K_top, H, dtype=torch.float32, device=DEV)
+    o.gemm_skinny(act, w_down, y, group_offsets=offsets, active_groups=active, tokens_hint=T)
+    for i in range(T * K_top):
+        t, e, r = i // K_top, int(ids.flatten()[i]), int(inv[i])
+        gu = x[t].float() @ w_gu[e].float().T
+        a = (gu[:I] / (1 + torch.exp(-gu[:I])) * gu[I:])
+        assert rel(act[r], a) < TOL["bfloat16"]
+        assert rel(y[r], act[r].float() @ w_down[e].float().T) < 2e-5
+
+
+def test_skinny_refuses_what_it_cannot_do():
+    o = ops()
+    x, w = rnd(2, 40, dtype=torch.bfloat16), rnd(16, 40, dtype=torch.bfloat16)
+    assert not o.skinny_ok(x, w)
+    with pytest.raises(o.KernelError, match="size"):
+        o.gemm_skinny(x, w, torch.empty(2, 16, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(o.KernelError, match="CUDA tensors"):
+        o.gemm(x.cpu(), w, torch.empty(2, 16, dtype=torch.bfloat16, device=DEV))
+
+
+# ------------------------------------------------------------------ element-wise
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H", [16, 80, 333, 2048])
+def test_rmsnorm_embed_silu(dtype, H):
+    o, dt = ops(), DT[dtype]
+    x, w = rnd(9, H, scale=3.0), rnd(H, dtype=dt) + 1
+    eps = 1e-5
+    want = x * (1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)) * w.float()
+    out = torch.empty(9, H, dtype=dt, device=DEV)
+    o.rmsnorm(x, w, eps, out)
+    assert rel(out, want) < (1e-6 if dtype == "float32" else 5e-3)
+    rows = torch.tensor([7, 0, 7, 3], dtype=torch.int32, device=DEV)
+    picked = torch.empty(4, H, dtype=dt, device=DEV)
+    o.rmsnorm(x, w, eps, picked, rows=rows)
+    assert torch.equal(picked, out[rows.long()])
+    table = rnd(50, H, dtype=dt)
+    ids = torch.tensor([3, 49, 0, 3], dtype=torch.int32, device=DEV)
+    h = torch.empty(4, H, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.embed(table, ids, h, status)
+    assert torch.equal(h, table[ids.long()].float()) and int(status) == 0
+    o.embed(table, torch.tensor([50], dtype=torch.int32, device=DEV), h[:1], status)
+    assert int(status) == 1  # a token id outside the table is reported, not read
+    gu = rnd(5, 2 * H, dtype=dt)
+    act = torch.empty(5, H, dtype=dt, device=DEV)
+    o.silu_mul(gu, act)
+    g, u = gu[:, :H].float(), gu[:, H:].float()
+    assert rel(act, g / (1 + torch.exp(-g)) * u) < (1e-6 if dtype == "float32" else 5e-3)
+
+
+def test_router_topk_and_ties():
+    o = ops()
+    logits = torch.arange(1.0, 9.0, device=DEV).reshape(1, 8)
+    ids = torch.empty(1, 3, dtype=torch.int32, device=DEV)
+    w = torch.empty(1, 3, dtype=torch.float32, device=DEV)
+    o.router_topk(logits, 3, False, ids, w)
+    assert ids.tolist() == [[7, 6, 5]]
+    # the reference's golden for these logits (crates/ferrox-moe/src/lib.rs:864-893), its tolerance
+    assert torch.allclose(w.cpu(), torch.tensor([[0.6323223, 0.2326232, 0.0855683]]), atol=1e-4)
+    o.router_topk(logits, 3, True, ids, w)
+    assert abs(float(w.sum()) - 1) < 1e-6
+    tie = torch.tensor([[0.5, 2.0, 2.0, 0.1, 2.0]], device=DEV)
+    ids2 = torch.empty(1, 2, dtype=torch.int32, device=DEV)
+    o.router_topk(tie, 2, False, ids2, torch.empty(1, 2, device=DEV))
+    assert ids2.tolist() == [[1, 2]]  # equal probabilities: the lowest index first
+    g = torch.Generator().manual_seed(0)
+    big = torch.randn(300, 61, generator=g).to(DEV)
+    ids3 = torch.empty(300, 5, dtype=torch.int32, device=DEV)
+    w3 = torch.empty(300, 5, device=DEV)
+    o.router_topk(big, 5, False, ids3, w3)
+    p = torch.softmax(big, -1)
+    tv, ti = torch.topk(p, 5, dim=-1)
+    assert torch.equal(ids3.long(), ti) and rel(w3, tv) < 1e-6
+
+
+def test_moe_combine_in_rank_order():
+    o = ops()
+    T, K, H = 6, 3, 40
+    y, shared = rnd(T * K, H), rnd(T, H)
+    inv = torch.randperm(T * K, generator=torch.Generator().manual_seed(0)).to(torch.int32).to(DEV)
+    w = torch.rand(T, K, generator=torch.Generator().manual_seed(1)).to(DEV)
+    gate = rnd(T, 1)
+    h = rnd(T, H, seed=2)
+    want = h.clone()
+    for t in range(T):
+        acc = torch.zeros(H, device=DEV)
+        for k in range(K):
+            acc = acc + w[t, k] * y[inv[t * K + k]]
+        want[t] += acc + torch.sigmoid(gate[t]) * shared[t]
+    o.moe_combine(h, y, inv, w, shared, gate)
+    assert rel(h, want) < 1e-6
+
+
+# ------------------------------------------------------------------ rotary + cache write + attention
+def build_cache(dtype, seqs, nkv, d, page_size, n_pages, seed=0):
+    """Random K/V for requests of the given lengths, scattered into shuffled pages."""
+    rng = random.Random(seed)
+    free = list(range(n_pages))
+    rng.shuffle(free)
+    width = max(-(-L // page_size) for L in seqs) + 1
+    table = torch.full((len(seqs) + 2, width), -1, dtype=torch.int32)
+    kp = torch.zeros(n_pages, nkv, page_size, d)
+    vp = torch.zeros(n_pages, nkv, page_size, d)
+    ks, vs = [], []
+    for s, L in enumerate(seqs):
+        k = torch.randn(L, nkv, d, generator=torch.Generator().manual_seed(seed * 100 + s)).to(dtype).float()
+        v = torch.randn(L, nkv, d, generator=torch.Generator().manual_seed(seed * 100 + 50 + s)).to(dtype).float()
+        ks.append(k)
+        vs.append(v)
+        for j in range(-(-L // page_size)):
+            pg = free.pop()
+            table[s + 1, j] = pg  # slot = s + 1: slots and entries are different things
+            n = min(page_size, L - j * page_size)
+            kp[pg, :, :n] = k[j * page_size:j * page_size + n].transpose(0, 1)
+            vp[pg, :, :n] = v[j * page_size:j * page_size + n].transpose(0, 1)
+    return kp.to(dtype).to(DEV), vp.to(dtype).to(DEV), table.to(DEV), ks, vs
+
+
+def plain_attention(q, k, v, pos, window, scale):
+    """One query (heads, d) at position pos over keys k[:pos+1] (nkv heads)."""
+    nh, nkv = q.shape[0], k.shape[1]
+    lo = max(0, pos - window + 1) if window else 0
+    out = torch.zeros_like(q)
+    for h in range(nh):
+        kv = h // (nh // nkv)
+        s = (k[lo:pos + 1, kv] @ q[h]) * scale
+        out[h] = torch.softmax(s, 0) @ v[lo:pos + 1, kv]
+    return out
+
+
+ATT_CASES = [
+    # nh, nkv, d, page, window, lengths
+    (4, 2, 16, 4, 0, [1, 5, 33]),
+    (2, 1, 64, 16, 16, [70, 16, 17]),
+    (6, 3, 48, 8, 7, [40, 9]),
+    (16, 16, 128, 64, 0, [300, 64, 65]),
+    (28, 4, 128, 64, 100, [130]),
+    (3, 3, 256, 16, 0, [50]),
+    (12, 1, 32, 16, 0, [90]),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ATT_CASES)
+@pytest.mark.parametrize("kernel", ["generic", "decode"])
+def test_attention_over_pages(dtype, case, kernel):
+    o, dt = ops(), DT[dtype]
+    nh, nkv, d, ps, window, lens = case
+    kp, vp, table, ks, vs = build_cache(dt, lens, nkv, d, ps, n_pages=sum(-(-L // ps) for L in lens) + 3)
+    # queries: for each request its last position, one in the middle and position 0
+    toks = []
+    for s, L in enumerate(lens):
+        for pos in sorted({L - 1, L // 2, 0}):
+            toks.append((s, pos))
+    T = len(toks)
+    q = rnd(T, nh * d + 8, dtype=dt)[:, : nh * d + 8]  # rows wider than the heads: a strided view
+    positions = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor([s + 1 for s in range(len(lens))], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, nh * d, dtype=dt, device=DEV)
+    scale = 1 / math.sqrt(d)
+    if kernel == "generic":
+        o.paged_attention(q, kp, vp, table, ps, positions, token_seq, seq_slot, out, nh, nkv, d, window, scale)
+    else:
+        for split_len, n_splits in ((64, 5), (128, 3), (4096, 1)):
+            pa = torch.empty(T, nh, n_splits, d, device=DEV)
+            pm = torch.empty(T, nh, n_splits, 2, device=DEV)
+            out.zero_()
+            o.decode_attention(q, kp, vp, table, ps, positions, token_seq, seq_slot, out, nh, nkv, d, window, scale,
+                               split_len, n_splits, pa, pm)
+            _check_attention(out, q, ks, vs, toks, nh, d, window, scale, dtype)
+        return
+    _check_attention(out, q, ks, vs, toks, nh, d, window, scale, dtype)
+
+
+def _check_attention(out, q, ks, vs, toks, nh, d, window, scale, dtype):
+    for i, (s, pos) in enumerate(toks):
+        want = plain_attention(q[i, : nh * d].float().cpu().reshape(nh, d), ks[s], vs[s], pos, window, scale)
+        got = out[i].float().cpu().reshape(nh, d)
+        assert rel(got, want) < (2e-6 if dtype == "float32" else 1e-2), (s, pos)
+
+
+@pytest.mark.parametrize("kernel", ["generic", "decode"])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(kernel):
+    """One key among hundreds is made to stand out; the output must be its value when
+    it is visible and must not contain it one position past the window."""
+    o = ops()
+    nh = nkv = 2
+    d, ps, L = 32, 16, 400
+    kp, vp, table, ks, vs = build_cache(torch.float32, [L], nkv, d, ps, n_pages=30, seed=4)
+    far = 37
+    q = torch.zeros(1, nh * d)
+    spike = torch.randn(d, generator=torch.Generator().manual_seed(1))
+    spike = spike / spike.norm() * 12
+    q[0, :d], q[0, d:] = spike, spike
+    page, off = int(table[1, far // ps]), far % ps
+    kp[page, :, off, :] = (spike * 8).to(DEV)  # score far above every other key
+    ks[0][far, :, :] = spike * 8
+    q = q.to(DEV)
+    args = dict(n_heads=nh, n_kv_heads=nkv, head_dim=d, scale=1 / math.sqrt(d))
+    positions = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    slot = torch.ones(1, dtype=torch.int32, device=DEV)
+
+    def run(window):
+        out = torch.empty(1, nh * d, device=DEV)
+        if kernel == "generic":
+            o.paged_attention(q, kp, vp, table, ps, positions, z, slot, out, window=window, **args)
+        else:
+            pa, pm = torch.empty(1, nh, 7, d, device=DEV), torch.empty(1, nh, 7, 2, device=DEV)
+            o.decode_attention(q, kp, vp, table, ps, positions, z, slot, out, window=window, split_len=64, n_splits=7,
+                               part_acc=pa, part_ml=pm, **args)
+        return out.cpu().reshape(nh, d)
+
+    full = run(0)
+    assert rel(full[0], vs[0][far, 0]) < 1e-4  # all the weight on the far key
+    inside = run(L - far)  # window reaches back exactly to the far key
+    assert rel(inside[0], vs[0][far, 0]) < 1e-4
+    outside = run(L - far - 1)  # one less: the far key is out
+    want = plain_attention(q[0].cpu().reshape(nh, d), ks[0], vs[0], L - 1, L - far - 1, args["scale"])
+    assert rel(outside, want) < 1e-5 and rel(outside[0], vs[0][far, 0]) > 0.1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,d,rot", [(4, 2, 16, 16), (3, 1, 48, 48), (2, 2, 128, 64)])
+def test_rope_and_cache_write(dtype, nh, nkv, d, rot):
+    o, dt = ops(), DT[dtype]
+    ps, T = 4, 7
+    theta = 10000.0
+    width = nh * d + 2 * nkv * d
+    qkv = rnd(T, width, dtype=dt)
+    before = qkv.clone()
+    positions = torch.tensor([0, 1, 2, 3, 9, 10, 150], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([0, 0, 0, 0, 1, 1, 2], dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+    table = torch.full((3, 40), -1, dtype=torch.int32)
+    table[2, 0], table[0, 2], table[1, 37] = 5, 1, 3
+    table = table.to(DEV)
+    kp = torch.zeros(6, nkv, ps, d, dtype=dt, device=DEV)
+    vp = torch.zeros_like(kp)
+    inv_freq = (1.0 / torch.pow(torch.tensor(theta), torch.arange(0, rot // 2).float() * 2 / rot)).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.rope_kv_write(qkv, positions, token_seq, seq_slot, inv_freq, rot, kp, vp, table, ps, nh, nkv, d, True, status)
+    assert int(status) == 0
+    x = before.float().cpu()
+    ang = positions.cpu().float()[:, None] * inv_freq.cpu()[None, :]
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    tol = 2e-6 if dtype == "float32" else 8e-3
+    for t in range(T):
+        for hh in range(nh + nkv):
+            a, b = x[t, hh * d: hh * d + rot // 2], x[t, hh * d + rot // 2: hh * d + rot]
+            want = torch.cat([a * cos[t] - b * sin[t], a * sin[t] + b * cos[t], x[t, hh * d + rot:(hh + 1) * d]])
+            assert rel(qkv[t, hh * d:(hh + 1) * d].cpu(), want) < tol
+        assert torch.equal(qkv[t, (nh + nkv) * d:], before[t, (nh + nkv) * d:])  # v untouched
+    # where the rows landed: page table[slot][pos // ps], offset pos % ps
+    where = {0: (5, 0), 1: (5, 1), 2: (5, 2), 3: (5, 3), 4: (1, 1), 5: (1, 2), 6: (3, 2)}
+    for t, (pg, off) in where.items():
+        assert torch.equal(kp[pg, :, off, :].reshape(-1), qkv[t, nh * d:(nh + nkv) * d])
+        assert torch.equal(vp[pg, :, off, :].reshape(-1), qkv[t, (nh + nkv) * d:])
+    assert int((kp != 0).any(dim=-1).sum()) == T * nkv  # nothing else was written
+    # a position without a page is reported, not written
+    o.rope_kv_write(qkv[:1], torch.tensor([20], dtype=torch.int32, device=DEV), token_seq[:1], seq_slot, inv_freq, rot,
+                    kp, vp, table, ps, nh, nkv, d, True, status)
+    assert int(status) == 2
