@@ -22,7 +22,7 @@ from ..parts.build import build_model
 from ..weights import loader as wl
 from ..weights.random_init import random_tensors
 from .batch import StepEntry
-from .step import step as _step
+from .step import GraphedDecode, step as _step
 
 DTYPES = {
     "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -43,7 +43,7 @@ def _dtype(d) -> torch.dtype:
 
 class Engine:
     def __init__(self, config, spec, model, *, page_size=64, n_pages=None, max_tokens=None, max_slots=64,
-                 max_positions=None):
+                 max_positions=None, cuda_graphs=True):
         """Use :meth:`from_folder` or :meth:`from_random`.  The cache pool holds
         ``n_pages`` pages per group, or enough for ``max_tokens`` positions."""
         self.config = config
@@ -60,6 +60,8 @@ class Engine:
             model.cache_specs(), page_size=page_size, n_pages=n_pages, max_slots=max_slots,
             max_positions=max_positions, device=self.rt.device, dtype=self.rt.dtype,
         )
+        # decode steps replay CUDA graphs when every part of the model can be captured
+        self.graphs = GraphedDecode(model, self.cache) if cuda_graphs and model.graph_safe() else None
 
     # ---- construction ---------------------------------------------------------
     @classmethod
@@ -105,7 +107,7 @@ class Engine:
 
     def step(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
         """Run the entries' tokens as one batch; [wanted, vocab] float32 logits."""
-        return _step(self.model, self.cache, entries, check=check)
+        return _step(self.model, self.cache, entries, check=check, graphs=self.graphs)
 
     # ---- generation -------------------------------------------------------------
     def generate(self, prompts, max_new_tokens=128, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0,

@@ -62,6 +62,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launches(n: int) -> None:
+    """Account for kernels launched outside :func:`call` (a CUDA graph's replay)."""
+    global _launches
+    _launches += n
+
+
 def _get(name: str):
     f = _fn.get(name)
     if f is None:

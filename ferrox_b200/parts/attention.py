@@ -29,6 +29,7 @@ def _common_dtype(tensors):
 
 
 class GqaAttention(Mixer):
+    graph_safe = True
     def __init__(self, spec):
         super().__init__(spec)
         s = spec

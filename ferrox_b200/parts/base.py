@@ -37,6 +37,11 @@ class Runtime:
 
 
 class Part:
+    # True when ``forward`` only enqueues kernels on the batch's stream at fixed
+    # addresses (no host reads of device data, no Python state that changes per
+    # step), so that a decode step can be captured in a CUDA graph.
+    graph_safe = False
+
     def __init__(self, spec):
         self.spec = spec
         self.rt: Runtime | None = None

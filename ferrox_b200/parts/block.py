@@ -29,6 +29,10 @@ class PreNormBlock(Block):
         for part in (self.norm1, self.mixer, self.norm2, self.ffn):
             part.load(src, rt)
 
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.ffn))
+
     def forward(self, h, batch, cache):
         self.mixer.forward_add(self.norm1.forward(h), h, batch, cache)
         self.ffn.forward_add(self.norm2.forward(h), h, batch)

@@ -16,6 +16,7 @@ def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 class SwigluMlp(FeedForward):
+    graph_safe = True
     def tensor_decls(self):
         s, p = self.spec, self.spec.prefix
         return [

@@ -61,6 +61,9 @@ class DecoderModel(Part):
         self.final_norm.load(src, rt)
         self.head = self.embedding if s.head_name is None else src.get(s.head_name)
 
+    def graph_safe(self) -> bool:
+        return all(l.graph_safe for l in self.layers) and self.final_norm.graph_safe
+
     def weight_bytes(self) -> int:
         seen, total = set(), 0
 

@@ -23,6 +23,7 @@ from .mlp import pack_gate_up
 
 
 class SoftmaxTopkMoe(FeedForward):
+    graph_safe = True
     def tensor_decls(self):
         s, p = self.spec, self.spec.prefix
         d = [TensorDecl(p + "gate.weight", (s.n_experts, s.hidden))]

@@ -8,6 +8,7 @@ from .base import Norm, register_part
 
 
 class RmsNorm(Norm):
+    graph_safe = True
     def tensor_decls(self):
         return [TensorDecl(self.spec.prefix + "weight", (self.spec.size,), init="ones")]
 

@@ -14,6 +14,7 @@ from .base import Part, register_part
 
 
 class RopeNeox(Part):
+    graph_safe = True
     def load(self, src, rt):
         super().load(src, rt)
         r = self.spec.rotary_dim
@@ -25,6 +26,7 @@ class RopeNeox(Part):
 
 
 class NoPosition(Part):
+    graph_safe = True
     """No position encoding: keys and queries are stored as projected."""
 
     def load(self, src, rt):
