@@ -18,7 +18,7 @@ int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, floa
 int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev, int rows, int n,
                 void* stream);
 int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const int* token_seq, const int* seq_slot,
-                     const float* inv_freq, int rotary_dim, void* k_pages, void* v_pages, const int* block_table,
+                     const float* inv_freq, const float* cos_sin, int rotary_dim, void* k_pages, void* v_pages, const int* block_table,
                      int table_width, int page_size, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                      int write_cache, int* status, void* stream);
 int fx_moe_combine(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w, int top_k,
@@ -35,6 +35,9 @@ int fx_router_topk(const float* logits, int n_tokens, int n_experts, int top_k, 
 int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets, int* src_token,
                  int* inv_perm, int* active, int n_slots, void* stream);
 
+int fx_route_small(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
+                   int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
+int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin, void* stream);
 int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, long ldw, long w_group_stride,
                    const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int n_tokens,
                    int N, int K, int gated, int gate_up_offset, const int* group_offsets, const int* active_groups,

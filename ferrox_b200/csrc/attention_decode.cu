@@ -96,51 +96,60 @@ __global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
         const long head_stride = (long)page_size * head_dim;
         // the loop bounds are the same for every thread, so the group-wide shuffles
         // below are always executed by whole warps
-        for (int kb = k_begin; kb < k_end; kb += GROUPS) {
-            const int key = kb + grp;
-            bool valid = key < k_end;
-            const int page = valid ? table[key / page_size] : -1;
-            valid = valid && page >= 0;  // a position without a page is skipped, never dereferenced
-            const long base = valid ? ((long)page * n_kv_heads + kvh) * head_stride + (long)(key % page_size) * head_dim : 0;
-            float kv[VPL][N];
-            float s[GQ];
+        // U keys per group and pass: their loads are issued together, so that several
+        // are in flight per lane; the running (m, l, acc) then takes them in key order
+        constexpr int U = (GQ * VPL <= 2) ? 4 : 2;
+        for (int kb = k_begin; kb < k_end; kb += GROUPS * U) {
+            bool valid[U];
+            long base[U];
+            float kk[U][VPL][N], vv[U][VPL][N];
 #pragma unroll
-            for (int h = 0; h < GQ; ++h) s[h] = 0.f;
+            for (int u = 0; u < U; ++u) {
+                const int key = kb + u * GROUPS + grp;
+                valid[u] = key < k_end;
+                const int page = valid[u] ? table[key / page_size] : -1;
+                valid[u] = valid[u] && page >= 0;  // a position without a page is skipped, never dereferenced
+                base[u] = valid[u] ? ((long)page * n_kv_heads + kvh) * head_stride + (long)(key % page_size) * head_dim : 0;
+            }
 #pragma unroll
-            for (int v = 0; v < VPL; ++v) {
-                const int e = (v * LPK + ln) * N;
-                if (valid && e < head_dim) {
-                    Vec<T>::load(k_pages + base + e, kv[v]);
+            for (int u = 0; u < U; ++u)
 #pragma unroll
-                    for (int h = 0; h < GQ; ++h)
+                for (int v = 0; v < VPL; ++v) {
+                    const int e = (v * LPK + ln) * N;
 #pragma unroll
-                        for (int i = 0; i < N; ++i) s[h] = fmaf(qr[h][v][i], kv[v][i], s[h]);
+                    for (int i = 0; i < N; ++i) { kk[u][v][i] = 0.f; vv[u][v][i] = 0.f; }
+                    if (valid[u] && e < head_dim) {
+                        Vec<T>::load(k_pages + base[u] + e, kk[u][v]);
+                        Vec<T>::load(v_pages + base[u] + e, vv[u][v]);
+                    }
                 }
-            }
 #pragma unroll
-            for (int h = 0; h < GQ; ++h)
+            for (int u = 0; u < U; ++u) {
+                float s[GQ];
 #pragma unroll
-                for (int o = LPK / 2; o > 0; o >>= 1) s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);
-            if (!valid) continue;
+                for (int h = 0; h < GQ; ++h) {
+                    s[h] = 0.f;
 #pragma unroll
-            for (int v = 0; v < VPL; ++v) {
-                const int e = (v * LPK + ln) * N;
+                    for (int v = 0; v < VPL; ++v)
 #pragma unroll
-                for (int i = 0; i < N; ++i) kv[v][i] = 0.f;
-                if (e < head_dim) Vec<T>::load(v_pages + base + e, kv[v]);
-            }
+                        for (int i = 0; i < N; ++i) s[h] = fmaf(qr[h][v][i], kk[u][v][i], s[h]);
 #pragma unroll
-            for (int h = 0; h < GQ; ++h) {
-                const float sc = s[h] * scale;
-                const float m_new = fmaxf(m[h], sc);
-                const float alpha = fx_exp<T>(m[h] - m_new);   // m = -inf at first: exp(-inf) = 0
-                const float p = fx_exp<T>(sc - m_new);
-                l[h] = l[h] * alpha + p;
+                    for (int o = LPK / 2; o > 0; o >>= 1) s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);
+                }
+                if (!valid[u]) continue;
 #pragma unroll
-                for (int v = 0; v < VPL; ++v)
+                for (int h = 0; h < GQ; ++h) {
+                    const float sc = s[h] * scale;
+                    const float m_new = fmaxf(m[h], sc);
+                    const float alpha = fx_exp<T>(m[h] - m_new);   // m = -inf at first: exp(-inf) = 0
+                    const float p = fx_exp<T>(sc - m_new);
+                    l[h] = l[h] * alpha + p;
 #pragma unroll
-                    for (int i = 0; i < N; ++i) acc[h][v][i] = acc[h][v][i] * alpha + p * kv[v][i];
-                m[h] = m_new;
+                    for (int v = 0; v < VPL; ++v)
+#pragma unroll
+                        for (int i = 0; i < N; ++i) acc[h][v][i] = acc[h][v][i] * alpha + p * vv[u][v][i];
+                    m[h] = m_new;
+                }
             }
         }
     }

@@ -69,12 +69,14 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, long ld_in, T* __restr
 // token's absolute position, decoder.rs:2106-2111, 3489-3507; K/V append
 // decoder.rs:2123-2125, paged cache.rs:382-404).  Elements beyond `rotary_dim`
 // pass through.  `inv_freq == nullptr` means no rotation (position encoding none).
+// `cos_sin` (optional, [tokens, rotary_dim/2, 2]) holds cos and sin of exactly these
+// angles, made once per step by rope_table_kernel for all layers that share them.
 // Page layout: [page][kv_head][token_in_page][head_dim].
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __restrict__ positions,
                                      const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
-                                     const float* __restrict__ inv_freq, int rotary_dim,
-                                     T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                     const float* __restrict__ inv_freq, const float* __restrict__ cos_sin,
+                                     int rotary_dim, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      const int* __restrict__ block_table, int table_width, int page_size,
                                      int n_heads, int n_kv_heads, int head_dim, int write_cache,
                                      int* __restrict__ status)
@@ -95,9 +97,13 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __
     if (inv_freq) {
         for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
             const int h = idx / half, i = idx - h * half;
-            const float angle = (float)pos * inv_freq[i];
             float s, c;
-            sincosf(angle, &s, &c);
+            if (cos_sin) {
+                const float2 cs = *reinterpret_cast<const float2*>(cos_sin + ((long)t * half + i) * 2);
+                c = cs.x; s = cs.y;
+            } else {
+                sincosf((float)pos * inv_freq[i], &s, &c);
+            }
             T* x = row + (long)h * head_dim;
             const float a = to_f32(x[i]), b = to_f32(x[i + half]);
             x[i] = from_f32<T>(a * c - b * s);
@@ -116,6 +122,20 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __
     }
 }
 
+// cos_sin[t, i] = (cos, sin)(pos_t * inv_freq[i]), 32-bit angle and functions.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int n_tokens,
+                                  int half, float* __restrict__ cos_sin)
+{
+    const long n = (long)n_tokens * half;
+    for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < n; idx += (long)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / half), i = (int)(idx - (long)t * half);
+        float s, c;
+        sincosf((float)positions[t] * inv_freq[i], &s, &c);
+        cos_sin[idx * 2] = c;
+        cos_sin[idx * 2 + 1] = s;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // h[t,:] += sum_k w[t,k] * y[inv_perm[t*K+k], :]  (rank order k = 0..K-1)
 //          + (gate ? sigmoid(gate[t]) : 1) * shared[t,:]
@@ -131,7 +151,7 @@ __global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ 
     const int t = blockIdx.x;
     float g = 1.f;
     if (shared && shared_gate_logit) g = 1.0f / (1.0f + expf(-shared_gate_logit[t]));
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hidden; i += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top_k; ++k) {
             const long r = inv_perm[(long)t * top_k + k];
@@ -192,7 +212,8 @@ extern "C" int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, i
 }
 
 extern "C" int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const int* token_seq,
-                                const int* seq_slot, const float* inv_freq, int rotary_dim, void* k_pages,
+                                const int* seq_slot, const float* inv_freq, const float* cos_sin, int rotary_dim,
+                                void* k_pages,
                                 void* v_pages, const int* block_table, int table_width, int page_size, int n_tokens,
                                 int n_heads, int n_kv_heads, int head_dim, int write_cache, int* status, void* stream)
 {
@@ -203,13 +224,23 @@ extern "C" int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positi
     const int nt = threads_for(work > 256 ? 256 : work);
     if (dtype == FX_F32)
         rope_kv_write_kernel<float><<<n_tokens, nt, 0, s>>>((float*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
-            rotary_dim, (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
+            cos_sin, rotary_dim, (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
             head_dim, write_cache, status);
     else if (dtype == FX_BF16)
         rope_kv_write_kernel<bf16><<<n_tokens, nt, 0, s>>>((bf16*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
-            rotary_dim, (bf16*)k_pages, (bf16*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
+            cos_sin, rotary_dim, (bf16*)k_pages, (bf16*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
             head_dim, write_cache, status);
     else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+extern "C" int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin,
+                             void* stream)
+{
+    if (n_tokens <= 0 || half <= 0) return FX_OK;
+    long blocks = fx_cdiv((long)n_tokens * half, 128);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    rope_table_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(positions, inv_freq, n_tokens, half, cos_sin);
     return fx_launch_status();
 }
 
@@ -219,13 +250,14 @@ extern "C" int fx_moe_combine(float* h, const void* y, int dtype, const int* inv
 {
     if (n_tokens <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    const int nt = threads_for(hidden > 256 ? 256 : hidden);
+    const int nt = threads_for(hidden > 128 ? 128 : hidden);
+    const dim3 grid(n_tokens, (unsigned)fx_cdiv(hidden, nt));
     if (dtype == FX_F32)
-        moe_combine_kernel<float><<<n_tokens, nt, 0, s>>>(h, (const float*)y, inv_perm, topk_w, top_k,
-                                                          (const float*)shared, shared_gate_logit, hidden);
+        moe_combine_kernel<float><<<grid, nt, 0, s>>>(h, (const float*)y, inv_perm, topk_w, top_k,
+                                                      (const float*)shared, shared_gate_logit, hidden);
     else if (dtype == FX_BF16)
-        moe_combine_kernel<bf16><<<n_tokens, nt, 0, s>>>(h, (const bf16*)y, inv_perm, topk_w, top_k,
-                                                         (const bf16*)shared, shared_gate_logit, hidden);
+        moe_combine_kernel<bf16><<<grid, nt, 0, s>>>(h, (const bf16*)y, inv_perm, topk_w, top_k,
+                                                     (const bf16*)shared, shared_gate_logit, hidden);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.f;
 
-        constexpr int UNROLL = GATED ? 2 : 4;
+        constexpr int UNROLL = (GATED ? 4 : 8) / (NT > 2 ? 2 : 1);
         for (int c0 = warp * UNROLL; c0 < n_chunks; c0 += WARPS * UNROLL) {
             uint4 wa[UNROLL], wb[UNROLL], ua[UNROLL], ub[UNROLL];
 #pragma unroll

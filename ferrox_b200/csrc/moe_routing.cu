@@ -11,15 +11,9 @@ namespace {
 // and the weights are the kept p, divided by their sum when `renorm` is set
 // (reference: crates/ferrox-moe/src/lib.rs:333-355; lowest-index tie-break as in
 // its GPU kernel, crates/ferrox-metal/src/gpu.rs:686-699).
-__global__ void router_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, int renorm,
-                                   int* __restrict__ ids, float* __restrict__ weights)
+__device__ __forceinline__ void route_token(const float* __restrict__ lg, float* p, int lane, int t, int n_experts,
+                                            int top_k, int renorm, int* __restrict__ ids, float* __restrict__ weights)
 {
-    extern __shared__ float smem[];  // [warps][n_experts]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= n_tokens) return;
-    float* p = smem + (long)warp * n_experts;
-    const float* lg = logits + (long)t * n_experts;
     float mx = -INFINITY;
     for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
     mx = warp_max(mx);
@@ -48,6 +42,59 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int n_token
     if (renorm) {
         __syncwarp();
         for (int k = lane; k < top_k; k += 32) weights[(long)t * top_k + k] /= kept;
+    }
+}
+
+__global__ void router_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, int renorm,
+                                   int* __restrict__ ids, float* __restrict__ weights)
+{
+    extern __shared__ float smem[];  // [warps][n_experts]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    route_token(logits + (long)t * n_experts, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
+                weights);
+}
+
+// Routing and bookkeeping of a small step in ONE block: top-k per token (a warp
+// each), then counts, offsets, the list of experts that got rows, and the placement
+// of every (token, rank) pair, all in shared memory.
+constexpr int SMALL_WARPS = 16;
+__global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
+    const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, int renorm, int* __restrict__ ids,
+    float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ src_token, int* __restrict__ inv_perm,
+    int* __restrict__ active, int n_slots)
+{
+    extern __shared__ float smem[];  // [SMALL_WARPS][n_experts] floats, then 2 * n_experts + 1 ints
+    int* counts = reinterpret_cast<int*>(smem + (long)SMALL_WARPS * n_experts);
+    int* offs = counts + n_experts;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    for (int t = warp; t < n_tokens; t += SMALL_WARPS) {
+        route_token(logits + (long)t * n_experts, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
+                    weights);
+        __syncwarp();
+    }
+    __syncthreads();  // ids written by this block are visible to it after the barrier
+    const int n = n_tokens * top_k;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&counts[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0, n_active = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            offs[e] = run; offsets[e] = run; run += counts[e];
+            if (active && counts[e] > 0 && n_active < n_slots) active[n_active++] = e;
+            counts[e] = 0;  // becomes the cursor
+        }
+        offsets[n_experts] = run;
+        if (active) for (int i = n_active; i < n_slots; ++i) active[i] = -1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = ids[i];
+        const int r = offs[e] + atomicAdd(&counts[e], 1);
+        src_token[r] = i / top_k;
+        inv_perm[i] = r;
     }
 }
 
@@ -104,6 +151,20 @@ extern "C" int fx_router_topk(const float* logits, int n_tokens, int n_experts, 
     if (smem > 48 * 1024) return FX_ERR_SIZE;
     router_topk_kernel<<<(unsigned)fx_cdiv(n_tokens, warps), warps * 32, smem, (cudaStream_t)stream>>>(
         logits, n_tokens, n_experts, top_k, renorm, ids, weights);
+    return fx_launch_status();
+}
+
+// Routing of at most 1024 tokens in one launch (see route_small_kernel).
+extern "C" int fx_route_small(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
+                              float* weights, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots,
+                              void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (top_k <= 0 || top_k > n_experts || n_tokens > 1024) return FX_ERR_SIZE;
+    const size_t smem = (size_t)SMALL_WARPS * n_experts * sizeof(float) + (2 * (size_t)n_experts + 1) * sizeof(int);
+    if (smem > 48 * 1024) return FX_ERR_SIZE;
+    route_small_kernel<<<1, SMALL_WARPS * 32, smem, (cudaStream_t)stream>>>(
+        logits, n_tokens, n_experts, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active, n_slots);
     return fx_launch_status();
 }
 

@@ -45,6 +45,7 @@ class StepBatch:
     max_len: int = 0  # longest request length after this step
     max_new: int = 0  # most tokens any entry brings
     h2d_bytes: int = 0  # size of the step's host-to-device copy
+    shared: dict = field(default_factory=dict)  # per-step values that several layers share (e.g. rotary tables)
 
 
 def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: int) -> StepBatch:

@@ -36,7 +36,9 @@ _SIGNATURES = {
     "fx_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
     "fx_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_silu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _P],
-    "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fx_rope_table": [_P, _P, _I, _I, _P, _P],
+    "fx_route_small": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
@@ -171,11 +173,26 @@ def silu_mul(gu, out, stream=None):
     return out
 
 
+def rope_table(positions, inv_freq, out, stream=None):
+    """out[t, i] = (cos, sin)(positions[t] * inv_freq[i]); out is float32 [T, half, 2]."""
+    call("fx_rope_table", _ptr(positions), _ptr(inv_freq), positions.numel(), inv_freq.numel(), _ptr(out),
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def route_small(logits, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active=None, stream=None):
+    """router_topk and moe_align of a small step (at most 1024 tokens) in one launch."""
+    T, E = logits.shape
+    call("fx_route_small", _ptr(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights), _ptr(offsets),
+         _ptr(src_token), _ptr(inv_perm), _ptr(active), active.numel() if active is not None else 0,
+         stream if stream is not None else stream_ptr())
+
+
 def rope_kv_write(qkv, positions, token_seq, seq_slot, inv_freq, rotary_dim, k_pages, v_pages, block_table, page_size,
-                  n_heads, n_kv_heads, head_dim, write_cache=True, status=None, stream=None):
+                  n_heads, n_kv_heads, head_dim, write_cache=True, status=None, stream=None, cos_sin=None):
     T = qkv.shape[0]
     call("fx_rope_kv_write", _ptr(qkv), code(qkv), _rows(qkv), _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
-         _ptr(inv_freq), rotary_dim, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
+         _ptr(inv_freq), _ptr(cos_sin), rotary_dim, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
          T, n_heads, n_kv_heads, head_dim, int(write_cache), _ptr(status), stream if stream is not None else stream_ptr())
 
 
@@ -237,7 +254,7 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
 def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int):
     """(split_len, n_splits) for :func:`decode_attention`: enough blocks to fill the
     GPU, as a function of the step's size and the context limit only."""
-    target = 148 * 4
+    target = 148 * 16
     want = max(1, -(-target // max(1, n_tokens * n_kv_blocks)))
     split_len = max(64, -(-max_positions // want))
     split_len = -(-split_len // 64) * 64

@@ -83,10 +83,11 @@ class GqaAttention(Mixer):
         ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, stream=batch.stream)
         inv_freq = self.position.inv_freq if self.position is not None else None
         rotary = self.position.rotary_dim if self.position is not None else 0
+        cos_sin = self.position.table(batch) if self.position is not None else None
         ops.rope_kv_write(
             qkv, batch.positions, batch.token_seq, batch.seq_slot, inv_freq, rotary, cache.k, cache.v,
             cache.block_table, cache.page_size, s.n_heads, s.n_kv_heads, s.head_dim,
-            write_cache=cache.writes, status=batch.status, stream=batch.stream,
+            write_cache=cache.writes, status=batch.status, stream=batch.stream, cos_sin=cos_sin,
         )
         attn = self.rt.empty(T, self.q_size)
         if T <= DECODE_ATTENTION_MAX_TOKENS:

@@ -76,12 +76,15 @@ class SoftmaxTopkMoe(FeedForward):
         ops.linear(x, self.w_router, logits, stream=st)
         ids = rt.empty(T, K, dtype=i32)
         weights = rt.empty(T, K, dtype=torch.float32)
-        ops.router_topk(logits, K, s.norm_topk_prob, ids, weights, stream=st)
         offsets = rt.empty(E + 1, dtype=i32)
         src_token = rt.empty(T * K, dtype=i32)
         inv_perm = rt.empty(T * K, dtype=i32)
         active = rt.empty(min(E, T * K), dtype=i32) if small else None
-        ops.moe_align(ids, E, self._scratch, offsets, src_token, inv_perm, active, stream=st)
+        if T <= 256 and E <= 512:
+            ops.route_small(logits, K, s.norm_topk_prob, ids, weights, offsets, src_token, inv_perm, active, stream=st)
+        else:
+            ops.router_topk(logits, K, s.norm_topk_prob, ids, weights, stream=st)
+            ops.moe_align(ids, E, self._scratch, offsets, src_token, inv_perm, active, stream=st)
 
         act = rt.empty(T * K, I)
         y = rt.empty(T * K, H)

@@ -24,6 +24,19 @@ class RopeNeox(Part):
         self.inv_freq = (1.0 / torch.pow(theta, expo)).to(torch.float32).to(rt.device)
         self.rotary_dim = r
 
+    def table(self, batch):
+        """cos and sin of this step's angles, made once and shared by every layer with
+        the same base and width."""
+        from ..kernels import ops
+
+        key = ("rope_neox", float(self.spec.theta), self.rotary_dim)
+        t = batch.shared.get(key)
+        if t is None:
+            t = self.rt.empty(batch.n_tokens, self.rotary_dim // 2, 2, dtype=torch.float32)
+            ops.rope_table(batch.positions, self.inv_freq, t, stream=batch.stream)
+            batch.shared[key] = t
+        return t
+
 
 class NoPosition(Part):
     graph_safe = True
@@ -33,6 +46,9 @@ class NoPosition(Part):
         super().load(src, rt)
         self.inv_freq = None
         self.rotary_dim = 0
+
+    def table(self, batch):
+        return None
 
 
 register_part("rope_neox", RopeNeox, replace=True)

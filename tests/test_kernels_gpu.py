@@ -384,3 +384,47 @@ def test_rope_and_cache_write(dtype, nh, nkv, d, rot):
     o.rope_kv_write(qkv[:1], torch.tensor([20], dtype=torch.int32, device=DEV), token_seq[:1], seq_slot, inv_freq, rot,
                     kp, vp, table, ps, nh, nkv, d, True, status)
     assert int(status) == 2
+
+
+@pytest.mark.parametrize("T,E,K", [(1, 4, 2), (8, 60, 4), (33, 61, 5), (256, 8, 3)])
+def test_route_small_equals_the_two_step_routing(T, E, K):
+    o = ops()
+    logits = rnd(T, E, scale=2.0, seed=T)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    ids_a, w_a = torch.empty(T, K, **i32), torch.empty(T, K, device=DEV)
+    o.router_topk(logits, K, True, ids_a, w_a)
+    ids_b, w_b = torch.empty(T, K, **i32), torch.empty(T, K, device=DEV)
+    offsets, src, inv = torch.empty(E + 1, **i32), torch.empty(T * K, **i32), torch.empty(T * K, **i32)
+    active = torch.empty(min(E, T * K), **i32)
+    o.route_small(logits, K, True, ids_b, w_b, offsets, src, inv, active)
+    assert torch.equal(ids_a, ids_b) and torch.equal(w_a, w_b)
+    counts = torch.bincount(ids_b.flatten().long(), minlength=E)
+    assert offsets.tolist() == [0] + counts.cumsum(0).tolist()
+    assert sorted(inv.tolist()) == list(range(T * K))
+    flat = ids_b.flatten().tolist()
+    for i, r in enumerate(inv.tolist()):
+        assert int(offsets[flat[i]]) <= r < int(offsets[flat[i] + 1]) and int(src[r]) == i // K
+    act = [e for e in active.tolist() if e >= 0]
+    assert act == [e for e in range(E) if counts[e] > 0]
+
+
+def test_rope_table_matches_inline_angles():
+    o = ops()
+    nh, nkv, d, ps = 2, 1, 32, 8
+    T = 5
+    positions = torch.tensor([0, 3, 77, 1000, 4095], dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / torch.pow(torch.tensor(1e6), torch.arange(0, d // 2).float() * 2 / d)).to(DEV)
+    table = torch.empty(T, d // 2, 2, device=DEV)
+    o.rope_table(positions, inv_freq, table)
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    assert rel(table[..., 0], torch.cos(ang)) < 1e-6 and rel(table[..., 1], torch.sin(ang)) < 1e-6
+    qkv = rnd(T, (nh + 2 * nkv) * d)
+    a, b = qkv.clone(), qkv.clone()
+    z = torch.zeros(T, dtype=torch.int32, device=DEV)
+    slot = torch.zeros(1, dtype=torch.int32, device=DEV)
+    bt = torch.arange(0, 520, dtype=torch.int32, device=DEV).reshape(1, -1)
+    kp = torch.zeros(520, nkv, ps, d, device=DEV)
+    vp = torch.zeros_like(kp)
+    o.rope_kv_write(a, positions, z, slot, inv_freq, d, kp, vp, bt, ps, nh, nkv, d)
+    o.rope_kv_write(b, positions, z, slot, inv_freq, d, kp, vp, bt, ps, nh, nkv, d, cos_sin=table)
+    assert torch.equal(a, b)  # the table holds exactly the angles the kernel would compute
