@@ -35,6 +35,11 @@ int fx_router_topk(const float* logits, int n_tokens, int n_experts, int top_k, 
 int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets, int* src_token,
                  int* inv_perm, int* active, int n_slots, void* stream);
 
+int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, const void* bias,
+               int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
+               int gate_up_offset, const int* group_offsets, int n_groups, int* status, void* stream);
+int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo, int dtype, int n_rows, int width,
+                   void* stream);
 int fx_route_small(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
                    int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
 int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin, void* stream);

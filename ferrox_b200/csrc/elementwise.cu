@@ -162,6 +162,23 @@ __global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ 
     }
 }
 
+// out[r, :] = x[rows[r], :]  (tokens brought into expert order for the grouped products)
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, long ldx, const int* __restrict__ rows,
+                                   T* __restrict__ out, long ldo, int width, int vec_ok)
+{
+    const int r = blockIdx.x;
+    const T* src = x + (long)rows[r] * ldx;
+    T* dst = out + (long)r * ldo;
+    if (vec_ok) {
+        constexpr int V = 16 / sizeof(T);
+        for (int i = threadIdx.x; i < width / V; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
 // h[t,:] += y[t,:]
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ y, long n)
@@ -258,6 +275,22 @@ extern "C" int fx_moe_combine(float* h, const void* y, int dtype, const int* inv
     else if (dtype == FX_BF16)
         moe_combine_kernel<bf16><<<grid, nt, 0, s>>>(h, (const bf16*)y, inv_perm, topk_w, top_k,
                                                      (const bf16*)shared, shared_gate_logit, hidden);
+    else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+extern "C" int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo, int dtype, int n_rows,
+                              int width, void* stream)
+{
+    if (n_rows <= 0 || width <= 0) return FX_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int es = dtype == FX_F32 ? 4 : 2;
+    const int vec_ok = (width * es) % 16 == 0 && (ldx * es) % 16 == 0 && (ldo * es) % 16 == 0 &&
+                       (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0;
+    if (dtype == FX_F32)
+        gather_rows_kernel<float><<<n_rows, 128, 0, s>>>((const float*)x, ldx, rows, (float*)out, ldo, width, vec_ok);
+    else if (dtype == FX_BF16)
+        gather_rows_kernel<bf16><<<n_rows, 128, 0, s>>>((const bf16*)x, ldx, rows, (bf16*)out, ldo, width, vec_ok);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

@@ -1,0 +1,406 @@
+// Prompt-sized matrix products on the 5th-generation tensor cores:
+//   C[M, N] (+)= X[M, K] . W[N, K]^T (+ bias)          bfloat16 in, 32-bit sums in TMEM
+// plus the gated form (silu(gate) * up in the epilogue) and the grouped form for
+// experts (rows sorted by expert; tile (expert, m) found on the device).
+//
+// One CTA computes one 128 x BN tile.  Warp 0 is the producer: one thread issues
+// TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a 128 x 64 slice of X and a
+// BN x 64 slice of W per stage into a ring of shared-memory stages guarded by
+// mbarriers.  Warp 1 issues tcgen05.mma (one thread, cta_group::1, kind::f16 with
+// bfloat16 operands): four K=16 instructions per stage, accumulating into BN
+// columns of tensor memory, and releases each stage with tcgen05.commit.  Warps 2-5
+// are the epilogue: each reads its quadrant of 32 TMEM lanes (= 32 rows of the tile)
+// with tcgen05.ld, applies bias / SiLU gate / accumulation and stores rows.
+// No cluster launch and no multicast: every CTA fetches its own tiles.
+//
+// Every wait is bounded: a wait that runs out raises `status` (code 3), the roles
+// leave their loops, the producer waits (bounded) for loads it has in flight, tensor
+// memory is freed and the kernel returns.
+//
+// Shapes: any M, N; K a multiple of 8 (16-byte row pitch for TMA), pointers 16-byte
+// aligned; rows and columns beyond the edges are zero-filled by TMA and masked at
+// the store.  Other shapes are refused (the caller falls back to the CUDA-core
+// kernel).
+//
+// Reference: none on the GPU (the reference's prefill loops a mat-vec per token,
+// crates/ferrox-core/src/weight_matrix.rs:1115-1122); the product itself is
+// crates/ferrox-core/src/matmul.rs:18-58, experts crates/ferrox-moe/src/lib.rs:619-659.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+constexpr int BM = 128;          // rows of X per tile = TMEM lanes
+constexpr int BK = 64;           // bfloat16 elements per stage along K = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NTHREADS = 192;    // producer warp, mma warp, four epilogue warps
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr int FX_STATUS_TC_TIMEOUT = 3;
+
+template <int BN> struct Cfg {
+    static constexpr int STAGES = BN <= 128 ? 6 : 4;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+struct TcArgs {
+    void* C; long ldc; int c_dtype; int accumulate;
+    const void* bias; int bias_dtype;
+    int M, N, K;
+    int gate_up_offset;             // gated: W row of `up` feature j is gate_up_offset + j
+    const int* group_offsets;       // grouped: rows [off[e], off[e+1]) use matrix e
+    int n_groups;
+    int* status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle
+// (rows of 128 bytes, 8-row groups 1024 bytes apart): start address, stride between
+// row groups, descriptor version 1, swizzle mode 2 (128 B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // bits 0-13: start address / 16
+    d |= (uint64_t)1 << 16;                            // bits 16-29: leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // bits 32-45: stride byte offset / 16
+    d |= (uint64_t)1 << 46;                            // bits 46-47: descriptor version
+    d |= (uint64_t)2 << 61;                            // bits 61-63: 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: D = f32, A = B = bf16, both K-major, N / 8 and M / 16.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN, bool GATED>
+__global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                              const __grid_constant__ CUtensorMap map_b, TcArgs a)
+{
+    using C = Cfg<BN>;
+    constexpr int STAGES = C::STAGES;
+    constexpr int OUT_N = GATED ? BN / 2 : BN;   // output features per tile
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int tile_info[3];
+    __shared__ int abort_flag_s;
+    __shared__ uint32_t tmem_base_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- which tile -----------------------------------------------------------
+    int group = 0, row_begin = 0, row_end = a.M, m_tile = blockIdx.y;
+    if (a.group_offsets) {
+        if (threadIdx.x == 0) {
+            int y = blockIdx.y, found = -1;
+            for (int e = 0; e < a.n_groups; ++e) {
+                const int rows = a.group_offsets[e + 1] - a.group_offsets[e];
+                const int tiles = (rows + BM - 1) / BM;
+                if (y < tiles) { found = e; break; }
+                y -= tiles;
+            }
+            tile_info[0] = found; tile_info[1] = y;
+        }
+        __syncthreads();
+        group = tile_info[0];
+        if (group < 0) return;   // the grid is an upper bound on the number of tiles
+        m_tile = tile_info[1];
+        row_begin = a.group_offsets[group];
+        row_end = a.group_offsets[group + 1];
+    }
+    const int m0 = row_begin + m_tile * BM;
+    if (m0 >= row_end) return;
+    const int n0 = blockIdx.x * OUT_N;
+    const int k_blocks = (a.K + BK - 1) / BK;
+
+    // ---- shared memory: stages (1024-byte aligned), then barriers ---------------
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t bar_base = base + STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bar_base + 8u * (2 * STAGES);
+    volatile int* abort_flag = &abort_flag_s;
+
+    if (threadIdx.x == 0) {
+        abort_flag_s = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {   // tensor memory: BN columns of 128 lanes x 32 bit
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
+                if (!mbar_wait(empty_bar(s), parity, abort_flag)) break;
+                const uint32_t sa = base + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+                mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                tma_load_2d(sa, &map_a, kb * BK, m0, full_bar(s));
+                if (GATED) {
+                    tma_load_3d(sb, &map_b, kb * BK, n0, group, full_bar(s));
+                    tma_load_3d(sb + C::B_BYTES / 2, &map_b, kb * BK, a.gate_up_offset + n0, group, full_bar(s));
+                } else {
+                    tma_load_3d(sb, &map_b, kb * BK, n0, group, full_bar(s));
+                }
+                issued = kb + 1;
+            }
+            if (*abort_flag) {
+                // loads already issued must land before the CTA's shared memory is released
+                for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+                    const int s = kb % STAGES;
+                    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+                        if (mbar_try_wait(full_bar(s), (kb / STAGES) & 1)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- tensor-core issue ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(full_bar(s), (kb / STAGES) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = base + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+                const uint64_t da = smem_desc(sa), db = smem_desc(sb);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 elements = 32 bytes further along K inside the swizzled row: +2 in units of 16 bytes
+                    tc_mma(tmem_base, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                }
+                tc_commit(empty_bar(s));   // the stage is free once these instructions have read it
+            }
+            if (ok) tc_commit(accum_bar);  // the accumulator is complete once all instructions have retired
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int quad = warp & 3;                       // TMEM lanes 32*quad .. 32*quad+31
+        const int row = m0 + quad * 32 + lane;
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0, abort_flag));  // tcgen05.ld needs whole warps
+        if (ok) {
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            const bool row_ok = row < row_end;
+#pragma unroll 1
+            for (int c = 0; c < OUT_N / 32; ++c) {
+                uint32_t r[32], u[32];
+                tc_ld32(lane_addr + c * 32, r);
+                if (GATED) tc_ld32(lane_addr + BN / 2 + c * 32, u);
+                tc_ld_wait();
+                const int nb = n0 + c * 32;
+                if (!row_ok || nb >= a.N) continue;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float x = __uint_as_float(r[j]);
+                    if (a.bias && nb + j < a.N) x += load_any(a.bias, a.bias_dtype, nb + j);
+                    if (GATED) x = x / (1.0f + __expf(-x)) * __uint_as_float(u[j]);
+                    v[j] = x;
+                }
+                const bool full = nb + 32 <= a.N;
+                if (a.c_dtype == FX_F32) {
+                    float* cp = reinterpret_cast<float*>(a.C) + (long)row * a.ldc + nb;
+                    if (full && (a.ldc % 4 == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (a.accumulate) {
+                                const float4 p = *reinterpret_cast<const float4*>(cp + j);
+                                o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                            }
+                            *reinterpret_cast<float4*>(cp + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && nb + j < a.N; ++j) cp[j] = a.accumulate ? cp[j] + v[j] : v[j];
+                    }
+                } else {
+                    bf16* cp = reinterpret_cast<bf16*>(a.C) + (long)row * a.ldc + nb;
+                    if (full && (a.ldc % 8 == 0) && !a.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 o;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                            o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                            o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                            *reinterpret_cast<uint4*>(cp + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && nb + j < a.N; ++j)
+                            cp[j] = __float2bfloat16_rn(a.accumulate ? __bfloat162float(cp[j]) + v[j] : v[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown ---------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag_s && a.status) atomicExch(a.status, FX_STATUS_TC_TIMEOUT);
+}
+
+// ---- host side ----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// bf16 tensor [d2][d1][K] (row pitch ld1 elements, matrix pitch ld2 elements), box {64, box1, 1}
+bool make_map(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t d1, uint64_t d2, uint64_t ld1, uint64_t ld2,
+              uint32_t box1, int rank)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {K, d1, d2};
+    cuuint64_t strides[2] = {ld1 * 2, ld2 * 2};
+    cuuint32_t box[3] = {(cuuint32_t)BK, box1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool GATED>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t s)
+{
+    auto kern = gemm_tc_kernel<BN, GATED>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kern<<<grid, NTHREADS, Cfg<BN>::SMEM, s>>>(ma, mb, a);
+    return fx_launch_status();
+}
+
+}  // namespace
+
+// X [M, K] and W [G, w_rows, K] bfloat16; C bfloat16 or float32.  gated: W holds gate rows [0, N) and up rows
+// [gate_up_offset, gate_up_offset + N), C = silu(gate) * up.  grouped: group_offsets [n_groups + 1] on the device,
+// rows of X (and of C) sorted by group; M is then the total number of rows.
+extern "C" int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows,
+                          const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate,
+                          int M, int N, int K, int gated, int gate_up_offset, const int* group_offsets, int n_groups,
+                          int* status, void* stream)
+{
+    if (M <= 0 || N <= 0) return FX_OK;
+    if (K <= 0 || K % 8) return FX_ERR_SIZE;
+    if (ldx % 8 || ldw % 8 || w_group_stride % 8 || (uintptr_t)X % 16 || (uintptr_t)W % 16) return FX_ERR_ALIGN;
+    if (c_dtype != FX_F32 && c_dtype != FX_BF16) return FX_ERR_DTYPE;
+    constexpr int BN = 128;
+    const int out_n = gated ? BN / 2 : BN;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, X, (uint64_t)K, (uint64_t)M, 1, (uint64_t)ldx, 0, BM, 2)) return FX_ERR_SIZE;
+    const int G = group_offsets ? n_groups : 1;
+    if (!make_map(&mb, W, (uint64_t)K, (uint64_t)w_rows, (uint64_t)G, (uint64_t)ldw,
+                  (uint64_t)(G > 1 ? w_group_stride : (long)w_rows * ldw), gated ? BN / 2 : BN, 3))
+        return FX_ERR_SIZE;
+    TcArgs a;
+    a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
+    a.bias = bias; a.bias_dtype = bias_dtype;
+    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset;
+    a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status;
+    const long m_tiles = group_offsets ? fx_cdiv(M, BM) + n_groups : fx_cdiv(M, BM);
+    dim3 grid((unsigned)fx_cdiv(N, out_n), (unsigned)m_tiles);
+    if (grid.y > 65535u) return FX_ERR_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    return gated ? launch<BN, true>(ma, mb, a, grid, s) : launch<BN, false>(ma, mb, a, grid, s);
+}

@@ -71,7 +71,8 @@ def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True, grap
         code = int(status.item())
         if code:
             status.zero_()
-            what = {1: "a token id outside the vocabulary", 2: "a position without a cache page"}.get(code, code)
+            what = {1: "a token id outside the vocabulary", 2: "a position without a cache page",
+                    3: "a bounded wait that ran out inside a tensor-core kernel"}.get(code, code)
             raise StepFault(f"step met {what}")
     return logits
 

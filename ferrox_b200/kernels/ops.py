@@ -38,6 +38,8 @@ _SIGNATURES = {
     "fx_silu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _P],
     "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_rope_table": [_P, _P, _I, _I, _P, _P],
+    "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
+    "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
     "fx_route_small": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
@@ -272,10 +274,42 @@ def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, tok
     return out
 
 
-def linear(x, w, out, *, bias=None, accumulate=False, stream=None):
+def tc_ok(x, w) -> bool:
+    """Whether the tcgen05 kernel takes these operands (bfloat16, 16-byte aligned rows)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and w.stride(-2) % 8 == 0 and (w.dim() == 2 or w.stride(0) % 8 == 0) and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(-1) == 1)
+
+
+def gemm_tc(x, w, out, *, bias=None, accumulate=False, gated=False, group_offsets=None, status=None, stream=None):
+    """out[M, N] (+)= x . w^T on the tcgen05 tensor cores.  ``gated``: ``w`` is [gate rows ; up rows] and
+    out = silu(gate) * up.  Grouped: ``w`` is [G, rows, K] and the rows of ``x``/``out`` are sorted by group."""
+    M, N = out.shape
+    K = x.shape[1]
+    if group_offsets is not None:
+        G, wrows, ldw, wstride = w.shape[0], w.shape[1], w.stride(1), w.stride(0)
+    else:
+        G, wrows, ldw, wstride = 0, w.shape[0], w.stride(0), 0
+    if wrows != (2 * N if gated else N) or w.shape[-1] != K or x.shape[0] != M:
+        raise KernelError(f"gemm_tc shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    call("fx_gemm_tc", _ptr(x), _rows(x), _ptr(w), ldw, wstride, wrows, _ptr(bias), code(bias) if bias is not None else 0,
+         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0,
+         _ptr(group_offsets), G, _ptr(status), stream if stream is not None else stream_ptr())
+    return out
+
+
+def gather_rows(x, rows, out, stream=None):
+    call("fx_gather_rows", _ptr(x), _rows(x), _ptr(rows), _ptr(out), _rows(out), code(x), out.shape[0], x.shape[1],
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None):
     """out (+)= x . w^T (+ bias): picks the kernel by size and element type."""
     if x.shape[0] <= SKINNY_MAX_TOKENS and skinny_ok(x, w):
         return gemm_skinny(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
+    if x.shape[0] > SKINNY_MAX_TOKENS and tc_ok(x, w):
+        return gemm_tc(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
     return gemm(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
 
 

@@ -80,7 +80,7 @@ class GqaAttention(Mixer):
         s = self.spec
         T = x.shape[0]
         qkv = self.rt.empty(T, self.q_size + 2 * self.kv_size)
-        ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, stream=batch.stream)
+        ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, status=batch.status, stream=batch.stream)
         inv_freq = self.position.inv_freq if self.position is not None else None
         rotary = self.position.rotary_dim if self.position is not None else 0
         cos_sin = self.position.table(batch) if self.position is not None else None
@@ -107,7 +107,7 @@ class GqaAttention(Mixer):
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
             )
-        ops.linear(attn, self.w_o, h, accumulate=True, stream=batch.stream)
+        ops.linear(attn, self.w_o, h, accumulate=True, status=batch.status, stream=batch.stream)
 
 
 register_part("gqa_attention", GqaAttention, replace=True)

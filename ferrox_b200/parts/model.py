@@ -94,5 +94,5 @@ class DecoderModel(Part):
             return rt.empty(0, s.vocab_size, dtype=torch.float32)
         x = self.final_norm.forward(h, rows=batch.want_rows)
         logits = rt.empty(batch.n_want, s.vocab_size, dtype=torch.float32)
-        ops.linear(x, self.head, logits, stream=batch.stream)
+        ops.linear(x, self.head, logits, status=batch.status, stream=batch.stream)
         return logits

@@ -72,8 +72,9 @@ class SoftmaxTopkMoe(FeedForward):
         T, E, K, I, H = x.shape[0], s.n_experts, s.top_k, s.expert_intermediate, s.hidden
         i32 = torch.int32
         small = T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
+        big = T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_gu) and I % 8 == 0
         logits = rt.empty(T, E, dtype=torch.float32)
-        ops.linear(x, self.w_router, logits, stream=st)
+        ops.linear(x, self.w_router, logits, status=batch.status, stream=st)
         ids = rt.empty(T, K, dtype=i32)
         weights = rt.empty(T, K, dtype=torch.float32)
         offsets = rt.empty(E + 1, dtype=i32)
@@ -93,6 +94,12 @@ class SoftmaxTopkMoe(FeedForward):
             ops.gemm_skinny(x, self.w_gu, act, gated=True, x_rows=src_token, group_offsets=offsets,
                             active_groups=active, tokens_hint=T, stream=st)
             ops.gemm_skinny(act, self.w_down, y, group_offsets=offsets, active_groups=active, tokens_hint=T, stream=st)
+        elif big:
+            # many tokens: bring them into expert order once, then grouped tensor-core products
+            xp = rt.empty(T * K, H)
+            ops.gather_rows(x, src_token, xp, stream=st)
+            ops.gemm_tc(xp, self.w_gu, act, gated=True, group_offsets=offsets, status=batch.status, stream=st)
+            ops.gemm_tc(act, self.w_down, y, group_offsets=offsets, status=batch.status, stream=st)
         else:
             gu = rt.empty(T * K, 2 * I)
             ops.gemm(x, self.w_gu, gu, a_rows=src_token, group_offsets=offsets, stream=st)
@@ -105,15 +112,17 @@ class SoftmaxTopkMoe(FeedForward):
             sact = rt.empty(T, Is)
             if T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_shared_gu):
                 ops.gemm_skinny(x, self.w_shared_gu, sact, gated=True, stream=st)
+            elif T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_shared_gu):
+                ops.gemm_tc(x, self.w_shared_gu, sact, gated=True, status=batch.status, stream=st)
             else:
                 sgu = rt.empty(T, 2 * Is)
                 ops.gemm(x, self.w_shared_gu, sgu, stream=st)
                 ops.silu_mul(sgu, sact, stream=st)
             shared = rt.empty(T, H)
-            ops.linear(sact, self.w_shared_down, shared, stream=st)
+            ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
             if self.w_shared_gate is not None:
                 gate_logit = rt.empty(T, 1, dtype=torch.float32)
-                ops.linear(x, self.w_shared_gate, gate_logit, stream=st)
+                ops.linear(x, self.w_shared_gate, gate_logit, status=batch.status, stream=st)
         ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st)
 
 

@@ -428,3 +428,75 @@ def test_rope_table_matches_inline_angles():
     o.rope_kv_write(a, positions, z, slot, inv_freq, d, kp, vp, bt, ps, nh, nkv, d)
     o.rope_kv_write(b, positions, z, slot, inv_freq, d, kp, vp, bt, ps, nh, nkv, d, cos_sin=table)
     assert torch.equal(a, b)  # the table holds exactly the angles the kernel would compute
+
+
+# ------------------------------------------------------------------ tcgen05 products
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 512), (65, 60, 72), (300, 200, 2048), (129, 130, 200),
+                                   (2048, 256, 1408)])
+def test_gemm_tc_dense(M, N, K):
+    o = ops()
+    x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1), rnd(N)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = x.float() @ w.float().T
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(x, w, out, bias=bias, status=status)
+    assert int(status) == 0
+    assert rel(out, want + bias) < TOL["bfloat16"]
+    acc = rnd(M, N, seed=3)
+    base = acc.clone()
+    o.gemm_tc(x, w, acc, accumulate=True, status=status)
+    assert int(status) == 0 and rel(acc, base + want) < 2e-5
+    # a strided view of wider rows, as the attention output is inside the fused q|k|v rows
+    wide = rnd(M, K + 64, dtype=torch.bfloat16, seed=11)
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    o.gemm_tc(wide[:, :K], w, out32, status=status)
+    assert rel(out32, wide[:, :K].float() @ w.float().T) < 2e-5
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (200, 1408, 256), (70, 100, 96)])
+def test_gemm_tc_gated(M, I, K):
+    o = ops()
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(2 * I, K, dtype=torch.bfloat16, scale=0.2)
+    gate, up = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
+    out = torch.empty(M, I, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.gemm_tc(x, w, out, gated=True, status=status)
+    assert int(status) == 0 and rel(out, gate / (1 + torch.exp(-gate)) * up) < 3e-5
+
+
+@pytest.mark.parametrize("counts", [[0, 130, 1, 0, 128, 255], [3, 0, 0, 0, 0, 700], [64, 64, 64, 64, 64, 64]])
+def test_gemm_tc_grouped(counts):
+    o = ops()
+    G, I, H = len(counts), 96, 128
+    R = sum(counts)
+    x = rnd(R, H, dtype=torch.bfloat16)
+    w_gu, w_down = rnd(G, 2 * I, H, dtype=torch.bfloat16, scale=0.1), rnd(G, H, I, dtype=torch.bfloat16, scale=0.1)
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    act = torch.full((R, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(x, w_gu, act, gated=True, group_offsets=offsets, status=status)
+    y = torch.empty(R, H, dtype=torch.float32, device=DEV)
+    o.gemm_tc(act, w_down, y, group_offsets=offsets, status=status)
+    assert int(status) == 0
+    r = 0
+    for g, c in enumerate(counts):
+        if c == 0:
+            continue
+        gu = x[r:r + c].float() @ w_gu[g].float().T
+        want = gu[:, :I] / (1 + torch.exp(-gu[:, :I])) * gu[:, I:]
+        assert rel(act[r:r + c], want) < TOL["bfloat16"], g
+        assert rel(y[r:r + c], act[r:r + c].float() @ w_down[g].float().T) < 2e-5, g
+        r += c
+
+
+def test_gather_rows():
+    o = ops()
+    x = rnd(9, 72, dtype=torch.bfloat16)
+    rows = torch.tensor([8, 0, 0, 3, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, dtype=torch.bfloat16, device=DEV)
+    o.gather_rows(x, rows, out)
+    assert torch.equal(out, x[rows.long()])
+    xf = rnd(9, 7)
+    outf = torch.empty(5, 7, device=DEV)
+    o.gather_rows(xf, rows, outf)
+    assert torch.equal(outf, xf[rows.long()])
