@@ -30,6 +30,10 @@ int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void*
                        const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens, int n_heads,
                        int n_kv_heads, int head_dim, int window, float scale, void* stream);
 
+int fx_prefill_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table,
+                         int table_width, int page_size, const int* tiles, int n_tiles, const int* seq_slot, void* out,
+                         long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale, void* stream);
+
 int fx_router_topk(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
                    void* stream);
 int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets, int* src_token,

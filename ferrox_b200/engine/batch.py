@@ -21,6 +21,9 @@ import numpy as np
 import torch
 
 
+QUERY_TILE = 64  # query tokens per tile of the prompt attention kernel
+
+
 @dataclass
 class StepEntry:
     slot: int
@@ -45,6 +48,7 @@ class StepBatch:
     max_len: int = 0  # longest request length after this step
     max_new: int = 0  # most tokens any entry brings
     h2d_bytes: int = 0  # size of the step's host-to-device copy
+    q_tiles: torch.Tensor = None  # [n_tiles, 4] int32: (first flat token, rows <= 64, entry, first position)
     shared: dict = field(default_factory=dict)  # per-step values that several layers share (e.g. rotary tables)
 
 
@@ -52,10 +56,12 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
     T = sum(len(e.tokens) for e in entries)
     B = len(entries)
     W = sum(len(e.want) for e in entries)
-    buf = np.empty(3 * T + B + W, dtype=np.int32)
+    n_tiles = sum(-(-len(e.tokens) // QUERY_TILE) for e in entries)
+    buf = np.empty(3 * T + B + W + 4 * n_tiles, dtype=np.int32)
     tok, pos, seq = buf[:T], buf[T:2 * T], buf[2 * T:3 * T]
-    slots, want = buf[3 * T:3 * T + B], buf[3 * T + B:]
-    t = w = 0
+    slots, want = buf[3 * T:3 * T + B], buf[3 * T + B:3 * T + B + W]
+    tiles = buf[3 * T + B + W:].reshape(n_tiles, 4)
+    t = w = ti = 0
     max_len = max_new = 0
     for b, e in enumerate(entries):
         n = len(e.tokens)
@@ -68,6 +74,9 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
                 raise ValueError(f"want index {i} outside the entry's {n} tokens")
             want[w] = t + i
             w += 1
+        for i in range(0, n, QUERY_TILE):
+            tiles[ti] = (t + i, min(QUERY_TILE, n - i), b, e.start + i)
+            ti += 1
         t += n
         max_len = max(max_len, e.start + n)
         max_new = max(max_new, n)
@@ -75,7 +84,8 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
     return StepBatch(
         n_tokens=T, n_seqs=B, n_want=W,
         token_ids=dev[:T], positions=dev[T:2 * T], token_seq=dev[2 * T:3 * T],
-        seq_slot=dev[3 * T:3 * T + B], want_rows=dev[3 * T + B:],
+        seq_slot=dev[3 * T:3 * T + B], want_rows=dev[3 * T + B:3 * T + B + W],
+        q_tiles=dev[3 * T + B + W:].view(n_tiles, 4),
         status=status, stream=stream, entries=list(entries), max_len=max_len, max_new=max_new,
         h2d_bytes=buf.nbytes,
     )

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
+    "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P],
     "fx_router_topk": [_P, _I, _I, _I, _I, _P, _P, _P],
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P],
@@ -205,6 +206,21 @@ def paged_attention(q, k_pages, v_pages, block_table, page_size, positions, toke
     call("fx_paged_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), code(q), _ptr(block_table),
          block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out), _rows(out), T,
          n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), stream if stream is not None else stream_ptr())
+    return out
+
+
+PREFILL_TILE = 64
+
+
+def prefill_attention(q, k_pages, v_pages, block_table, page_size, tiles, seq_slot, out, n_heads, n_kv_heads, head_dim,
+                      window, scale, stream=None):
+    """Flash attention of prompt portions (bfloat16).  ``tiles``: int32 [n, 4] rows of
+    (first flat token, rows <= 64, entry index, absolute position of the first row)."""
+    if q.dtype != torch.bfloat16:
+        raise KernelError("prefill_attention is a bfloat16 kernel")
+    call("fx_prefill_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+         block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0], _ptr(seq_slot), _ptr(out), _rows(out), n_heads,
+         n_kv_heads, head_dim, int(window or 0), float(scale), stream if stream is not None else stream_ptr())
     return out
 
 

@@ -21,7 +21,7 @@ from ..weights.loader import TensorDecl
 from .base import Mixer, build_part, register_part
 
 
-DECODE_ATTENTION_MAX_TOKENS = 64
+DECODE_ATTENTION_MAX_NEW = 8  # entries that bring at most this many tokens use the split-key kernel
 
 
 def _common_dtype(tensors):
@@ -90,7 +90,7 @@ class GqaAttention(Mixer):
             write_cache=cache.writes, status=batch.status, stream=batch.stream, cos_sin=cos_sin,
         )
         attn = self.rt.empty(T, self.q_size)
-        if T <= DECODE_ATTENTION_MAX_TOKENS:
+        if batch.max_new <= DECODE_ATTENTION_MAX_NEW:
             # few query tokens: split each request's keys over many blocks
             group = s.n_heads // s.n_kv_heads
             kv_blocks = s.n_kv_heads * -(-group // 8)
@@ -101,6 +101,12 @@ class GqaAttention(Mixer):
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, split_len, n_splits,
                 part_acc, part_ml, stream=batch.stream,
+            )
+        elif qkv.dtype == torch.bfloat16 and batch.q_tiles is not None:
+            # prompt portions: tiles of 64 queries on the tensor cores
+            ops.prefill_attention(
+                qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.q_tiles, batch.seq_slot, attn,
+                s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
             )
         else:
             ops.paged_attention(

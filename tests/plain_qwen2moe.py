@@ -165,6 +165,19 @@ def route(logits, k, renorm):
     return order, wts
 
 
+def router_margins(x, w, cfg, l):
+    """For each token, how clearly the router separates the last expert it takes from
+    the first it leaves out: the gap between their logits, relative to the largest
+    |logit| of the token.  A reduced-precision engine cannot be expected to make the
+    same choice where this gap is a few roundings of a logit."""
+    lg = x @ w[f"model.layers.{l}.mlp.gate.weight"].T
+    k = cfg["num_experts_per_tok"]
+    if lg.shape[-1] <= k:
+        return torch.full((x.shape[0],), float("inf"))
+    top = torch.topk(lg, k + 1, dim=-1).values
+    return ((top[:, k - 1] - top[:, k]) / lg.abs().max(dim=-1).values).to(torch.float32)
+
+
 def moe_block(x, w, cfg, l):
     """Router, routed experts summed in rank order, shared expert scaled by
     sigmoid(w_sg . x) (crates/ferrox-moe/src/lib.rs:735-752;
@@ -198,7 +211,7 @@ def dense_block(x, w, l):
 
 
 # --------------------------------------------------------------------------- whole model
-def forward(cfg, w, tokens, return_hidden=False):
+def forward(cfg, w, tokens, return_hidden=False, return_margins=False):
     """Logits [T, vocab] for one whole sequence starting at position 0
     (crates/ferrox-models/src/decoder.rs:3014-3677 and :2952-2973)."""
     dtype = w["model.embed_tokens.weight"].dtype
@@ -206,15 +219,20 @@ def forward(cfg, w, tokens, return_hidden=False):
     positions = torch.arange(tokens.numel())
     eps = cfg.get("rms_norm_eps", 1e-6)
     h = w["model.embed_tokens.weight"][tokens].clone()
+    margins = torch.full((tokens.numel(),), float("inf"))
     for l in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{l}."
         h = h + attention_block(rms_norm(h, w[p + "input_layernorm.weight"], eps), w, cfg, l, positions)
         n = rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+        if layer_is_moe(cfg, l) and return_margins:
+            margins = torch.minimum(margins, router_margins(n, w, cfg, l))
         h = h + (moe_block(n, w, cfg, l) if layer_is_moe(cfg, l) else dense_block(n, w, l))
     hn = rms_norm(h, w["model.norm.weight"], eps)
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     logits = hn @ head.T
     assert logits.dtype == dtype
+    if return_margins:
+        return logits, margins
     return (logits, h) if return_hidden else logits
 
 

@@ -15,6 +15,24 @@ def plain_logits(folder: str, prompts: Dict[str, List[int]], dtype=torch.float32
     return {rid: plain.forward(cfg, w, toks).to(torch.float32) for rid, toks in prompts.items()}
 
 
+class Expected:
+    """Plain logits per request plus, per position, the router's smallest relative
+    margin over the layers (see plain.router_margins)."""
+
+    def __init__(self, folder: str, prompts: Dict[str, List[int]]):
+        cfg, w = plain.load_model(folder, torch.float32)
+        self.logits, self.margins = {}, {}
+        for rid, toks in prompts.items():
+            lg, mg = plain.forward(cfg, w, toks, return_margins=True)
+            self.logits[rid], self.margins[rid] = lg, mg
+
+    def __getitem__(self, rid):
+        return self.logits[rid]
+
+    def __iter__(self):
+        return iter(self.logits)
+
+
 class Collector:
     """Runs steps against an engine and stores logits by (request, position)."""
 

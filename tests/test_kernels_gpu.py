@@ -500,3 +500,35 @@ def test_gather_rows():
     outf = torch.empty(5, 7, device=DEV)
     o.gather_rows(xf, rows, outf)
     assert torch.equal(outf, xf[rows.long()])
+
+
+@pytest.mark.parametrize("case", ATT_CASES + [(4, 4, 80, 16, 33, [200, 70]), (2, 2, 16, 4, 0, [129])])
+def test_prefill_attention_tiles(case):
+    """Prompt portions (whole prompts and continuations after a cached prefix) through
+    the tiled tensor-core kernel, against the plain per-query statement."""
+    o = ops()
+    nh, nkv, d, ps, window, lens = case
+    dt = torch.bfloat16
+    kp, vp, table, ks, vs = build_cache(dt, lens, nkv, d, ps, n_pages=sum(-(-L // ps) for L in lens) + 3, seed=2)
+    starts = [0 if i % 2 == 0 else min(L - 1, max(1, L // 3)) for i, L in enumerate(lens)]
+    toks, tiles, flat = [], [], 0
+    for s, (L, st) in enumerate(zip(lens, starts)):
+        n = L - st
+        for i in range(0, n, 64):
+            tiles.append((flat + i, min(64, n - i), s, st + i))
+        toks += [(s, p) for p in range(st, L)]
+        flat += n
+    T = len(toks)
+    q = rnd(T, nh * d + 2 * nkv * d, dtype=dt, seed=T)
+    tiles_t = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor([s + 1 for s in range(len(lens))], dtype=torch.int32, device=DEV)
+    out = torch.zeros(T, nh * d, dtype=dt, device=DEV)
+    scale = 1 / math.sqrt(d)
+    o.prefill_attention(q, kp, vp, table, ps, tiles_t, seq_slot, out, nh, nkv, d, window, scale)
+    assert torch.isfinite(out.float()).all()
+    step = max(1, T // 40)  # a spread of tokens, plus tile edges
+    check = sorted(set(list(range(0, T, step)) + [t for t in (0, 1, 63, 64, 65, 127, 128, T - 1) if t < T]))
+    for i in check:
+        s, pos = toks[i]
+        want = plain_attention(q[i, : nh * d].float().cpu().reshape(nh, d), ks[s], vs[s], pos, window, scale)
+        assert rel(out[i].float().cpu().reshape(nh, d), want) < 1.5e-2, (i, s, pos)

@@ -16,7 +16,13 @@ pytestmark = pytest.mark.gpu
 # 32-bit: both sides round 32-bit sums in different orders.  bfloat16: activations
 # between kernels are rounded to 8 bits of mantissa.
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
-
+# In bfloat16 a router choice is not comparable where the plain implementation itself
+# separates the experts at the cut by less than a few roundings: the gap between the
+# two logits is under 2^-7 of the token's largest |logit| (bfloat16 spaces values
+# 2^-8 apart).  The engine may then take the other expert and the logits of that
+# position differ by whole percents.  Such positions are left out of the bfloat16
+# comparison (never of the 32-bit one); they must stay few.
+BF16_ROUTER_MARGIN = 2.0 ** -7
 
 def prompts_for(name, n=5, lo=1, hi=96, seed=0):
     cfg = CONFIGS[name][0]
@@ -34,7 +40,7 @@ def folders(tmp_path_factory):
 
 @pytest.fixture(scope="module")
 def expected(folders):
-    return {name: ru.plain_logits(folders[name], prompts_for(name)) for name in CONFIGS}
+    return {name: ru.Expected(folders[name], prompts_for(name)) for name in CONFIGS}
 
 
 def engine(folder, dtype, **kw):
@@ -44,17 +50,22 @@ def engine(folder, dtype, **kw):
 
 
 def compare(got, want, tol, what):
-    worst = 0.0
+    worst, left_out, total = 0.0, 0, 0
     for rid in want:
         assert got[rid].shape == want[rid].shape, (what, rid)
         assert torch.isfinite(got[rid]).all(), (what, rid)
-        err = ru.max_rel_err(got[rid], want[rid])
-        if err > tol:
-            diff = (got[rid] - want[rid]).abs().max(dim=1).values / want[rid].abs().max()
+        diff = (got[rid] - want[rid]).abs().max(dim=1).values / want[rid].abs().max()
+        total += diff.numel()
+        if "bfloat16" in what:
+            undecided = want.margins[rid] < BF16_ROUTER_MARGIN
+            left_out += int(undecided.sum())
+            diff = torch.where(undecided, torch.zeros_like(diff), diff)
+        if float(diff.max()) > tol:
             first = int((diff > tol).nonzero()[0])
-            raise AssertionError(f"{what}: request {rid} (length {want[rid].shape[0]}): relative error {err:.3e} > {tol}; "
-                                 f"first wrong position {first}")
-        worst = max(worst, err)
+            raise AssertionError(f"{what}: request {rid} (length {want[rid].shape[0]}): relative error "
+                                 f"{float(diff.max()):.3e} > {tol}; first wrong position {first}")
+        worst = max(worst, float(diff.max()))
+    assert left_out <= 0.1 * total, f"{what}: {left_out} of {total} positions have undecided routing"
     return worst
 
 
@@ -88,7 +99,7 @@ def test_portions_of_changing_size(folders, expected, name, dtype, page_size):
 @pytest.mark.parametrize("page_size", [4, 16])
 def test_mixed_batches_reuse_pages(folders, name, dtype, page_size):
     prompts = prompts_for(name, n=9, seed=3)
-    want = ru.plain_logits(folders[name], prompts)
+    want = ru.Expected(folders[name], prompts)
     # four live requests of at most 96 tokens: exactly enough pages, so that every
     # page a finished request gives back is taken again by a later one
     eng = engine(folders[name], dtype, page_size=page_size, n_pages=4 * (96 // page_size), max_slots=4)
