@@ -23,6 +23,7 @@ _ERRORS = {
     -2: "a size outside what the kernel handles",
     -3: "pointer or stride not aligned as the kernel requires",
     -4: "a bounded wait inside a kernel ran out",
+    -5: "the request needs more scratch than the library's fixed array holds",
 }
 
 
