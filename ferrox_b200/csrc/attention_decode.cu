@@ -21,6 +21,7 @@
 // crates/ferrox-core/src/attention.rs:146-175; window :484-524; pages :572-610.
 #include "common.cuh"
 #include "api.h"
+#include "no_alloc.h"
 
 namespace {
 
@@ -281,6 +282,63 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
     if (n_tokens <= 0) return FX_OK;
     if (split_len <= 0 || n_splits <= 0) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FX_F32)
+        return run<float>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
+                          out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
+                          split_len, n_splits, s);
+    if (dtype == FX_BF16)
+        return run<bf16>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
+                         out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
+                         split_len, n_splits, s);
+    return FX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in no_alloc.h; no counterpart in the
+// reference).  Same computation as fx_decode_attention, but the per-split partial
+// results live in the fixed array below instead of caller-provided scratch memory.
+//
+// The array is part of the library's image: every GPU on which the library is used
+// holds FX_NOALLOC_SCRATCH_FLOATS * 4 bytes from the moment the library is loaded
+// there until the process exits.  Host code cannot use the array's name as a
+// pointer (on the host it names a stand-in, not device memory), so the device
+// address is asked for once per device with cudaGetSymbolAddress and kept.
+static __device__ __align__(256) float fx_noalloc_scratch[FX_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int FX_MAX_DEVICES = 64;
+float* g_noalloc_ptr[FX_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+extern "C" int fx_decode_attention_noalloc(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
+                                           const int* block_table, int table_width, int page_size,
+                                           const int* positions, const int* token_seq, const int* seq_slot, void* out,
+                                           long ldo, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                           int window, float scale, int split_len, int n_splits, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (split_len <= 0 || n_splits <= 0 || n_heads <= 0 || head_dim <= 0) return FX_ERR_SIZE;
+    // partial sums [tokens, heads, splits, head_dim] followed by (max, sum) pairs [tokens, heads, splits, 2]
+    const long slots = (long)n_tokens * n_heads * n_splits;
+    const long need = slots * head_dim + slots * 2;
+    if (need > (long)FX_NOALLOC_SCRATCH_FLOATS) return FX_ERR_SCRATCH;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= FX_MAX_DEVICES) return FX_ERR_SIZE;
+    if (g_noalloc_ptr[dev] == nullptr) {
+        // first call on this device (it is the current one): resolve the array's device address
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, fx_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (p == nullptr) return FX_ERR_SIZE;
+        g_noalloc_ptr[dev] = p;
+    }
+    float* part_acc = g_noalloc_ptr[dev];
+    float* part_ml = part_acc + slots * head_dim;   // offset is a multiple of head_dim floats; only 4-byte access
+    cudaStream_t s = (cudaStream_t)stream;
+    // Every slot that the merge reads is written by the split kernel of the same call
+    // (empty splits write max = -inf, sum = 0), so nothing has to be cleared first.
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
                           out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
