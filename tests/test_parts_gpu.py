@@ -1,0 +1,298 @@
+"""Each part alone against the plain implementation's function for it, and the
+framework's openness: a toy mixer with per-request state, a toy architecture and a
+schedule that runs a layer twice are defined HERE, registered, built, loaded from a
+random model folder and stepped, with no change to the framework's files."""
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_qwen2moe as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = {"float32": (torch.float32, 3e-5), "bfloat16": (torch.bfloat16, 2e-2)}
+
+
+def rel(got, want):
+    return float((got.float().cpu() - want.float().cpu()).abs().max() / want.float().abs().max().clamp_min(1e-30))
+
+
+def load_part(spec, tensors, dtype):
+    from ferrox_b200.parts.base import Runtime, build_part
+    from ferrox_b200.parts import build  # noqa: F401  (registers the built-in parts)
+    from ferrox_b200.weights import loader as wl
+
+    part = build_part(spec)
+    rt = Runtime(torch.device(DEV), dtype)
+    part.load(wl.from_dict(tensors, part.tensor_decls(), DEV, dtype), rt)
+    return part, rt
+
+
+def random_tensors(part_spec, seed=0, std=0.1):
+    from ferrox_b200.parts.base import build_part
+    from ferrox_b200.parts import build  # noqa: F401
+    from ferrox_b200.weights.random_init import random_tensors as rt
+
+    return dict(rt(build_part(part_spec).tensor_decls(), seed, torch.bfloat16, std, "around_one"))
+
+
+# ------------------------------------------------------------------ parts alone
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_norm_alone(dtype):
+    from ferrox_b200.parts.specs import NormSpec
+
+    dt, tol = DTYPES[dtype]
+    spec = NormSpec(size=80, eps=3e-6, prefix="n.")
+    w = random_tensors(spec)
+    part, rt = load_part(spec, w, dt)
+    h = torch.randn(7, 80, generator=torch.Generator().manual_seed(0)) * 4
+    got = part.forward(h.to(DEV))
+    assert got.dtype == dt and rel(got, plain.rms_norm(h, w["n.weight"].float(), 3e-6)) < tol
+    rows = torch.tensor([6, 1], dtype=torch.int32, device=DEV)
+    assert torch.equal(part.forward(h.to(DEV), rows=rows), got[[6, 1]])
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_mlp_alone(dtype):
+    from ferrox_b200.parts.specs import DenseMlpSpec
+
+    dt, tol = DTYPES[dtype]
+    spec = DenseMlpSpec(hidden=96, intermediate=160, prefix="m.")
+    w = random_tensors(spec)
+    part, rt = load_part(spec, w, dt)
+    for T in (3, 70):  # the decode-sized and the prompt-sized kernels
+        x = torch.randn(T, 96, generator=torch.Generator().manual_seed(T))
+        h = torch.randn(T, 96, generator=torch.Generator().manual_seed(T + 1))
+        xd = x.to(dt)
+        want = h + plain.swiglu_mlp(xd.float(), w["m.gate_proj.weight"].float(), w["m.up_proj.weight"].float(),
+                                    w["m.down_proj.weight"].float())
+        hd = h.to(DEV)
+        part.forward_add(xd.to(DEV), hd, _FakeBatch())
+        assert rel(hd, want) < tol
+
+
+class _FakeBatch:
+    def __init__(self):
+        from ferrox_b200.kernels import ops
+
+        self.stream = ops.stream_ptr()
+        self.status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("renorm,gate,shared", [(False, True, 64), (True, False, 64), (True, True, 0)])
+def test_moe_alone(dtype, renorm, gate, shared):
+    from ferrox_b200.parts.specs import MoeSpec
+
+    dt, tol = DTYPES[dtype]
+    spec = MoeSpec(hidden=64, n_experts=6, top_k=2, expert_intermediate=32, shared_intermediate=shared,
+                   norm_topk_prob=renorm, shared_gate=gate, prefix="model.layers.0.mlp.")
+    w = random_tensors(spec, std=0.3)
+    if not gate:
+        w = {k: v for k, v in w.items() if "shared_expert_gate" not in k}
+    part, rt = load_part(spec, w, dt)
+    cfg = dict(num_experts_per_tok=2, norm_topk_prob=renorm)
+    wf = {k: v.float() for k, v in w.items()}
+    for T in (5, 90):
+        x = (torch.randn(T, 64, generator=torch.Generator().manual_seed(T))).to(dt)
+        # keep tokens whose routing is decided beyond rounding
+        lg = x.float() @ wf["model.layers.0.mlp.gate.weight"].T
+        top = torch.topk(lg, 3, dim=-1).values
+        keep = (top[:, 1] - top[:, 2]) > 0.05 * lg.abs().max()
+        h = torch.randn(T, 64, generator=torch.Generator().manual_seed(T + 1))
+        want = h + plain.moe_block(x.float(), wf, cfg, 0)
+        hd = h.to(DEV)
+        part.forward_add(x.to(DEV), hd, _FakeBatch())
+        assert int(keep.sum()) > T // 2
+        assert rel(hd.cpu()[keep], want[keep]) < tol
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("window,bias", [(None, True), (9, False)])
+def test_attention_alone_in_two_steps(dtype, window, bias):
+    """A prompt portion, then a second portion and a decoded token of another request in one batch."""
+    from ferrox_b200.parts.specs import AttentionSpec, PositionSpec
+
+    dt, tol = DTYPES[dtype]
+    nh, nkv, d, H = 6, 2, 32, 80
+    spec = AttentionSpec(hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=d, qkv_bias=bias,
+                         position=PositionSpec(rotary_dim=d, theta=50000.0), window=window,
+                         prefix="model.layers.0.self_attn.")
+    w = random_tensors(spec, std=0.2)
+    part, rt = load_part(spec, w, dt)
+    from ferrox_b200.cache.manager import CacheManager
+    from ferrox_b200.engine.batch import StepEntry, flatten
+    from ferrox_b200.kernels import ops
+
+    cm = CacheManager([part.cache_spec()], page_size=4, n_pages=64, max_slots=4, max_positions=256, device=DEV, dtype=dt)
+    cfg = dict(num_attention_heads=nh, num_key_value_heads=nkv, head_dim=d, hidden_size=H, rope_theta=50000.0,
+               use_sliding_window=window is not None, sliding_window=window, max_window_layers=0, num_hidden_layers=1)
+    wf = {k: v.float() for k, v in w.items()}
+    g = torch.Generator().manual_seed(3)
+    xa = torch.randn(30, H, generator=g).to(dt)
+    xb = torch.randn(21, H, generator=g).to(dt)
+    want_a = plain.attention_block(xa.float(), wf, cfg, 0, torch.arange(30))
+    want_b = plain.attention_block(xb.float(), wf, cfg, 0, torch.arange(21))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    sa, sb = cm.open_request(), cm.open_request()
+
+    def run(portions):
+        entries = []
+        for slot, x0, x1 in portions:
+            e = StepEntry(slot, list(range(x1 - x0)))
+            e.start = cm.seq_len[slot]
+            assert cm.reserve(slot, e.start + x1 - x0)
+            entries.append(e)
+        cm.sync_tables()
+        batch = flatten(entries, DEV, status, ops.stream_ptr())
+        xs = torch.cat([(xa if slot == sa else xb)[x0:x1] for slot, x0, x1 in portions]).to(DEV)
+        h = torch.zeros(xs.shape[0], H, dtype=torch.float32, device=DEV)
+        part.forward_add(xs, h, batch, cm.layer_cache(0))
+        for e in entries:
+            cm.commit(e.slot, e.start + len(e.tokens))
+        return h.cpu()
+
+    h1 = run([(sa, 0, 17), (sb, 0, 20)])
+    h2 = run([(sa, 17, 30), (sb, 20, 21)])
+    assert int(status) == 0
+    assert rel(h1[:17], want_a[:17]) < tol and rel(h1[17:], want_b[:20]) < tol
+    assert rel(h2[:13], want_a[17:]) < tol and rel(h2[13:], want_b[20:]) < tol
+
+
+# ------------------------------------------------------------------ toy parts and a toy architecture
+@dataclass(frozen=True)
+class RunningMeanSpec:
+    hidden: int
+    prefix: str
+    kind: str = "toy_running_mean"
+
+
+def _toy_classes():
+    from ferrox_b200.cache.specs import CacheSpec, StateSpec
+    from ferrox_b200.parts.base import Mixer
+    from ferrox_b200.weights.loader import TensorDecl
+
+    class RunningMean(Mixer):
+        """h += W . mean(x of this request so far).  Its state per request is the running
+        sum and the count, kept in the cache manager's slot for the request."""
+
+        def cache_spec(self):
+            return CacheSpec(state=StateSpec((self.spec.hidden + 1,), torch.float32))
+
+        def tensor_decls(self):
+            return [TensorDecl(self.spec.prefix + "mix.weight", (self.spec.hidden, self.spec.hidden))]
+
+        def load(self, src, rt):
+            super().load(src, rt)
+            self.w = src.get(self.spec.prefix + "mix.weight").float()
+
+        def forward_add(self, x, h, batch, cache):
+            t = 0
+            for e in batch.entries:
+                n = len(e.tokens)
+                st = cache.state[e.slot]
+                xs = x[t:t + n].float()
+                sums = st[:-1] + torch.cumsum(xs, dim=0)
+                counts = st[-1] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                h[t:t + n] += (sums / counts[:, None]) @ self.w.T
+                st[:-1] = sums[-1]
+                st[-1] = counts[-1]
+                t += n
+
+    return RunningMean
+
+
+TOY_ARCH = "ToyMixForCausalLM"
+
+
+def _register_toy():
+    from ferrox_b200 import register_architecture, register_part
+    from ferrox_b200.parts.specs import (AttentionSpec, BlockSpec, DenseMlpSpec, ModelSpec, NormSpec, PositionSpec,
+                                         ScheduleEntry)
+
+    register_part("toy_running_mean", _toy_classes(), replace=True)
+
+    def config_from_json(obj):
+        return dict(obj)
+
+    def model_spec(c):
+        H = c["hidden_size"]
+
+        def block(l, mixer):
+            p = f"model.layers.{l}."
+            return BlockSpec(norm1=NormSpec(H, 1e-5, p + "input_layernorm."), mixer=mixer,
+                             norm2=NormSpec(H, 1e-5, p + "post_attention_layernorm."),
+                             ffn=DenseMlpSpec(H, c["intermediate_size"], p + "mlp."))
+
+        attn = AttentionSpec(hidden=H, n_heads=2, n_kv_heads=1, head_dim=16, qkv_bias=False,
+                             position=PositionSpec(16, 10000.0), window=None, prefix="model.layers.1.self_attn.")
+        layers = (block(0, RunningMeanSpec(H, "model.layers.0.toy.")), block(1, attn))
+        # layer 0 (state), layer 1 (keys and values), then layer 1 AGAIN on a cache of its own
+        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(1, 2))
+        return ModelSpec(architecture=TOY_ARCH, vocab_size=c["vocab_size"], hidden=H, max_positions=64, layers=layers,
+                         schedule=schedule, final_norm=NormSpec(H, 1e-5, "model.norm."), head_name="lm_head.weight")
+
+    register_architecture(TOY_ARCH, config_from_json, model_spec, replace=True)
+
+
+def _toy_plain(cfg, w, tokens):
+    """The toy model, whole sequence, in plain torch."""
+    H = cfg["hidden_size"]
+    x = w["model.embed_tokens.weight"][torch.as_tensor(tokens)].clone()
+    pos = torch.arange(len(tokens))
+    acfg = dict(num_attention_heads=2, num_key_value_heads=1, head_dim=16, hidden_size=H, rope_theta=10000.0,
+                num_hidden_layers=2)
+
+    def mlp(h, l):
+        n = plain.rms_norm(h, w[f"model.layers.{l}.post_attention_layernorm.weight"], 1e-5)
+        return h + plain.dense_block(n, w, l)
+
+    n = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], 1e-5)
+    mean = torch.cumsum(n, 0) / torch.arange(1, len(tokens) + 1)[:, None]
+    x = mlp(x + mean @ w["model.layers.0.toy.mix.weight"].T, 0)
+    for _ in range(2):
+        n = plain.rms_norm(x, w["model.layers.1.input_layernorm.weight"], 1e-5)
+        x = mlp(x + plain.attention_block(n, w, acfg, 1, pos), 1)
+    return plain.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["lm_head.weight"].T
+
+
+def test_toy_mixer_with_state_and_a_layer_run_twice(tmp_path):
+    import ferrox_b200
+    from ferrox_b200 import Engine, StepEntry
+
+    _register_toy()
+    cfg = dict(architectures=[TOY_ARCH], hidden_size=48, intermediate_size=64, vocab_size=97)
+    folder = ferrox_b200.write_random_model(str(tmp_path / "toy"), cfg, seed=4, std=0.2, norm_init="around_one")
+    w = {k: v.float() for k, v in plain.read_safetensors(folder + "/model.safetensors").items()}
+    eng = Engine.from_folder(folder, dtype="float32", page_size=4, n_pages=24, max_slots=3)
+    assert eng.graphs is None  # a part written in Python is not captured in a CUDA graph
+    assert set(eng.cache.groups) == {None} and eng.cache.groups[None].caches == [1, 2]
+    assert eng.cache.layer_cache(0).k is None and eng.cache.layer_cache(0).state.shape == (3, 49)
+    g = torch.Generator().manual_seed(0)
+    seqs = {s: torch.randint(0, 97, (n,), generator=g).tolist() for s, n in (("a", 23), ("b", 9), ("c", 14))}
+    want = {s: _toy_plain(cfg, w, t) for s, t in seqs.items()}
+
+    def feed(slot, toks):
+        return StepEntry(slot, toks, want=list(range(len(toks))))
+
+    # a and b in mixed portions; then b ends and c takes over its slot (state zeroed, pages reused)
+    sa, sb = eng.open_request(), eng.open_request()
+    o1 = eng.step([feed(sa, seqs["a"][:10]), feed(sb, seqs["b"][:2])]).cpu()
+    o2 = eng.step([feed(sa, seqs["a"][10:11]), feed(sb, seqs["b"][2:])]).cpu()
+    eng.close_request(sb)
+    sc = eng.open_request()
+    assert sc == sb
+    o3 = eng.step([feed(sc, seqs["c"]), feed(sa, seqs["a"][11:])]).cpu()
+    got_a = torch.cat([o1[:10], o2[:1], o3[14:]])
+    got_b = torch.cat([o1[10:], o2[1:]])
+    got_c = o3[:14]
+    for got, s in ((got_a, "a"), (got_b, "b"), (got_c, "c")):
+        assert rel(got, want[s]) < 3e-5, s
+    eng.close_request(sa)
+    eng.close_request(sc)
+    eng.cache.check_invariants()
+    # generation works through the public entry point as well
+    out = eng.generate([seqs["b"]], max_new_tokens=4)[0]
+    assert out[0] == int(want["b"][-1].argmax())
