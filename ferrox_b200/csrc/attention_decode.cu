@@ -26,6 +26,7 @@
 namespace {
 
 constexpr int NTHREADS = 128;
+constexpr int STAGES = 4;    // buffers of the key/value ring
 constexpr int MAXQ = 8;      // query heads per block
 constexpr int MAX_D = 256;
 
@@ -77,6 +78,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int k_begin = max(lo, split * split_len);
     const int k_end = min(pos + 1, (split + 1) * split_len);
+    if (k_begin >= k_end) return;   // nothing of this range is visible: `merge` skips it by the same rule
     const int grp = threadIdx.x / LPK, ln = threadIdx.x % LPK;
 
     float qr[GQ][VPL][N], acc[GQ][VPL][N], m[GQ], l[GQ];
@@ -92,72 +94,128 @@ __global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
         }
     }
 
-    if (k_begin < k_end) {
+    // ---- stream the keys and values of this range through shared memory ------------
+    // Tiles of TK keys arrive by cp.async into a ring of STAGES buffers, so that the
+    // bytes in flight do not depend on registers; a position without a page, or past
+    // the range, is zero-filled and flagged.  Group g then takes keys g, g + GROUPS, ...
+    // of each tile, in key order.
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    const int row_bytes = head_dim * (int)sizeof(T);
+    const int TK = row_bytes <= 256 ? 32 : (row_bytes <= 512 ? 16 : 8);   // keys per tile (multiple of GROUPS)
+    const int stage_bytes = 2 * TK * row_bytes + 128;                     // K rows, V rows, validity flags
+    const int n_tiles = k_begin < k_end ? (k_end - k_begin + TK - 1) / TK : 0;
+    constexpr int KB = (GQ * VPL <= 2) ? 4 : (GQ * VPL <= 4 ? 2 : 1);    // keys of a group scored together
+    if (n_tiles > 0) {
         const int* table = block_table + (long)seq_slot[token_seq[tkn]] * table_width;
         const long head_stride = (long)page_size * head_dim;
-        // the loop bounds are the same for every thread, so the group-wide shuffles
-        // below are always executed by whole warps
-        // U keys per group and pass: their loads are issued together, so that several
-        // are in flight per lane; the running (m, l, acc) then takes them in key order
-        constexpr int U = (GQ * VPL <= 2) ? 4 : 2;
-        for (int kb = k_begin; kb < k_end; kb += GROUPS * U) {
-            bool valid[U];
-            long base[U];
-            float kk[U][VPL][N], vv[U][VPL][N];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int key = kb + u * GROUPS + grp;
-                valid[u] = key < k_end;
-                const int page = valid[u] ? table[key / page_size] : -1;
-                valid[u] = valid[u] && page >= 0;  // a position without a page is skipped, never dereferenced
-                base[u] = valid[u] ? ((long)page * n_kv_heads + kvh) * head_stride + (long)(key % page_size) * head_dim : 0;
+        const int cpk = row_bytes / 16;                                   // 16-byte chunks per key row
+        const uint32_t smem_u = (uint32_t)__cvta_generic_to_shared(dyn_smem);
+        auto issue = [&](int tile) {
+            if (tile < n_tiles) {
+                uint8_t* st = dyn_smem + (tile % STAGES) * stage_bytes;
+                const uint32_t su = smem_u + (tile % STAGES) * stage_bytes;
+                for (int c = threadIdx.x; c < TK * cpk; c += NTHREADS) {
+                    const int r = c / cpk, ch = c - r * cpk;
+                    const int key = k_begin + tile * TK + r;
+                    int page = -1;
+                    if (key < k_end) page = table[key / page_size];
+                    const bool ok = page >= 0;
+                    const long base = ok ? ((long)page * n_kv_heads + kvh) * head_stride + (long)(key % page_size) * head_dim : 0;
+                    const uint32_t dst = su + r * row_bytes + ch * 16;
+                    const uint8_t* ksrc = reinterpret_cast<const uint8_t*>(k_pages + base) + ch * 16;
+                    const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(v_pages + base) + ch * 16;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(ksrc), "r"(ok ? 16 : 0) : "memory");
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + TK * row_bytes), "l"(vsrc), "r"(ok ? 16 : 0) : "memory");
+                    if (ch == 0) st[2 * TK * row_bytes + r] = ok ? 1 : 0;
+                }
             }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        for (int s = 0; s < STAGES - 1; ++s) issue(s);
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+            __syncthreads();                 // tile `tile` has landed; everyone is done with tile - 1
+            issue(tile + STAGES - 1);        // refills the buffer that tile - 1 used
+            const uint8_t* st = dyn_smem + (tile % STAGES) * stage_bytes;
+            const T* ks = reinterpret_cast<const T*>(st);
+            const T* vs = reinterpret_cast<const T*>(st + TK * row_bytes);
+            const uint8_t* flags = st + 2 * TK * row_bytes;
+            // A group takes KPG = TK / GROUPS keys of the tile (same count for every thread, so
+            // the group-wide shuffles are executed by whole warps).  Their scores are
+            // independent, so they are computed together; then ONE update of (m, l, acc)
+            // takes them in key order.
+            for (int r0 = 0; r0 < TK; r0 += GROUPS * KB) {
+                float sc[KB][GQ];
+                bool valid[KB];
 #pragma unroll
-            for (int u = 0; u < U; ++u)
+                for (int u = 0; u < KB; ++u) {
+                    const int r = r0 + u * GROUPS + grp;
+                    valid[u] = r < TK && flags[r] != 0;
+                    float kv[VPL][N];
 #pragma unroll
-                for (int v = 0; v < VPL; ++v) {
-                    const int e = (v * LPK + ln) * N;
+                    for (int h = 0; h < GQ; ++h) sc[u][h] = 0.f;
 #pragma unroll
-                    for (int i = 0; i < N; ++i) { kk[u][v][i] = 0.f; vv[u][v][i] = 0.f; }
-                    if (valid[u] && e < head_dim) {
-                        Vec<T>::load(k_pages + base[u] + e, kk[u][v]);
-                        Vec<T>::load(v_pages + base[u] + e, vv[u][v]);
+                    for (int v = 0; v < VPL; ++v) {
+                        const int e = (v * LPK + ln) * N;
+                        if (r < TK && e < head_dim) {
+                            Vec<T>::load(ks + (long)r * head_dim + e, kv[v]);
+#pragma unroll
+                            for (int h = 0; h < GQ; ++h)
+#pragma unroll
+                                for (int i = 0; i < N; ++i) sc[u][h] = fmaf(qr[h][v][i], kv[v][i], sc[u][h]);
+                        }
                     }
                 }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                float s[GQ];
+                for (int u = 0; u < KB; ++u)
+#pragma unroll
+                    for (int h = 0; h < GQ; ++h) {
+#pragma unroll
+                        for (int o = LPK / 2; o > 0; o >>= 1) sc[u][h] += __shfl_xor_sync(0xffffffffu, sc[u][h], o);
+                        sc[u][h] = valid[u] ? sc[u][h] * scale : -INFINITY;
+                    }
 #pragma unroll
                 for (int h = 0; h < GQ; ++h) {
-                    s[h] = 0.f;
+                    float m_new = m[h];
 #pragma unroll
-                    for (int v = 0; v < VPL; ++v)
+                    for (int u = 0; u < KB; ++u) m_new = fmaxf(m_new, sc[u][h]);
+                    if (m_new == -INFINITY) continue;              // nothing visible yet for this head
+                    const float alpha = fx_exp<T>(m[h] - m_new);  // m = -inf at first: exp(-inf) = 0
+                    float p[KB];
+                    float psum = 0.f;
 #pragma unroll
-                        for (int i = 0; i < N; ++i) s[h] = fmaf(qr[h][v][i], kk[u][v][i], s[h]);
-#pragma unroll
-                    for (int o = LPK / 2; o > 0; o >>= 1) s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);
-                }
-                if (!valid[u]) continue;
-#pragma unroll
-                for (int h = 0; h < GQ; ++h) {
-                    const float sc = s[h] * scale;
-                    const float m_new = fmaxf(m[h], sc);
-                    const float alpha = fx_exp<T>(m[h] - m_new);   // m = -inf at first: exp(-inf) = 0
-                    const float p = fx_exp<T>(sc - m_new);
-                    l[h] = l[h] * alpha + p;
-#pragma unroll
-                    for (int v = 0; v < VPL; ++v)
-#pragma unroll
-                        for (int i = 0; i < N; ++i) acc[h][v][i] = acc[h][v][i] * alpha + p * vv[u][v][i];
+                    for (int u = 0; u < KB; ++u) { p[u] = fx_exp<T>(sc[u][h] - m_new); psum += p[u]; }
+                    l[h] = l[h] * alpha + psum;
                     m[h] = m_new;
+#pragma unroll
+                    for (int v = 0; v < VPL; ++v)
+#pragma unroll
+                        for (int i = 0; i < N; ++i) acc[h][v][i] *= alpha;
+#pragma unroll
+                    for (int u = 0; u < KB; ++u) {
+                        const int r = r0 + u * GROUPS + grp;
+                        if (!valid[u]) continue;
+#pragma unroll
+                        for (int v = 0; v < VPL; ++v) {
+                            const int e = (v * LPK + ln) * N;
+                            if (e < head_dim) {
+                                float vv[N];
+                                Vec<T>::load(vs + (long)r * head_dim + e, vv);
+#pragma unroll
+                                for (int i = 0; i < N; ++i) acc[h][v][i] = fmaf(p[u], vv[i], acc[h][v][i]);
+                            }
+                        }
+                    }
                 }
             }
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();   // the ring is reused below for the merge
     }
 
     // merge the groups of this block, in group order
     __shared__ float sm_m[GROUPS][GQ], sm_l[GROUPS][GQ];
-    extern __shared__ float sm_acc[];   // [GROUPS][GQ][head_dim_padded]
+    float* sm_acc = reinterpret_cast<float*>(dyn_smem);   // [GROUPS][GQ][head_dim_padded]
     const int dpad = VPL * LPK * N;
     if (ln == 0) {
 #pragma unroll
@@ -191,15 +249,20 @@ __global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
 
 template <typename T>
 __global__ void merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                             T* __restrict__ out, long ldo, int n_heads, int head_dim, int n_splits)
+                             const int* __restrict__ positions, T* __restrict__ out, long ldo, int n_heads,
+                             int head_dim, int n_splits, int split_len, int window)
 {
     const int tkn = blockIdx.x, h = blockIdx.y;
     const long base = ((long)tkn * n_heads + h) * n_splits;
+    // the splits that hold visible keys of this token (the others were not written)
+    const int pos = positions[tkn];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int s_lo = lo / split_len, s_hi = min(n_splits - 1, pos / split_len);
     float mm = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
     for (int e = threadIdx.x; e < head_dim; e += blockDim.x) {
         float ll = 0.f, a = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
+        for (int s = s_lo; s <= s_hi; ++s) {
             const float ms = part_ml[(base + s) * 2];
             if (ms == -INFINITY) continue;
             const float w = fx_exp<T>(ms - mm);
@@ -216,7 +279,11 @@ int launch_one(dim3 grid, cudaStream_t s, const T* q, long ldq, const T* k, cons
                int window, float scale, int split_len, int n_splits)
 {
     auto kern = decode_split_kernel<T, LPK, VPL, GQ>;
-    const size_t smem = sizeof(float) * (NTHREADS / LPK) * GQ * (VPL * LPK * Vec<T>::N);
+    const size_t merge_bytes = sizeof(float) * (NTHREADS / LPK) * GQ * (VPL * LPK * Vec<T>::N);
+    const int row_bytes = d * (int)sizeof(T);
+    const int tk = row_bytes <= 256 ? 32 : (row_bytes <= 512 ? 16 : 8);
+    const size_t ring_bytes = (size_t)STAGES * (2 * tk * row_bytes + 128);
+    const size_t smem = merge_bytes > ring_bytes ? merge_bytes : ring_bytes;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -266,7 +333,8 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, const
     else { FX_GO(16, 4); }
 #undef FX_GO
     if (rc != FX_OK) return rc;
-    merge_kernel<T><<<dim3(n_tokens, n_heads), 64, 0, s>>>(part_acc, part_ml, (T*)out, ldo, n_heads, head_dim, n_splits);
+    merge_kernel<T><<<dim3(n_tokens, n_heads), 64, 0, s>>>(part_acc, part_ml, positions, (T*)out, ldo, n_heads, head_dim,
+                                                          n_splits, split_len, window);
     return fx_launch_status();
 }
 

@@ -53,13 +53,16 @@ struct SkinnyArgs {
     const int* active_groups;      // grouped form: expert of each grid.y slot, -1 = none
 };
 
-template <int NT, bool GATED>
+// MODE 0: 16 features per block.  MODE 1 (gated): 16 gate rows and their 16 up rows, out = silu(gate) * up.
+// MODE 2: 32 features per block (two tiles of rows), for wide matrices: half as many, fatter blocks.
+template <int NT, int MODE>
 __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
 {
+    constexpr bool GATED = MODE != 0;   // a second set of 16 rows is streamed beside the first
     __shared__ float red[WARPS][GATED ? 2 : 1][NT][16][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16;
+    const int n0 = blockIdx.x * (MODE == 2 ? 32 : 16);
 
     int row_begin = 0, row_end = a.n_tokens;
     const bf16* W = a.W;
@@ -74,8 +77,15 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
     const int r0 = min(n0 + g, a.N - 1), r1 = min(n0 + g + 8, a.N - 1);
     const bf16* w0 = W + (long)r0 * a.ldw + t * 8;
     const bf16* w1 = W + (long)r1 * a.ldw + t * 8;
-    const bf16* u0 = GATED ? w0 + (long)a.gate_up_offset * a.ldw : nullptr;
-    const bf16* u1 = GATED ? w1 + (long)a.gate_up_offset * a.ldw : nullptr;
+    const bf16* u0 = nullptr;
+    const bf16* u1 = nullptr;
+    if (MODE == 1) {
+        u0 = w0 + (long)a.gate_up_offset * a.ldw;
+        u1 = w1 + (long)a.gate_up_offset * a.ldw;
+    } else if (MODE == 2) {
+        u0 = W + (long)min(n0 + 16 + g, a.N - 1) * a.ldw + t * 8;
+        u1 = W + (long)min(n0 + 24 + g, a.N - 1) * a.ldw + t * 8;
+    }
     const int n_chunks = a.K >> 5;
 
     for (int tok0 = row_begin; tok0 < row_end; tok0 += 8 * NT) {
@@ -94,12 +104,15 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.f;
 
+        // Chunk c of K belongs to warp c % 8, so that the 8 warps read 512 contiguous
+        // bytes of a row together and share the chunks evenly whatever K is; a warp
+        // issues the loads of UNROLL of its chunks before it uses the first.
         constexpr int UNROLL = (GATED ? 4 : 8) / (NT > 2 ? 2 : 1);
-        for (int c0 = warp * UNROLL; c0 < n_chunks; c0 += WARPS * UNROLL) {
+        for (int i0 = 0; warp + WARPS * i0 < n_chunks; i0 += UNROLL) {
             uint4 wa[UNROLL], wb[UNROLL], ua[UNROLL], ub[UNROLL];
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const int c = c0 + u;
+                const int c = warp + WARPS * (i0 + u);
                 if (c < n_chunks) {
                     wa[u] = ldg_stream(w0 + c * 32);
                     wb[u] = ldg_stream(w1 + c * 32);
@@ -108,7 +121,7 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
             }
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const int c = c0 + u;
+                const int c = warp + WARPS * (i0 + u);
                 if (c >= n_chunks) break;
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
@@ -148,24 +161,31 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
                 if (GATED) up += red[w][1][j][f][tn];
             }
             if (a.bias) v += load_any(a.bias, a.bias_dtype, n);
-            if (GATED) v = v / (1.0f + expf(-v)) * up;
-            if (a.c_dtype == FX_F32) {
-                float* c = reinterpret_cast<float*>(a.C) + (long)r * a.ldc + n;
-                *c = a.accumulate ? *c + v : v;
-            } else {
-                bf16* c = reinterpret_cast<bf16*>(a.C) + (long)r * a.ldc + n;
-                *c = __float2bfloat16_rn(a.accumulate ? __bfloat162float(*c) + v : v);
+            if (MODE == 1) v = v / (1.0f + expf(-v)) * up;
+            auto store = [&](int col, float val) {
+                if (a.c_dtype == FX_F32) {
+                    float* c = reinterpret_cast<float*>(a.C) + (long)r * a.ldc + col;
+                    *c = a.accumulate ? *c + val : val;
+                } else {
+                    bf16* c = reinterpret_cast<bf16*>(a.C) + (long)r * a.ldc + col;
+                    *c = __float2bfloat16_rn(a.accumulate ? __bfloat162float(*c) + val : val);
+                }
+            };
+            store(n, v);
+            if (MODE == 2 && n + 16 < a.N) {
+                if (a.bias) up += load_any(a.bias, a.bias_dtype, n + 16);
+                store(n + 16, up);
             }
         }
     }
 }
 
-template <bool GATED>
+template <int MODE>
 int launch_nt(const SkinnyArgs& a, int max_tokens_per_group, dim3 grid, cudaStream_t s)
 {
-    if (max_tokens_per_group <= 8) skinny_kernel<1, GATED><<<grid, NTHREADS, 0, s>>>(a);
-    else if (max_tokens_per_group <= 16) skinny_kernel<2, GATED><<<grid, NTHREADS, 0, s>>>(a);
-    else skinny_kernel<4, GATED><<<grid, NTHREADS, 0, s>>>(a);
+    if (max_tokens_per_group <= 8) skinny_kernel<1, MODE><<<grid, NTHREADS, 0, s>>>(a);
+    else if (max_tokens_per_group <= 16) skinny_kernel<2, MODE><<<grid, NTHREADS, 0, s>>>(a);
+    else skinny_kernel<4, MODE><<<grid, NTHREADS, 0, s>>>(a);
     return fx_launch_status();
 }
 
@@ -193,9 +213,13 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.n_tokens = n_tokens; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset;
     a.group_offsets = group_offsets; a.active_groups = active_groups;
-    dim3 grid((unsigned)fx_cdiv(N, 16), group_offsets ? n_slots : 1);
+    const int slots = group_offsets ? n_slots : 1;
+    // wide matrices: 32 features per block, so that half as many blocks pay the start-up latency
+    const bool two_tiles = !gated && fx_cdiv(N, 32) * slots >= 2 * 148;
+    dim3 grid((unsigned)fx_cdiv(N, two_tiles ? 32 : 16), slots);
     if (grid.y > 65535u) return FX_ERR_SIZE;
     const int hint = group_offsets ? tokens_hint : n_tokens;
     cudaStream_t s = (cudaStream_t)stream;
-    return gated ? launch_nt<true>(a, hint, grid, s) : launch_nt<false>(a, hint, grid, s);
+    if (gated) return launch_nt<1>(a, hint, grid, s);
+    return two_tiles ? launch_nt<2>(a, hint, grid, s) : launch_nt<0>(a, hint, grid, s);
 }

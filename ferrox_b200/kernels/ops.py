@@ -273,7 +273,7 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
 def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int):
     """(split_len, n_splits) for :func:`decode_attention`: enough blocks to fill the
     GPU, as a function of the step's size and the context limit only."""
-    target = 148 * 16
+    target = 148 * 6
     want = max(1, -(-target // max(1, n_tokens * n_kv_blocks)))
     split_len = max(64, -(-max_positions // want))
     split_len = -(-split_len // 64) * 64

@@ -73,7 +73,7 @@ def test_gemm_grouped_with_gather(dtype):
 
 
 @pytest.mark.parametrize("T", [1, 3, 8, 9, 17, 40, 64])
-@pytest.mark.parametrize("N,K", [(16, 32), (60, 64), (1, 96), (200, 2048), (33, 160)])
+@pytest.mark.parametrize("N,K", [(16, 32), (60, 64), (1, 96), (200, 2048), (33, 160), (9493, 64)])
 def test_gemm_skinny(T, N, K):
     o = ops()
     x, w, bias = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1), rnd(N)
