@@ -11,6 +11,9 @@ int fx_gemm(const void* A, int a_dtype, long lda, const int* a_rows, const void*
             const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K,
             const int* group_offsets, int n_groups, long w_group_stride, void* stream);
 
+// Programmatic dependent launch of the short kernels on (1, default) or off (0); returns the old setting.
+int fx_set_pdl(int on);
+
 int fx_embed(const void* table, int dtype, const int* ids, float* out, int n_tokens, int hidden, int vocab,
              int* status, void* stream);
 int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, float eps, void* out, int out_dtype,

@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
 {
     constexpr int N = Vec<T>::N;
     constexpr int GROUPS = NTHREADS / LPK;
+    fx_pdl_wait();
     const int group_size = n_heads / n_kv_heads;
     const int chunks = (group_size + GQ - 1) / GQ;
     const int kvh = blockIdx.x / chunks;
@@ -252,6 +253,7 @@ __global__ void merge_kernel(const float* __restrict__ part_acc, const float* __
                              const int* __restrict__ positions, T* __restrict__ out, long ldo, int n_heads,
                              int head_dim, int n_splits, int split_len, int window)
 {
+    fx_pdl_wait();
     const int tkn = blockIdx.x, h = blockIdx.y;
     const long base = ((long)tkn * n_heads + h) * n_splits;
     // the splits that hold visible keys of this token (the others were not written)
@@ -288,7 +290,7 @@ int launch_one(dim3 grid, cudaStream_t s, const T* q, long ldq, const T* k, cons
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kern<<<grid, NTHREADS, smem, s>>>(q, ldq, k, v, bt, tw, ps, pos, tseq, sslot, pa, pm, nh, nkv, d, window, scale,
+    fx_launch_pdl(kern, grid, NTHREADS, smem, s, q, ldq, k, v, bt, tw, ps, pos, tseq, sslot, pa, pm, nh, nkv, d, window, scale,
                                       split_len, n_splits);
     return fx_launch_status();
 }
@@ -333,7 +335,7 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, const
     else { FX_GO(16, 4); }
 #undef FX_GO
     if (rc != FX_OK) return rc;
-    merge_kernel<T><<<dim3(n_tokens, n_heads), 64, 0, s>>>(part_acc, part_ml, positions, (T*)out, ldo, n_heads, head_dim,
+    fx_launch_pdl(merge_kernel<T>, dim3(n_tokens, n_heads), 64, 0, s, part_acc, part_ml, positions, (T*)out, ldo, n_heads, head_dim,
                                                           n_splits, split_len, window);
     return fx_launch_status();
 }

@@ -65,6 +65,35 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     return scratch[32];
 }
 
+// Programmatic dependent launch.  A kernel launched with fx_launch_pdl may be set up
+// on the GPU while the kernel before it on the stream is still running; it must
+// call fx_pdl_wait() before it touches anything that kernel wrote (here: first
+// thing), which also lets the kernel after it start its own set-up.  Launch
+// latencies of a chain of short kernels then overlap instead of adding up.
+__device__ __forceinline__ void fx_pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// fx_set_pdl(0) (elementwise.cu) makes fx_launch_pdl launch without the attribute; for measurements.
+extern int g_fx_pdl_enabled;
+
+template <typename... KArgs, typename... Args>
+static inline void fx_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_fx_pdl_enabled ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface through cudaGetLastError
+}
+
 static inline int fx_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FX_OK : (int)e;

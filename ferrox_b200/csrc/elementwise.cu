@@ -4,6 +4,15 @@
 #include "common.cuh"
 #include "api.h"
 
+int g_fx_pdl_enabled = 1;
+
+extern "C" int fx_set_pdl(int on)
+{
+    const int was = g_fx_pdl_enabled;
+    g_fx_pdl_enabled = on ? 1 : 0;
+    return was;
+}
+
 namespace {
 
 // ---------------------------------------------------------------------------
@@ -14,6 +23,7 @@ template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int hidden, int vocab, int* __restrict__ status)
 {
+    fx_pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -34,6 +44,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
                                OT* __restrict__ out, int hidden)
 {
     __shared__ float scratch[33];
+    fx_pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (long)(rows ? rows[r] : r) * hidden;
     float ss = 0.f;
@@ -81,6 +92,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __
                                      int n_heads, int n_kv_heads, int head_dim, int write_cache,
                                      int* __restrict__ status)
 {
+    fx_pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     T* row = qkv + (long)t * ld;
@@ -126,6 +138,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int n_tokens,
                                   int half, float* __restrict__ cos_sin)
 {
+    fx_pdl_wait();
     const long n = (long)n_tokens * half;
     for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < n; idx += (long)gridDim.x * blockDim.x) {
         const int t = (int)(idx / half), i = (int)(idx - (long)t * half);
@@ -148,6 +161,7 @@ __global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ 
                                    const T* __restrict__ shared, const float* __restrict__ shared_gate_logit,
                                    int hidden)
 {
+    fx_pdl_wait();
     const int t = blockIdx.x;
     float g = 1.f;
     if (shared && shared_gate_logit) g = 1.0f / (1.0f + expf(-shared_gate_logit[t]));
@@ -197,8 +211,8 @@ extern "C" int fx_embed(const void* table, int dtype, const int* ids, float* out
     if (n_tokens <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = threads_for(hidden > 256 ? 256 : hidden);
-    if (dtype == FX_F32) embed_kernel<float><<<n_tokens, nt, 0, s>>>((const float*)table, ids, out, hidden, vocab, status);
-    else if (dtype == FX_BF16) embed_kernel<bf16><<<n_tokens, nt, 0, s>>>((const bf16*)table, ids, out, hidden, vocab, status);
+    if (dtype == FX_F32) fx_launch_pdl(embed_kernel<float>, n_tokens, nt, 0, s, (const float*)table, ids, out, hidden, vocab, status);
+    else if (dtype == FX_BF16) fx_launch_pdl(embed_kernel<bf16>, n_tokens, nt, 0, s, (const bf16*)table, ids, out, hidden, vocab, status);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
@@ -209,8 +223,8 @@ extern "C" int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_
     if (n_rows <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = threads_for(hidden / 4 > 32 ? hidden / 4 : 32);
-    if (out_dtype == FX_F32) rmsnorm_kernel<float><<<n_rows, nt, 0, s>>>(x, rows, w, w_dtype, eps, (float*)out, hidden);
-    else if (out_dtype == FX_BF16) rmsnorm_kernel<bf16><<<n_rows, nt, 0, s>>>(x, rows, w, w_dtype, eps, (bf16*)out, hidden);
+    if (out_dtype == FX_F32) fx_launch_pdl(rmsnorm_kernel<float>, n_rows, nt, 0, s, x, rows, w, w_dtype, eps, (float*)out, hidden);
+    else if (out_dtype == FX_BF16) fx_launch_pdl(rmsnorm_kernel<bf16>, n_rows, nt, 0, s, x, rows, w, w_dtype, eps, (bf16*)out, hidden);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
@@ -240,11 +254,11 @@ extern "C" int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positi
     const int work = (n_heads + n_kv_heads) * (head_dim / 2);
     const int nt = threads_for(work > 256 ? 256 : work);
     if (dtype == FX_F32)
-        rope_kv_write_kernel<float><<<n_tokens, nt, 0, s>>>((float*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
+        fx_launch_pdl(rope_kv_write_kernel<float>, n_tokens, nt, 0, s, (float*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
             cos_sin, rotary_dim, (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
             head_dim, write_cache, status);
     else if (dtype == FX_BF16)
-        rope_kv_write_kernel<bf16><<<n_tokens, nt, 0, s>>>((bf16*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
+        fx_launch_pdl(rope_kv_write_kernel<bf16>, n_tokens, nt, 0, s, (bf16*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
             cos_sin, rotary_dim, (bf16*)k_pages, (bf16*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
             head_dim, write_cache, status);
     else return FX_ERR_DTYPE;
@@ -257,7 +271,7 @@ extern "C" int fx_rope_table(const int* positions, const float* inv_freq, int n_
     if (n_tokens <= 0 || half <= 0) return FX_OK;
     long blocks = fx_cdiv((long)n_tokens * half, 128);
     if (blocks > 148 * 8) blocks = 148 * 8;
-    rope_table_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(positions, inv_freq, n_tokens, half, cos_sin);
+    fx_launch_pdl(rope_table_kernel, (unsigned)blocks, 128, 0, (cudaStream_t)stream, positions, inv_freq, n_tokens, half, cos_sin);
     return fx_launch_status();
 }
 
@@ -270,10 +284,10 @@ extern "C" int fx_moe_combine(float* h, const void* y, int dtype, const int* inv
     const int nt = threads_for(hidden > 128 ? 128 : hidden);
     const dim3 grid(n_tokens, (unsigned)fx_cdiv(hidden, nt));
     if (dtype == FX_F32)
-        moe_combine_kernel<float><<<grid, nt, 0, s>>>(h, (const float*)y, inv_perm, topk_w, top_k,
+        fx_launch_pdl(moe_combine_kernel<float>, grid, nt, 0, s, h, (const float*)y, inv_perm, topk_w, top_k,
                                                       (const float*)shared, shared_gate_logit, hidden);
     else if (dtype == FX_BF16)
-        moe_combine_kernel<bf16><<<grid, nt, 0, s>>>(h, (const bf16*)y, inv_perm, topk_w, top_k,
+        fx_launch_pdl(moe_combine_kernel<bf16>, grid, nt, 0, s, h, (const bf16*)y, inv_perm, topk_w, top_k,
                                                      (const bf16*)shared, shared_gate_logit, hidden);
     else return FX_ERR_DTYPE;
     return fx_launch_status();

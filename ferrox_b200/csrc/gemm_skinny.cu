@@ -50,131 +50,147 @@ struct SkinnyArgs {
     int n_tokens; int N; int K;
     int gate_up_offset;            // gated form: row of `up` matching gate row i is i + gate_up_offset
     const int* group_offsets;      // grouped form: rows [off[e], off[e+1]) belong to expert e
-    const int* active_groups;      // grouped form: expert of each grid.y slot, -1 = none
+    const int* active_groups;      // grouped form: the experts that got rows, then -1
+    int n_slots;                   // length of active_groups
 };
 
 // MODE 0: 16 features per block.  MODE 1 (gated): 16 gate rows and their 16 up rows, out = silu(gate) * up.
 // MODE 2: 32 features per block (two tiles of rows), for wide matrices: half as many, fatter blocks.
+//
+// Grouped form: blockIdx.y walks the list of experts that got rows in steps of gridDim.y, so that a block pays
+// its start-up once for several experts.  The weight loads of a pass are issued before the token rows are
+// looked up, and in the plain form even before the wait on the kernel that produced X: the weights do not
+// depend on it.
 template <int NT, int MODE>
 __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
 {
     constexpr bool GATED = MODE != 0;   // a second set of 16 rows is streamed beside the first
+    constexpr int UNROLL = (GATED ? 4 : 8) / (NT > 2 ? 2 : 1);
     __shared__ float red[WARPS][GATED ? 2 : 1][NT][16][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (MODE == 2 ? 32 : 16);
-
-    int row_begin = 0, row_end = a.n_tokens;
-    const bf16* W = a.W;
-    if (a.group_offsets) {
-        const int e = a.active_groups[blockIdx.y];
-        if (e < 0) return;
-        row_begin = a.group_offsets[e];
-        row_end = a.group_offsets[e + 1];
-        W += (long)e * a.w_group_stride;
-    }
-    // rows of W this lane reads: g and g+8 of the tile (clamped; masked at the store)
-    const int r0 = min(n0 + g, a.N - 1), r1 = min(n0 + g + 8, a.N - 1);
-    const bf16* w0 = W + (long)r0 * a.ldw + t * 8;
-    const bf16* w1 = W + (long)r1 * a.ldw + t * 8;
-    const bf16* u0 = nullptr;
-    const bf16* u1 = nullptr;
-    if (MODE == 1) {
-        u0 = w0 + (long)a.gate_up_offset * a.ldw;
-        u1 = w1 + (long)a.gate_up_offset * a.ldw;
-    } else if (MODE == 2) {
-        u0 = W + (long)min(n0 + 16 + g, a.N - 1) * a.ldw + t * 8;
-        u1 = W + (long)min(n0 + 24 + g, a.N - 1) * a.ldw + t * 8;
-    }
     const int n_chunks = a.K >> 5;
+    const bool grouped = a.group_offsets != nullptr;
+    // rows of W this lane reads: g and g+8 of the tile (clamped; masked at the store)
+    const long o0 = (long)min(n0 + g, a.N - 1) * a.ldw + t * 8;
+    const long o1 = (long)min(n0 + g + 8, a.N - 1) * a.ldw + t * 8;
+    long p0 = 0, p1 = 0;   // the second set of rows
+    if (MODE == 1) { p0 = o0 + (long)a.gate_up_offset * a.ldw; p1 = o1 + (long)a.gate_up_offset * a.ldw; }
+    if (MODE == 2) {
+        p0 = (long)min(n0 + 16 + g, a.N - 1) * a.ldw + t * 8;
+        p1 = (long)min(n0 + 24 + g, a.N - 1) * a.ldw + t * 8;
+    }
 
-    for (int tok0 = row_begin; tok0 < row_end; tok0 += 8 * NT) {
-        // token rows this lane reads for the B operand: token g of each n-tile
-        const bf16* xp[NT];
+    uint4 wa[UNROLL], wb[UNROLL], ua[UNROLL], ub[UNROLL];
+    auto load_pass = [&](const bf16* W, int i0) {
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const int r = tok0 + j * 8 + g;
-            xp[j] = r < row_end ? a.X + (long)(a.x_rows ? a.x_rows[r] : r) * a.ldx + t * 8 : nullptr;
-        }
-        float acc[GATED ? 2 : 1][NT][4];
-#pragma unroll
-        for (int s = 0; s < (GATED ? 2 : 1); ++s)
-#pragma unroll
-            for (int j = 0; j < NT; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.f;
-
-        // Chunk c of K belongs to warp c % 8, so that the 8 warps read 512 contiguous
-        // bytes of a row together and share the chunks evenly whatever K is; a warp
-        // issues the loads of UNROLL of its chunks before it uses the first.
-        constexpr int UNROLL = (GATED ? 4 : 8) / (NT > 2 ? 2 : 1);
-        for (int i0 = 0; warp + WARPS * i0 < n_chunks; i0 += UNROLL) {
-            uint4 wa[UNROLL], wb[UNROLL], ua[UNROLL], ub[UNROLL];
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const int c = warp + WARPS * (i0 + u);
-                if (c < n_chunks) {
-                    wa[u] = ldg_stream(w0 + c * 32);
-                    wb[u] = ldg_stream(w1 + c * 32);
-                    if (GATED) { ua[u] = ldg_stream(u0 + c * 32); ub[u] = ldg_stream(u1 + c * 32); }
-                }
+        for (int u = 0; u < UNROLL; ++u) {
+            const int c = warp + WARPS * (i0 + u);
+            if (c < n_chunks) {
+                wa[u] = ldg_stream(W + o0 + c * 32);
+                wb[u] = ldg_stream(W + o1 + c * 32);
+                if (GATED) { ua[u] = ldg_stream(W + p0 + c * 32); ub[u] = ldg_stream(W + p1 + c * 32); }
             }
+        }
+    };
+
+    bool have_first = false;
+    if (!grouped) { load_pass(a.W, 0); have_first = true; }   // independent of the kernel before this one
+    fx_pdl_wait();
+
+    for (int slot = grouped ? blockIdx.y : 0; slot < (grouped ? a.n_slots : 1); slot += grouped ? gridDim.y : 1) {
+        int row_begin = 0, row_end = a.n_tokens;
+        const bf16* W = a.W;
+        if (grouped) {
+            const int e = a.active_groups[slot];
+            if (e < 0) break;   // the list is compact: nothing after the first -1
+            W += (long)e * a.w_group_stride;
+            load_pass(W, 0);
+            have_first = true;
+            row_begin = a.group_offsets[e];
+            row_end = a.group_offsets[e + 1];
+        }
+        for (int tok0 = row_begin; tok0 < row_end; tok0 += 8 * NT) {
+            // token rows this lane reads for the B operand: token g of each n-tile
+            const bf16* xp[NT];
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const int c = warp + WARPS * (i0 + u);
-                if (c >= n_chunks) break;
+            for (int j = 0; j < NT; ++j) {
+                const int r = tok0 + j * 8 + g;
+                xp[j] = r < row_end ? a.X + (long)(a.x_rows ? a.x_rows[r] : r) * a.ldx + t * 8 : nullptr;
+            }
+            float acc[GATED ? 2 : 1][NT][4];
 #pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-                    if (xp[j]) xv = *reinterpret_cast<const uint4*>(xp[j] + c * 32);
-                    mma16816(acc[0][j], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
-                    mma16816(acc[0][j], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
-                    if (GATED) {
-                        mma16816(acc[1][j], ua[u].x, ub[u].x, ua[u].y, ub[u].y, xv.x, xv.y);
-                        mma16816(acc[1][j], ua[u].z, ub[u].z, ua[u].w, ub[u].w, xv.z, xv.w);
+            for (int s = 0; s < (GATED ? 2 : 1); ++s)
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[s][j][i] = 0.f;
+
+            // Chunk c of K belongs to warp c % 8, so that the 8 warps read 512 contiguous bytes of a row
+            // together and share the chunks evenly whatever K is; a warp issues the loads of UNROLL of its
+            // chunks before it uses the first.
+            for (int i0 = 0; warp + WARPS * i0 < n_chunks; i0 += UNROLL) {
+                if (!(have_first && i0 == 0)) load_pass(W, i0);
+                have_first = false;
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int c = warp + WARPS * (i0 + u);
+                    if (c >= n_chunks) break;
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+                        if (xp[j]) xv = *reinterpret_cast<const uint4*>(xp[j] + c * 32);
+                        mma16816(acc[0][j], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
+                        mma16816(acc[0][j], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
+                        if (GATED) {
+                            mma16816(acc[1][j], ua[u].x, ub[u].x, ua[u].y, ub[u].y, xv.x, xv.y);
+                            mma16816(acc[1][j], ua[u].z, ub[u].z, ua[u].w, ub[u].w, xv.z, xv.w);
+                        }
                     }
                 }
             }
-        }
-        // partial sums of this warp -> shared memory: [row g | g+8][token 2t | 2t+1]
-        __syncthreads();  // the previous token tile's reduction has been read
+            have_first = false;
+            // partial sums of this warp -> shared memory: [row g | g+8][token 2t | 2t+1]
+            __syncthreads();  // the previous reduction has been read
 #pragma unroll
-        for (int s = 0; s < (GATED ? 2 : 1); ++s)
+            for (int s = 0; s < (GATED ? 2 : 1); ++s)
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                red[warp][s][j][g][2 * t] = acc[s][j][0];
-                red[warp][s][j][g][2 * t + 1] = acc[s][j][1];
-                red[warp][s][j][g + 8][2 * t] = acc[s][j][2];
-                red[warp][s][j][g + 8][2 * t + 1] = acc[s][j][3];
-            }
-        __syncthreads();
-        // 16 features x 8*NT tokens: consecutive threads take consecutive features of one token
-        for (int o = threadIdx.x; o < 16 * 8 * NT; o += NTHREADS) {
-            const int f = o & 15, tk = o >> 4;
-            const int j = tk >> 3, tn = tk & 7;
-            const int r = tok0 + tk, n = n0 + f;
-            if (r >= row_end || n >= a.N) continue;
-            float v = 0.f, up = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) {
-                v += red[w][0][j][f][tn];
-                if (GATED) up += red[w][1][j][f][tn];
-            }
-            if (a.bias) v += load_any(a.bias, a.bias_dtype, n);
-            if (MODE == 1) v = v / (1.0f + expf(-v)) * up;
-            auto store = [&](int col, float val) {
-                if (a.c_dtype == FX_F32) {
-                    float* c = reinterpret_cast<float*>(a.C) + (long)r * a.ldc + col;
-                    *c = a.accumulate ? *c + val : val;
-                } else {
-                    bf16* c = reinterpret_cast<bf16*>(a.C) + (long)r * a.ldc + col;
-                    *c = __float2bfloat16_rn(a.accumulate ? __bfloat162float(*c) + val : val);
+                for (int j = 0; j < NT; ++j) {
+                    red[warp][s][j][g][2 * t] = acc[s][j][0];
+                    red[warp][s][j][g][2 * t + 1] = acc[s][j][1];
+                    red[warp][s][j][g + 8][2 * t] = acc[s][j][2];
+                    red[warp][s][j][g + 8][2 * t + 1] = acc[s][j][3];
                 }
-            };
-            store(n, v);
-            if (MODE == 2 && n + 16 < a.N) {
-                if (a.bias) up += load_any(a.bias, a.bias_dtype, n + 16);
-                store(n + 16, up);
+            __syncthreads();
+            // 16 features x 8*NT tokens: consecutive threads take consecutive features of one token
+            for (int o = threadIdx.x; o < 16 * 8 * NT; o += NTHREADS) {
+                const int f = o & 15, tk = o >> 4;
+                const int j = tk >> 3, tn = tk & 7;
+                const int r = tok0 + tk, n = n0 + f;
+                if (r >= row_end || n >= a.N) continue;
+                float v = 0.f, up = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    v += red[w][0][j][f][tn];
+                    if (GATED) up += red[w][1][j][f][tn];
+                }
+                if (a.bias) v += load_any(a.bias, a.bias_dtype, n);
+                if (MODE == 1) v = v / (1.0f + expf(-v)) * up;
+                auto store = [&](int col, float val) {
+                    if (a.c_dtype == FX_F32) {
+                        float* c = reinterpret_cast<float*>(a.C) + (long)r * a.ldc + col;
+                        *c = a.accumulate ? *c + val : val;
+                    } else {
+                        bf16* c = reinterpret_cast<bf16*>(a.C) + (long)r * a.ldc + col;
+                        *c = __float2bfloat16_rn(a.accumulate ? __bfloat162float(*c) + val : val);
+                    }
+                };
+                store(n, v);
+                if (MODE == 2 && n + 16 < a.N) {
+                    if (a.bias) up += load_any(a.bias, a.bias_dtype, n + 16);
+                    store(n + 16, up);
+                }
             }
         }
     }
@@ -183,9 +199,9 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
 template <int MODE>
 int launch_nt(const SkinnyArgs& a, int max_tokens_per_group, dim3 grid, cudaStream_t s)
 {
-    if (max_tokens_per_group <= 8) skinny_kernel<1, MODE><<<grid, NTHREADS, 0, s>>>(a);
-    else if (max_tokens_per_group <= 16) skinny_kernel<2, MODE><<<grid, NTHREADS, 0, s>>>(a);
-    else skinny_kernel<4, MODE><<<grid, NTHREADS, 0, s>>>(a);
+    if (max_tokens_per_group <= 8) fx_launch_pdl(skinny_kernel<1, MODE>, grid, NTHREADS, 0, s, a);
+    else if (max_tokens_per_group <= 16) fx_launch_pdl(skinny_kernel<2, MODE>, grid, NTHREADS, 0, s, a);
+    else fx_launch_pdl(skinny_kernel<4, MODE>, grid, NTHREADS, 0, s, a);
     return fx_launch_status();
 }
 
@@ -212,7 +228,9 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.n_tokens = n_tokens; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset;
-    a.group_offsets = group_offsets; a.active_groups = active_groups;
+    a.group_offsets = group_offsets; a.active_groups = active_groups; a.n_slots = n_slots;
+    // grouped: one block row per expert slot (many short blocks hide each other's start-up better than
+    // few long ones; measured)
     const int slots = group_offsets ? n_slots : 1;
     // wide matrices: 32 features per block, so that half as many blocks pay the start-up latency
     const bool two_tiles = !gated && fx_cdiv(N, 32) * slots >= 2 * 148;

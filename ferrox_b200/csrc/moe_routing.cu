@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
     int* __restrict__ active, int n_slots)
 {
     extern __shared__ float smem[];  // [SMALL_WARPS][n_experts] floats, then 2 * n_experts + 1 ints
+    fx_pdl_wait();
     int* counts = reinterpret_cast<int*>(smem + (long)SMALL_WARPS * n_experts);
     int* offs = counts + n_experts;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -163,7 +164,7 @@ extern "C" int fx_route_small(const float* logits, int n_tokens, int n_experts, 
     if (top_k <= 0 || top_k > n_experts || n_tokens > 1024) return FX_ERR_SIZE;
     const size_t smem = (size_t)SMALL_WARPS * n_experts * sizeof(float) + (2 * (size_t)n_experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return FX_ERR_SIZE;
-    route_small_kernel<<<1, SMALL_WARPS * 32, smem, (cudaStream_t)stream>>>(
+    fx_launch_pdl(route_small_kernel, 1, SMALL_WARPS * 32, smem, (cudaStream_t)stream,
         logits, n_tokens, n_experts, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active, n_slots);
     return fx_launch_status();
 }

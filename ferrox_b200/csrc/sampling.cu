@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(NT) argmax_kernel(const float* __restrict__ lo
 {
     __shared__ float sv[32];
     __shared__ int si[32];
+    fx_pdl_wait();
     const float* row = logits + (long)blockIdx.x * ld;
     float best = -INFINITY; int best_i = 0x7fffffff;
     for (int i = threadIdx.x; i < vocab; i += NT) {
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(NT) sample_kernel(float* __restrict__ work, lo
 extern "C" int fx_argmax(const float* logits, long ld, int n_rows, int vocab, int* out, void* stream)
 {
     if (n_rows <= 0) return FX_OK;
-    argmax_kernel<<<n_rows, NT, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out);
+    fx_launch_pdl(argmax_kernel, n_rows, NT, 0, (cudaStream_t)stream, logits, ld, vocab, out);
     return fx_launch_status();
 }
 
