@@ -45,6 +45,7 @@ template <int BN> struct Cfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static_assert(2 * BN <= 512, "two accumulators must fit the 512 columns of tensor memory");
 };
 
 struct TcArgs {
@@ -136,6 +137,39 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Where a tile lies.  Dense: ids run over the row tiles first, so that CTAs working at the same time share
+// a slice of W.  Grouped: ids run over the feature tiles first, so that they share an expert's rows of X.
+struct TileCoord { int group, m0, row_end, n0; };
+
+template <int OUT_N>
+__device__ __forceinline__ TileCoord tile_coord(int id, const TcArgs& a, int m_tiles, int n_tiles, const int* cum) {
+    TileCoord t;
+    if (!a.group_offsets) {
+        t.group = 0;
+        t.n0 = (id / m_tiles) * OUT_N;
+        t.m0 = (id % m_tiles) * BM;
+        t.row_end = a.M;
+    } else {
+        const int mi = id / n_tiles;
+        t.n0 = (id % n_tiles) * OUT_N;
+        int lo = 0, hi = a.n_groups;            // largest e with cum[e] <= mi
+        while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (cum[mid] <= mi) lo = mid; else hi = mid; }
+        t.group = lo;
+        t.m0 = a.group_offsets[lo] + (mi - cum[lo]) * BM;
+        t.row_end = a.group_offsets[lo + 1];
+    }
+    return t;
+}
+
+constexpr int MAX_GROUPS = 1024;
+
+// Persistent: gridDim.x CTAs (at most one per SM) take tiles id = blockIdx.x, + gridDim.x, ...  The
+// accumulator is double-buffered in tensor memory (2 x BN columns), so the epilogue of one tile runs while
+// the tensor cores work on the next.
 template <int BN, bool GATED>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                               const __grid_constant__ CUtensorMap map_b, TcArgs a)
@@ -144,35 +178,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     constexpr int STAGES = C::STAGES;
     constexpr int OUT_N = GATED ? BN / 2 : BN;   // output features per tile
     extern __shared__ uint8_t smem_raw[];
-    __shared__ int tile_info[3];
+    __shared__ int cum_s[MAX_GROUPS + 1];        // grouped: row tiles before each group
     __shared__ int abort_flag_s;
     __shared__ uint32_t tmem_base_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    // ---- which tile -----------------------------------------------------------
-    int group = 0, row_begin = 0, row_end = a.M, m_tile = blockIdx.y;
+    const int n_tiles = (a.N + OUT_N - 1) / OUT_N;
+    int m_tiles = (a.M + BM - 1) / BM;
     if (a.group_offsets) {
+        for (int e = threadIdx.x; e < a.n_groups; e += NTHREADS)     // row tiles of each group, loaded in parallel
+            cum_s[e + 1] = (a.group_offsets[e + 1] - a.group_offsets[e] + BM - 1) / BM;
+        __syncthreads();
         if (threadIdx.x == 0) {
-            int y = blockIdx.y, found = -1;
-            for (int e = 0; e < a.n_groups; ++e) {
-                const int rows = a.group_offsets[e + 1] - a.group_offsets[e];
-                const int tiles = (rows + BM - 1) / BM;
-                if (y < tiles) { found = e; break; }
-                y -= tiles;
-            }
-            tile_info[0] = found; tile_info[1] = y;
+            int run = 0;
+            for (int e = 0; e < a.n_groups; ++e) { const int n = cum_s[e + 1]; cum_s[e] = run; run += n; }
+            cum_s[a.n_groups] = run;
         }
         __syncthreads();
-        group = tile_info[0];
-        if (group < 0) return;   // the grid is an upper bound on the number of tiles
-        m_tile = tile_info[1];
-        row_begin = a.group_offsets[group];
-        row_end = a.group_offsets[group + 1];
+        m_tiles = cum_s[a.n_groups];
     }
-    const int m0 = row_begin + m_tile * BM;
-    if (m0 >= row_end) return;
-    const int n0 = blockIdx.x * OUT_N;
+    const int total = m_tiles * n_tiles;
+    if ((int)blockIdx.x >= total) return;
     const int k_blocks = (a.K + BK - 1) / BK;
 
     // ---- shared memory: stages (1024-byte aligned), then barriers ---------------
@@ -181,19 +207,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     const uint32_t bar_base = base + STAGES * C::STAGE_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-    const uint32_t accum_bar = bar_base + 8u * (2 * STAGES);
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
     volatile int* abort_flag = &abort_flag_s;
 
     if (threadIdx.x == 0) {
         abort_flag_s = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(accum_bar, 1);
+        for (int b2 = 0; b2 < 2; ++b2) { mbar_init(acc_full_bar(b2), 1); mbar_init(acc_empty_bar(b2), 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {   // tensor memory: BN columns of 128 lanes x 32 bit
+    if (warp == 1) {   // tensor memory: two accumulators of BN columns (128 lanes x 32 bit each)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)BN) : "memory");
+                     ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -204,28 +231,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
-                if (!mbar_wait(empty_bar(s), parity, abort_flag)) break;
-                const uint32_t sa = base + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-                mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-                tma_load_2d(sa, &map_a, kb * BK, m0, full_bar(s));
-                if (GATED) {
-                    tma_load_3d(sb, &map_b, kb * BK, n0, group, full_bar(s));
-                    tma_load_3d(sb + C::B_BYTES / 2, &map_b, kb * BK, a.gate_up_offset + n0, group, full_bar(s));
-                } else {
-                    tma_load_3d(sb, &map_b, kb * BK, n0, group, full_bar(s));
+            long issued = 0;   // k-blocks issued so far, over all tiles of this CTA
+            bool ok = true;
+            for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
+                const TileCoord tc = tile_coord<OUT_N>(id, a, m_tiles, n_tiles, cum_s);
+                for (int kb = 0; kb < k_blocks; ++kb, ++issued) {
+                    const int s = (int)(issued % STAGES);
+                    const uint32_t parity = (uint32_t)((issued / STAGES) & 1) ^ 1u;
+                    if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = base + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+                    mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, kb * BK, tc.m0, full_bar(s));
+                    if (GATED) {
+                        tma_load_3d(sb, &map_b, kb * BK, tc.n0, tc.group, full_bar(s));
+                        tma_load_3d(sb + C::B_BYTES / 2, &map_b, kb * BK, a.gate_up_offset + tc.n0, tc.group, full_bar(s));
+                    } else {
+                        tma_load_3d(sb, &map_b, kb * BK, tc.n0, tc.group, full_bar(s));
+                    }
                 }
-                issued = kb + 1;
             }
             if (*abort_flag) {
                 // loads already issued must land before the CTA's shared memory is released
-                for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
-                    const int s = kb % STAGES;
+                for (long kb = issued > STAGES ? issued - STAGES : 0; kb < issued; ++kb) {
+                    const int s = (int)(kb % STAGES);
                     for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-                        if (mbar_try_wait(full_bar(s), (kb / STAGES) & 1)) break;
+                        if (mbar_try_wait(full_bar(s), (uint32_t)((kb / STAGES) & 1))) break;
                 }
             }
         }
@@ -233,39 +263,60 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
         // ---------------- tensor-core issue ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(BM, BN);
+            long used = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(full_bar(s), (kb / STAGES) & 1, abort_flag);
+            int it = 0;
+            for (int id = blockIdx.x; id < total && ok; id += gridDim.x, ++it) {
+                const int buf = it & 1;
+                // the epilogue has drained this accumulator (first use of each passes at once)
+                ok = mbar_wait(acc_empty_bar(buf), (uint32_t)((it >> 1) & 1) ^ 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sa = base + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-                const uint64_t da = smem_desc(sa), db = smem_desc(sb);
+                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++used) {
+                    const int s = (int)(used % STAGES);
+                    ok = mbar_wait(full_bar(s), (uint32_t)((used / STAGES) & 1), abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+                    const uint64_t da = smem_desc(sa), db = smem_desc(sb);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 elements = 32 bytes further along K inside the swizzled row: +2 in units of 16 bytes
-                    tc_mma(tmem_base, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 elements = 32 bytes further along K inside the swizzled row: +2 in units of 16 bytes
+                        tc_mma(acc, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                    }
+                    tc_commit(empty_bar(s));   // the stage is free once these instructions have read it
                 }
-                tc_commit(empty_bar(s));   // the stage is free once these instructions have read it
+                if (ok) tc_commit(acc_full_bar(buf));  // complete once all instructions so far have retired
             }
-            if (ok) tc_commit(accum_bar);  // the accumulator is complete once all instructions have retired
         }
     } else {
         // ---------------- epilogue ----------------
         const int quad = warp & 3;                       // TMEM lanes 32*quad .. 32*quad+31
-        const int row = m0 + quad * 32 + lane;
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0, abort_flag));  // tcgen05.ld needs whole warps
-        if (ok) {
+        int it = 0;
+        for (int id = blockIdx.x; id < total; id += gridDim.x, ++it) {
+            const TileCoord tc = tile_coord<OUT_N>(id, a, m_tiles, n_tiles, cum_s);
+            const int buf = it & 1;
+            const int row = tc.m0 + quad * 32 + lane;
+            // tcgen05.ld needs whole warps: agree on the outcome of the wait
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (uint32_t)((it >> 1) & 1), abort_flag));
+            if (!ok) break;
             tc_fence_after();
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-            const bool row_ok = row < row_end;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+            const bool row_ok = row < tc.row_end;
 #pragma unroll 1
             for (int c = 0; c < OUT_N / 32; ++c) {
                 uint32_t r[32], u[32];
                 tc_ld32(lane_addr + c * 32, r);
                 if (GATED) tc_ld32(lane_addr + BN / 2 + c * 32, u);
                 tc_ld_wait();
-                const int nb = n0 + c * 32;
+                if (c == OUT_N / 32 - 1) {
+                    // everything of this accumulator is in registers: hand it back to the tensor cores
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                }
+                const int nb = tc.n0 + c * 32;
                 if (!row_ok || nb >= a.N) continue;
                 float v[32];
 #pragma unroll
@@ -319,7 +370,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
     }
     if (threadIdx.x == 0 && abort_flag_s && a.status) atomicExch(a.status, FX_STATUS_TC_TIMEOUT);
 }
@@ -357,8 +408,19 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t d1, uint64
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int sm_count()
+{
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
 template <int BN, bool GATED>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t s)
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, long max_tiles, cudaStream_t s)
 {
     auto kern = gemm_tc_kernel<BN, GATED>;
     static bool configured = false;
@@ -367,8 +429,25 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 g
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
+    const unsigned grid = (unsigned)(max_tiles < sm_count() ? max_tiles : sm_count());
     kern<<<grid, NTHREADS, Cfg<BN>::SMEM, s>>>(ma, mb, a);
     return fx_launch_status();
+}
+
+template <int BN>
+int run_bn(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, TcArgs& a, int gated,
+           cudaStream_t s)
+{
+    const int out_n = gated ? BN / 2 : BN;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, X, (uint64_t)a.K, (uint64_t)a.M, 1, (uint64_t)ldx, 0, BM, 2)) return FX_ERR_SIZE;
+    const int G = a.group_offsets ? a.n_groups : 1;
+    if (!make_map(&mb, W, (uint64_t)a.K, (uint64_t)w_rows, (uint64_t)G, (uint64_t)ldw,
+                  (uint64_t)(G > 1 ? w_group_stride : (long)w_rows * ldw), gated ? BN / 2 : BN, 3))
+        return FX_ERR_SIZE;
+    const long m_tiles = a.group_offsets ? fx_cdiv(a.M, BM) + a.n_groups : fx_cdiv(a.M, BM);   // an upper bound when grouped
+    const long max_tiles = m_tiles * fx_cdiv(a.N, out_n);
+    return gated ? launch<BN, true>(ma, mb, a, max_tiles, s) : launch<BN, false>(ma, mb, a, max_tiles, s);
 }
 
 }  // namespace
@@ -385,22 +464,15 @@ extern "C" int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long
     if (K <= 0 || K % 8) return FX_ERR_SIZE;
     if (ldx % 8 || ldw % 8 || w_group_stride % 8 || (uintptr_t)X % 16 || (uintptr_t)W % 16) return FX_ERR_ALIGN;
     if (c_dtype != FX_F32 && c_dtype != FX_BF16) return FX_ERR_DTYPE;
-    constexpr int BN = 128;
-    const int out_n = gated ? BN / 2 : BN;
-    CUtensorMap ma, mb;
-    if (!make_map(&ma, X, (uint64_t)K, (uint64_t)M, 1, (uint64_t)ldx, 0, BM, 2)) return FX_ERR_SIZE;
-    const int G = group_offsets ? n_groups : 1;
-    if (!make_map(&mb, W, (uint64_t)K, (uint64_t)w_rows, (uint64_t)G, (uint64_t)ldw,
-                  (uint64_t)(G > 1 ? w_group_stride : (long)w_rows * ldw), gated ? BN / 2 : BN, 3))
-        return FX_ERR_SIZE;
+    if (group_offsets && n_groups > MAX_GROUPS) return FX_ERR_SIZE;
     TcArgs a;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset;
     a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status;
-    const long m_tiles = group_offsets ? fx_cdiv(M, BM) + n_groups : fx_cdiv(M, BM);
-    dim3 grid((unsigned)fx_cdiv(N, out_n), (unsigned)m_tiles);
-    if (grid.y > 65535u) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    return gated ? launch<BN, true>(ma, mb, a, grid, s) : launch<BN, false>(ma, mb, a, grid, s);
+    // wide outputs take 128 x 256 tiles (fewer bytes fetched per flop); narrow ones 128 x 128
+    const int wide = gated ? N >= 256 : N >= 512;
+    if (wide) return run_bn<256>(X, ldx, W, ldw, w_group_stride, w_rows, a, gated, s);
+    return run_bn<128>(X, ldx, W, ldw, w_group_stride, w_rows, a, gated, s);
 }

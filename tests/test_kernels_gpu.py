@@ -432,7 +432,7 @@ def test_rope_table_matches_inline_angles():
 
 # ------------------------------------------------------------------ tcgen05 products
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 512), (65, 60, 72), (300, 200, 2048), (129, 130, 200),
-                                   (2048, 256, 1408)])
+                                   (2048, 256, 1408), (2048, 6144, 2048), (1000, 1000, 520), (4096, 640, 72)])
 def test_gemm_tc_dense(M, N, K):
     o = ops()
     x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1), rnd(N)
@@ -453,7 +453,7 @@ def test_gemm_tc_dense(M, N, K):
     assert rel(out32, wide[:, :K].float() @ w.float().T) < 2e-5
 
 
-@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (200, 1408, 256), (70, 100, 96)])
+@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (200, 1408, 256), (70, 100, 96), (2048, 5632, 2048), (700, 300, 136)])
 def test_gemm_tc_gated(M, I, K):
     o = ops()
     x, w = rnd(M, K, dtype=torch.bfloat16), rnd(2 * I, K, dtype=torch.bfloat16, scale=0.2)
@@ -464,10 +464,12 @@ def test_gemm_tc_gated(M, I, K):
     assert int(status) == 0 and rel(out, gate / (1 + torch.exp(-gate)) * up) < 3e-5
 
 
-@pytest.mark.parametrize("counts", [[0, 130, 1, 0, 128, 255], [3, 0, 0, 0, 0, 700], [64, 64, 64, 64, 64, 64]])
+@pytest.mark.parametrize("counts", [[0, 130, 1, 0, 128, 255], [3, 0, 0, 0, 0, 700], [64, 64, 64, 64, 64, 64],
+                                    [137, 0, 512, 9] * 15])
 def test_gemm_tc_grouped(counts):
     o = ops()
-    G, I, H = len(counts), 96, 128
+    G = len(counts)
+    I, H = (96, 128) if G < 10 else (320, 520)   # the large case takes 128 x 256 tiles and several tiles per CTA
     R = sum(counts)
     x = rnd(R, H, dtype=torch.bfloat16)
     w_gu, w_down = rnd(G, 2 * I, H, dtype=torch.bfloat16, scale=0.1), rnd(G, H, I, dtype=torch.bfloat16, scale=0.1)
