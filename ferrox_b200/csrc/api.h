@@ -25,7 +25,8 @@ int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const 
                      int table_width, int page_size, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                      int write_cache, int* status, void* stream);
 int fx_moe_combine(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w, int top_k,
-                   const void* shared, const float* shared_gate_logit, int n_tokens, int hidden, void* stream);
+                   const void* shared, const float* shared_gate_logit, long gate_ld, int n_tokens, int hidden,
+                   void* stream);
 int fx_residual_add(float* h, const void* y, int dtype, long n, void* stream);
 
 int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
@@ -37,8 +38,8 @@ int fx_prefill_attention(const void* q, long ldq, const void* k_pages, const voi
                          int table_width, int page_size, const int* tiles, int n_tiles, const int* seq_slot, void* out,
                          long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale, void* stream);
 
-int fx_router_topk(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
-                   void* stream);
+int fx_router_topk(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
+                   float* weights, void* stream);
 int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets, int* src_token,
                  int* inv_perm, int* active, int n_slots, void* stream);
 
@@ -47,7 +48,7 @@ int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long w_group_st
                int gate_up_offset, const int* group_offsets, int n_groups, int* status, void* stream);
 int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo, int dtype, int n_rows, int width,
                    void* stream);
-int fx_route_small(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
+int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
                    int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
 int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin, void* stream);
 int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, long ldw, long w_group_stride,

@@ -159,12 +159,12 @@ template <typename T>
 __global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ y, const int* __restrict__ inv_perm,
                                    const float* __restrict__ topk_w, int top_k,
                                    const T* __restrict__ shared, const float* __restrict__ shared_gate_logit,
-                                   int hidden)
+                                   long gate_ld, int hidden)
 {
     fx_pdl_wait();
     const int t = blockIdx.x;
     float g = 1.f;
-    if (shared && shared_gate_logit) g = 1.0f / (1.0f + expf(-shared_gate_logit[t]));
+    if (shared && shared_gate_logit) g = 1.0f / (1.0f + expf(-shared_gate_logit[(long)t * gate_ld]));
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hidden; i += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top_k; ++k) {
@@ -201,6 +201,183 @@ __global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__
         h[i] += to_f32(y[i]);
 }
 
+// ---------------------------------------------------------------------------
+// 16-byte vector forms of the kernels above, used when widths and addresses allow.
+template <typename T> struct Pack;
+template <> struct Pack<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* o) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* o) {
+        *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+    }
+};
+template <> struct Pack<bf16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16* p, float* o) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[2 * i] = __uint_as_float(w[i] << 16);
+            o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float* o) {
+        uint4 v;
+        __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b = __floats2bfloat162_rn(o[2], o[3]);
+        __nv_bfloat162 c = __floats2bfloat162_rn(o[4], o[5]), d = __floats2bfloat162_rn(o[6], o[7]);
+        v.x = *reinterpret_cast<uint32_t*>(&a); v.y = *reinterpret_cast<uint32_t*>(&b);
+        v.z = *reinterpret_cast<uint32_t*>(&c); v.w = *reinterpret_cast<uint32_t*>(&d);
+        *reinterpret_cast<uint4*>(p) = v;
+    }
+};
+
+// RMSNorm, 4 elements per thread and pass (hidden % 4 == 0, rows 16-byte aligned).
+template <typename OT>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                   const void* __restrict__ w, int w_dtype, float eps,
+                                   OT* __restrict__ out, int hidden)
+{
+    __shared__ float scratch[33];
+    fx_pdl_wait();
+    const int r = blockIdx.x;
+    const float* xr = x + (long)(rows ? rows[r] : r) * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    OT* o = out + (long)r * hidden;
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        float wv[4];
+        if (w_dtype == FX_F32) {
+            const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i);
+            wv[0] = t.x; wv[1] = t.y; wv[2] = t.z; wv[3] = t.w;
+        } else {
+            const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(w) + i);
+            wv[0] = __uint_as_float(t.x << 16); wv[1] = __uint_as_float(t.x & 0xffff0000u);
+            wv[2] = __uint_as_float(t.y << 16); wv[3] = __uint_as_float(t.y & 0xffff0000u);
+        }
+        const float y0 = v.x * scale * wv[0], y1 = v.y * scale * wv[1], y2 = v.z * scale * wv[2], y3 = v.w * scale * wv[3];
+        if (sizeof(OT) == 4) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + i) = make_float4(y0, y1, y2, y3);
+        } else {
+            __nv_bfloat162 a = __floats2bfloat162_rn(y0, y1), b = __floats2bfloat162_rn(y2, y3);
+            uint2 pk; pk.x = *reinterpret_cast<uint32_t*>(&a); pk.y = *reinterpret_cast<uint32_t*>(&b);
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(o) + i) = pk;
+        }
+    }
+}
+
+// Rotary + cache write, 16 bytes per thread and pass.  Needs rotary_dim == head_dim, (head_dim / 2) a
+// multiple of the vector width and 16-byte aligned rows; same arithmetic as the scalar kernel.
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, long ld, const int* __restrict__ positions,
+                                         const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                         const float* __restrict__ inv_freq, const float* __restrict__ cos_sin,
+                                         T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                         const int* __restrict__ block_table, int table_width, int page_size,
+                                         int n_heads, int n_kv_heads, int head_dim, int write_cache,
+                                         int* __restrict__ status)
+{
+    constexpr int V = Pack<T>::N;
+    fx_pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    T* row = qkv + (long)t * ld;
+    const int half = head_dim >> 1;
+    long page_base = -1;
+    if (write_cache) {
+        const int slot = seq_slot[token_seq[t]];
+        const int page = block_table[(long)slot * table_width + pos / page_size];
+        if (page < 0) { if (threadIdx.x == 0 && status) atomicExch(status, 2); }
+        else page_base = ((long)page * n_kv_heads * page_size + (pos % page_size)) * head_dim;
+    }
+    const int cph = half / V;                       // vector chunks per half head
+    const int n_rot = (n_heads + n_kv_heads) * cph; // q and k heads: one item = a chunk of each half
+    const int n_v = n_kv_heads * (head_dim / V);    // v heads: plain copies into the pages
+    for (int idx = threadIdx.x; idx < n_rot + n_v; idx += blockDim.x) {
+        if (idx < n_rot) {
+            const int h = idx / cph, i = (idx - h * cph) * V;
+            T* x = row + (long)h * head_dim;
+            float a[V], b[V], ra[V], rb[V];
+            Pack<T>::load(x + i, a);
+            Pack<T>::load(x + i + half, b);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                float s, c;
+                if (inv_freq == nullptr) { s = 0.f; c = 1.f; }
+                else if (cos_sin) {
+                    const float2 cs = *reinterpret_cast<const float2*>(cos_sin + ((long)t * half + i + e) * 2);
+                    c = cs.x; s = cs.y;
+                } else {
+                    sincosf((float)pos * inv_freq[i + e], &s, &c);
+                }
+                ra[e] = a[e] * c - b[e] * s;
+                rb[e] = a[e] * s + b[e] * c;
+            }
+            if (inv_freq) { Pack<T>::store(x + i, ra); Pack<T>::store(x + i + half, rb); }
+            if (h >= n_heads && page_base >= 0) {
+                T* dst = k_pages + page_base + (long)(h - n_heads) * page_size * head_dim;
+                Pack<T>::store(dst + i, ra);
+                Pack<T>::store(dst + i + half, rb);
+            }
+        } else if (page_base >= 0) {
+            const int j = idx - n_rot;
+            const int h = j / (head_dim / V), i = (j - h * (head_dim / V)) * V;
+            const T* src = row + (long)(n_heads + n_kv_heads + h) * head_dim + i;
+            T* dst = v_pages + page_base + (long)h * page_size * head_dim + i;
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        }
+    }
+}
+
+// Expert combine, 16 bytes of y per thread and pass (hidden a multiple of the vector width).
+template <typename T>
+__global__ void moe_combine_vec_kernel(float* __restrict__ h, const T* __restrict__ y, const int* __restrict__ inv_perm,
+                                       const float* __restrict__ topk_w, int top_k,
+                                       const T* __restrict__ shared, const float* __restrict__ shared_gate_logit,
+                                       long gate_ld, int hidden)
+{
+    constexpr int V = Pack<T>::N;
+    fx_pdl_wait();
+    const int t = blockIdx.x;
+    float g = 1.f;
+    if (shared && shared_gate_logit) g = 1.0f / (1.0f + expf(-shared_gate_logit[(long)t * gate_ld]));
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * V; i < hidden; i += gridDim.y * blockDim.x * V) {
+        float acc[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = 0.f;
+        for (int k = 0; k < top_k; ++k) {
+            const long r = inv_perm[(long)t * top_k + k];
+            const float w = topk_w[(long)t * top_k + k];
+            float v[V];
+            Pack<T>::load(y + r * hidden + i, v);
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] = fmaf(w, v[e], acc[e]);
+        }
+        if (shared) {
+            float v[V];
+            Pack<T>::load(shared + (long)t * hidden + i, v);
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] = fmaf(g, v[e], acc[e]);
+        }
+        float* hp = h + (long)t * hidden + i;
+#pragma unroll
+        for (int e = 0; e < V; e += 4) {
+            float4 o = *reinterpret_cast<float4*>(hp + e);
+            o.x += acc[e]; o.y += acc[e + 1]; o.z += acc[e + 2]; o.w += acc[e + 3];
+            *reinterpret_cast<float4*>(hp + e) = o;
+        }
+    }
+}
+
 inline int threads_for(int n) { int t = 32; while (t < n && t < 1024) t <<= 1; return t; }
 
 }  // namespace
@@ -223,6 +400,14 @@ extern "C" int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_
     if (n_rows <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = threads_for(hidden / 4 > 32 ? hidden / 4 : 32);
+    const bool vec = hidden % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w % 16 == 0;
+    if (vec) {
+        const int vt = nt > 512 ? 512 : nt;
+        if (out_dtype == FX_F32) fx_launch_pdl(rmsnorm_vec_kernel<float>, n_rows, vt, 0, s, x, rows, w, w_dtype, eps, (float*)out, hidden);
+        else if (out_dtype == FX_BF16) fx_launch_pdl(rmsnorm_vec_kernel<bf16>, n_rows, vt, 0, s, x, rows, w, w_dtype, eps, (bf16*)out, hidden);
+        else return FX_ERR_DTYPE;
+        return fx_launch_status();
+    }
     if (out_dtype == FX_F32) fx_launch_pdl(rmsnorm_kernel<float>, n_rows, nt, 0, s, x, rows, w, w_dtype, eps, (float*)out, hidden);
     else if (out_dtype == FX_BF16) fx_launch_pdl(rmsnorm_kernel<bf16>, n_rows, nt, 0, s, x, rows, w, w_dtype, eps, (bf16*)out, hidden);
     else return FX_ERR_DTYPE;
@@ -253,6 +438,23 @@ extern "C" int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positi
     cudaStream_t s = (cudaStream_t)stream;
     const int work = (n_heads + n_kv_heads) * (head_dim / 2);
     const int nt = threads_for(work > 256 ? 256 : work);
+    const int vw = dtype == FX_F32 ? 4 : 8;
+    const int es = dtype == FX_F32 ? 4 : 2;
+    const bool vec = (rotary_dim == head_dim || inv_freq == nullptr) && (head_dim / 2) % vw == 0 && (ld * es) % 16 == 0 &&
+                     (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0;
+    if (vec && (dtype == FX_F32 || dtype == FX_BF16)) {
+        const int items = ((n_heads + n_kv_heads) * (head_dim / 2) + n_kv_heads * head_dim) / vw;
+        const int vt = threads_for(items > 256 ? 256 : items);
+        if (dtype == FX_F32)
+            fx_launch_pdl(rope_kv_write_vec_kernel<float>, n_tokens, vt, 0, s, (float*)qkv, ld, positions, token_seq, seq_slot,
+                          inv_freq, cos_sin, (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_heads,
+                          n_kv_heads, head_dim, write_cache, status);
+        else
+            fx_launch_pdl(rope_kv_write_vec_kernel<bf16>, n_tokens, vt, 0, s, (bf16*)qkv, ld, positions, token_seq, seq_slot,
+                          inv_freq, cos_sin, (bf16*)k_pages, (bf16*)v_pages, block_table, table_width, page_size, n_heads,
+                          n_kv_heads, head_dim, write_cache, status);
+        return fx_launch_status();
+    }
     if (dtype == FX_F32)
         fx_launch_pdl(rope_kv_write_kernel<float>, n_tokens, nt, 0, s, (float*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
             cos_sin, rotary_dim, (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
@@ -276,19 +478,32 @@ extern "C" int fx_rope_table(const int* positions, const float* inv_freq, int n_
 }
 
 extern "C" int fx_moe_combine(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w, int top_k,
-                              const void* shared, const float* shared_gate_logit, int n_tokens, int hidden,
-                              void* stream)
+                              const void* shared, const float* shared_gate_logit, long gate_ld, int n_tokens,
+                              int hidden, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = threads_for(hidden > 128 ? 128 : hidden);
     const dim3 grid(n_tokens, (unsigned)fx_cdiv(hidden, nt));
+    const int vw = dtype == FX_F32 ? 4 : 8;
+    if (hidden % vw == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)shared % 16 == 0 &&
+        (dtype == FX_F32 || dtype == FX_BF16)) {
+        const int vt = threads_for(hidden / vw > 128 ? 128 : hidden / vw);
+        const dim3 vgrid(n_tokens, (unsigned)fx_cdiv(hidden / vw, vt));
+        if (dtype == FX_F32)
+            fx_launch_pdl(moe_combine_vec_kernel<float>, vgrid, vt, 0, s, h, (const float*)y, inv_perm, topk_w, top_k,
+                          (const float*)shared, shared_gate_logit, gate_ld, hidden);
+        else
+            fx_launch_pdl(moe_combine_vec_kernel<bf16>, vgrid, vt, 0, s, h, (const bf16*)y, inv_perm, topk_w, top_k,
+                          (const bf16*)shared, shared_gate_logit, gate_ld, hidden);
+        return fx_launch_status();
+    }
     if (dtype == FX_F32)
         fx_launch_pdl(moe_combine_kernel<float>, grid, nt, 0, s, h, (const float*)y, inv_perm, topk_w, top_k,
-                                                      (const float*)shared, shared_gate_logit, hidden);
+                                                      (const float*)shared, shared_gate_logit, gate_ld, hidden);
     else if (dtype == FX_BF16)
         fx_launch_pdl(moe_combine_kernel<bf16>, grid, nt, 0, s, h, (const bf16*)y, inv_perm, topk_w, top_k,
-                                                     (const bf16*)shared, shared_gate_logit, hidden);
+                                                     (const bf16*)shared, shared_gate_logit, gate_ld, hidden);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

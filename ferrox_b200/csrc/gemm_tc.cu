@@ -181,6 +181,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     __shared__ int cum_s[MAX_GROUPS + 1];        // grouped: row tiles before each group
     __shared__ int abort_flag_s;
     __shared__ uint32_t tmem_base_s;
+    __shared__ __align__(16) float bias_s[4][OUT_N];   // each epilogue warp keeps the tile's bias for itself
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (a.N + OUT_N - 1) / OUT_N;
@@ -299,6 +300,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
             const int buf = it & 1;
             const int row = tc.m0 + quad * 32 + lane;
             // tcgen05.ld needs whole warps: agree on the outcome of the wait
+            if (a.bias) {   // the bias of this tile's columns, once per warp (no barrier between warps)
+                __syncwarp();
+                for (int j = lane; j < OUT_N; j += 32)
+                    bias_s[quad][j] = tc.n0 + j < a.N ? load_any(a.bias, a.bias_dtype, tc.n0 + j) : 0.f;
+                __syncwarp();
+            }
             const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (uint32_t)((it >> 1) & 1), abort_flag));
             if (!ok) break;
             tc_fence_after();
@@ -322,7 +329,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     float x = __uint_as_float(r[j]);
-                    if (a.bias && nb + j < a.N) x += load_any(a.bias, a.bias_dtype, nb + j);
+                    if (a.bias) x += bias_s[quad][c * 32 + j];
                     if (GATED) x = x / (1.0f + __expf(-x)) * __uint_as_float(u[j]);
                     v[j] = x;
                 }

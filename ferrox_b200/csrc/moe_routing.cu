@@ -45,14 +45,14 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
     }
 }
 
-__global__ void router_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, int renorm,
-                                   int* __restrict__ ids, float* __restrict__ weights)
+__global__ void router_topk_kernel(const float* __restrict__ logits, long ld, int n_tokens, int n_experts, int top_k,
+                                   int renorm, int* __restrict__ ids, float* __restrict__ weights)
 {
     extern __shared__ float smem[];  // [warps][n_experts]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= n_tokens) return;
-    route_token(logits + (long)t * n_experts, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
+    route_token(logits + (long)t * ld, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
                 weights);
 }
 
@@ -61,8 +61,8 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int n_token
 // of every (token, rank) pair, all in shared memory.
 constexpr int SMALL_WARPS = 16;
 __global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
-    const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, int renorm, int* __restrict__ ids,
-    float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ src_token, int* __restrict__ inv_perm,
+    const float* __restrict__ logits, long ld, int n_tokens, int n_experts, int top_k, int renorm,
+    int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ src_token, int* __restrict__ inv_perm,
     int* __restrict__ active, int n_slots)
 {
     extern __shared__ float smem[];  // [SMALL_WARPS][n_experts] floats, then 2 * n_experts + 1 ints
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
     for (int t = warp; t < n_tokens; t += SMALL_WARPS) {
-        route_token(logits + (long)t * n_experts, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
+        route_token(logits + (long)t * ld, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
                     weights);
         __syncwarp();
     }
@@ -142,7 +142,7 @@ __global__ void place_kernel(const int* __restrict__ ids, int n, int n_experts, 
 
 }  // namespace
 
-extern "C" int fx_router_topk(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
+extern "C" int fx_router_topk(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
                               float* weights, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
@@ -151,12 +151,12 @@ extern "C" int fx_router_topk(const float* logits, int n_tokens, int n_experts, 
     const size_t smem = (size_t)warps * n_experts * sizeof(float);
     if (smem > 48 * 1024) return FX_ERR_SIZE;
     router_topk_kernel<<<(unsigned)fx_cdiv(n_tokens, warps), warps * 32, smem, (cudaStream_t)stream>>>(
-        logits, n_tokens, n_experts, top_k, renorm, ids, weights);
+        logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights);
     return fx_launch_status();
 }
 
 // Routing of at most 1024 tokens in one launch (see route_small_kernel).
-extern "C" int fx_route_small(const float* logits, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
+extern "C" int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
                               float* weights, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots,
                               void* stream)
 {
@@ -165,7 +165,7 @@ extern "C" int fx_route_small(const float* logits, int n_tokens, int n_experts, 
     const size_t smem = (size_t)SMALL_WARPS * n_experts * sizeof(float) + (2 * (size_t)n_experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return FX_ERR_SIZE;
     fx_launch_pdl(route_small_kernel, 1, SMALL_WARPS * 32, smem, (cudaStream_t)stream,
-        logits, n_tokens, n_experts, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active, n_slots);
+        logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active, n_slots);
     return fx_launch_status();
 }
 

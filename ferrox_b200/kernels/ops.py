@@ -41,12 +41,12 @@ _SIGNATURES = {
     "fx_rope_table": [_P, _P, _I, _I, _P, _P],
     "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
-    "fx_route_small": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
-    "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _P],
+    "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
+    "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P],
-    "fx_router_topk": [_P, _I, _I, _I, _I, _P, _P, _P],
+    "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P],
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P],
     "fx_decode_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
@@ -184,10 +184,11 @@ def rope_table(positions, inv_freq, out, stream=None):
     return out
 
 
-def route_small(logits, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active=None, stream=None):
+def route_small(logits, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active=None, n_experts=None,
+                stream=None):
     """router_topk and moe_align of a small step (at most 1024 tokens) in one launch."""
-    T, E = logits.shape
-    call("fx_route_small", _ptr(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights), _ptr(offsets),
+    T, E = logits.shape[0], (n_experts or logits.shape[1])
+    call("fx_route_small", _ptr(logits), _rows(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights), _ptr(offsets),
          _ptr(src_token), _ptr(inv_perm), _ptr(active), active.numel() if active is not None else 0,
          stream if stream is not None else stream_ptr())
 
@@ -225,9 +226,10 @@ def prefill_attention(q, k_pages, v_pages, block_table, page_size, tiles, seq_sl
     return out
 
 
-def router_topk(logits, top_k, renorm, ids, weights, stream=None):
-    T, E = logits.shape
-    call("fx_router_topk", _ptr(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights),
+def router_topk(logits, top_k, renorm, ids, weights, n_experts=None, stream=None):
+    """``n_experts``: the first columns of ``logits`` that are router logits (default: all)."""
+    T, E = logits.shape[0], (n_experts or logits.shape[1])
+    call("fx_router_topk", _ptr(logits), _rows(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights),
          stream if stream is not None else stream_ptr())
 
 
@@ -333,7 +335,7 @@ def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None):
 def moe_combine(h, y, inv_perm, topk_w, shared=None, shared_gate_logit=None, stream=None):
     T, H = h.shape
     call("fx_moe_combine", _ptr(h), _ptr(y), code(y), _ptr(inv_perm), _ptr(topk_w), topk_w.shape[1], _ptr(shared),
-         _ptr(shared_gate_logit), T, H, stream if stream is not None else stream_ptr())
+         _ptr(shared_gate_logit), shared_gate_logit.stride(0) if shared_gate_logit is not None else 0, T, H, stream if stream is not None else stream_ptr())
 
 
 def residual_add(h, y, stream=None):

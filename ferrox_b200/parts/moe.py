@@ -65,6 +65,11 @@ class SoftmaxTopkMoe(FeedForward):
             self.w_shared_down = src.get(p + "shared_expert.down_proj.weight")
             if s.shared_gate and src.has(p + "shared_expert_gate.weight"):
                 self.w_shared_gate = src.get(p + "shared_expert_gate.weight").reshape(1, H).contiguous()
+        # router rows and the shared expert's gate row share one product: [E (+1), H]
+        self.w_route = self.w_router
+        if self.w_shared_gate is not None:
+            dtr = torch.float32 if torch.float32 in (self.w_router.dtype, self.w_shared_gate.dtype) else self.w_router.dtype
+            self.w_route = torch.cat([self.w_router.to(dtr), self.w_shared_gate.to(dtr)], dim=0).contiguous()
         self._scratch = torch.zeros(2 * E, dtype=torch.int32, device=rt.device)
 
     def forward_add(self, x, h, batch):
@@ -73,8 +78,9 @@ class SoftmaxTopkMoe(FeedForward):
         i32 = torch.int32
         small = T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
         big = T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_gu) and I % 8 == 0
-        logits = rt.empty(T, E, dtype=torch.float32)
-        ops.linear(x, self.w_router, logits, status=batch.status, stream=st)
+        n_route = self.w_route.shape[0]      # E router logits, then the shared expert's gate logit if it has one
+        logits = rt.empty(T, n_route, dtype=torch.float32)
+        ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
         ids = rt.empty(T, K, dtype=i32)
         weights = rt.empty(T, K, dtype=torch.float32)
         offsets = rt.empty(E + 1, dtype=i32)
@@ -82,9 +88,10 @@ class SoftmaxTopkMoe(FeedForward):
         inv_perm = rt.empty(T * K, dtype=i32)
         active = rt.empty(min(E, T * K), dtype=i32) if small else None
         if T <= 256 and E <= 512:
-            ops.route_small(logits, K, s.norm_topk_prob, ids, weights, offsets, src_token, inv_perm, active, stream=st)
+            ops.route_small(logits, K, s.norm_topk_prob, ids, weights, offsets, src_token, inv_perm, active,
+                            n_experts=E, stream=st)
         else:
-            ops.router_topk(logits, K, s.norm_topk_prob, ids, weights, stream=st)
+            ops.router_topk(logits, K, s.norm_topk_prob, ids, weights, n_experts=E, stream=st)
             ops.moe_align(ids, E, self._scratch, offsets, src_token, inv_perm, active, stream=st)
 
         act = rt.empty(T * K, I)
@@ -121,8 +128,7 @@ class SoftmaxTopkMoe(FeedForward):
             shared = rt.empty(T, H)
             ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
             if self.w_shared_gate is not None:
-                gate_logit = rt.empty(T, 1, dtype=torch.float32)
-                ops.linear(x, self.w_shared_gate, gate_logit, status=batch.status, stream=st)
+                gate_logit = logits[:, E:]      # [T, 1] view with the logits' row stride
         ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st)
 
 
