@@ -89,8 +89,34 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
         const bf16* src = q + (long)(tok0 + min(r, rows - 1)) * ldq + (long)head * head_dim + ch * 8;
         cp_async16(q_u + r * pitch + ch * 16, src, r < rows ? 16 : 0);
     }
+    // A thread always copies the same 16-byte column of several rows: (row, column) is found once.  When a
+    // block of keys lies inside one page (page_size a multiple of 64), one table lookup serves the block.
+    const bool lanes_fit = chunks <= NTHREADS && NTHREADS % chunks == 0;
+    const int my_ch = lanes_fit ? threadIdx.x % chunks : 0;
+    const int my_r0 = lanes_fit ? threadIdx.x / chunks : 0;
+    const int rows_per_pass = lanes_fit ? NTHREADS / chunks : 1;
+    const bool block_in_page = page_size % BKEY == 0;
     auto load_kv = [&](int blk, int buf) {
         const int kb = kb_begin + blk * BKEY;
+        if (lanes_fit) {
+            int page_blk = -1;
+            if (block_in_page) page_blk = table[kb / page_size];
+            const int off_blk = kb % page_size;
+            for (int r = my_r0; r < BKEY; r += rows_per_pass) {
+                const int key = kb + r;
+                int page = -1, off = 0;
+                if (key <= last_pos && key >= key_lo) {
+                    if (block_in_page) { page = page_blk; off = off_blk + r; }
+                    else { page = table[key / page_size]; off = key % page_size; }
+                }
+                const bool ok = page >= 0;
+                const long base = ok ? ((long)page * n_kv_heads + kvh) * head_stride + (long)off * head_dim + my_ch * 8 : 0;
+                const uint32_t dst = (buf * BKEY + r) * pitch + my_ch * 16;
+                cp_async16(k_u + dst, k_pages + base, ok ? 16 : 0);
+                cp_async16(v_u + dst, v_pages + base, ok ? 16 : 0);
+            }
+            return;
+        }
         for (int c = threadIdx.x; c < BKEY * chunks; c += NTHREADS) {
             const int r = c / chunks, ch = c - r * chunks;
             const int key = kb + r;
