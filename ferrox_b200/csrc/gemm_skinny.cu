@@ -66,24 +66,27 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
 {
     constexpr bool GATED = MODE != 0;   // a second set of 16 rows is streamed beside the first
     constexpr int UNROLL = (GATED ? 4 : 8) / (NT > 2 ? 2 : 1);
+    constexpr int RPB = MODE == 2 ? 32 : 16;   // output features per tile
     __shared__ float red[WARPS][GATED ? 2 : 1][NT][16][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * (MODE == 2 ? 32 : 16);
     const int n_chunks = a.K >> 5;
     const bool grouped = a.group_offsets != nullptr;
-    // rows of W this lane reads: g and g+8 of the tile (clamped; masked at the store)
-    const long o0 = (long)min(n0 + g, a.N - 1) * a.ldw + t * 8;
-    const long o1 = (long)min(n0 + g + 8, a.N - 1) * a.ldw + t * 8;
-    long p0 = 0, p1 = 0;   // the second set of rows
-    if (MODE == 1) { p0 = o0 + (long)a.gate_up_offset * a.ldw; p1 = o1 + (long)a.gate_up_offset * a.ldw; }
-    if (MODE == 2) {
-        p0 = (long)min(n0 + 16 + g, a.N - 1) * a.ldw + t * 8;
-        p1 = (long)min(n0 + 24 + g, a.N - 1) * a.ldw + t * 8;
-    }
+    const int tiles_n = (a.N + RPB - 1) / RPB;
+    const int total = tiles_n * (grouped ? a.n_slots : 1);
 
+    // One pass = UNROLL chunks of this warp, of the 16 (+16) rows of a tile, into registers.
     uint4 wa[UNROLL], wb[UNROLL], ua[UNROLL], ub[UNROLL];
-    auto load_pass = [&](const bf16* W, int i0) {
+    auto load_pass = [&](const bf16* W, int n0, int i0) {
+        // rows of W this lane reads: g and g+8 of the tile (clamped; masked at the store)
+        const long o0 = (long)min(n0 + g, a.N - 1) * a.ldw + t * 8;
+        const long o1 = (long)min(n0 + g + 8, a.N - 1) * a.ldw + t * 8;
+        long p0 = 0, p1 = 0;   // the second set of rows
+        if (MODE == 1) { p0 = o0 + (long)a.gate_up_offset * a.ldw; p1 = o1 + (long)a.gate_up_offset * a.ldw; }
+        if (MODE == 2) {
+            p0 = (long)min(n0 + 16 + g, a.N - 1) * a.ldw + t * 8;
+            p1 = (long)min(n0 + 24 + g, a.N - 1) * a.ldw + t * 8;
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int c = warp + WARPS * (i0 + u);
@@ -94,24 +97,36 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
             }
         }
     };
+    // the matrix a tile reads (nullptr: no such tile)
+    auto tile_matrix = [&](int idx) -> const bf16* {
+        if (idx >= total) return nullptr;
+        if (!grouped) return a.W;
+        const int e = a.active_groups[idx / tiles_n];
+        return e < 0 ? nullptr : a.W + (long)e * a.w_group_stride;
+    };
 
+    // The first pass of the first tile: in the plain form it does not depend on the kernel before this one.
     bool have_first = false;
-    if (!grouped) { load_pass(a.W, 0); have_first = true; }   // independent of the kernel before this one
+    if (!grouped && (int)blockIdx.x < total) { load_pass(a.W, (blockIdx.x % tiles_n) * RPB, 0); have_first = true; }
     fx_pdl_wait();
 
-    for (int slot = grouped ? blockIdx.y : 0; slot < (grouped ? a.n_slots : 1); slot += grouped ? gridDim.y : 1) {
+    for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {
+        const int slot = idx / tiles_n, n0 = (idx - slot * tiles_n) * RPB;
         int row_begin = 0, row_end = a.n_tokens;
         const bf16* W = a.W;
         if (grouped) {
             const int e = a.active_groups[slot];
             if (e < 0) break;   // the list is compact: nothing after the first -1
             W += (long)e * a.w_group_stride;
-            load_pass(W, 0);
-            have_first = true;
+            if (!have_first) { load_pass(W, n0, 0); have_first = true; }
             row_begin = a.group_offsets[e];
             row_end = a.group_offsets[e + 1];
+        } else if (!have_first) {
+            load_pass(W, n0, 0);
+            have_first = true;
         }
         for (int tok0 = row_begin; tok0 < row_end; tok0 += 8 * NT) {
+            const bool last_tokens = tok0 + 8 * NT >= row_end;
             // token rows this lane reads for the B operand: token g of each n-tile
             const bf16* xp[NT];
 #pragma unroll
@@ -131,7 +146,7 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
             // together and share the chunks evenly whatever K is; a warp issues the loads of UNROLL of its
             // chunks before it uses the first.
             for (int i0 = 0; warp + WARPS * i0 < n_chunks; i0 += UNROLL) {
-                if (!(have_first && i0 == 0)) load_pass(W, i0);
+                if (!(have_first && i0 == 0)) load_pass(W, n0, i0);
                 have_first = false;
 #pragma unroll
                 for (int u = 0; u < UNROLL; ++u) {
@@ -151,6 +166,12 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
                 }
             }
             have_first = false;
+            if (last_tokens) {
+                // the weights of this block's next tile start to arrive while this tile is reduced and stored
+                const int nidx = idx + gridDim.x;
+                const bf16* Wn = tile_matrix(nidx);
+                if (Wn) { load_pass(Wn, (nidx % tiles_n) * RPB, 0); have_first = true; }
+            }
             // partial sums of this warp -> shared memory: [row g | g+8][token 2t | 2t+1]
             __syncthreads();  // the previous reduction has been read
 #pragma unroll
@@ -234,8 +255,10 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
     const int slots = group_offsets ? n_slots : 1;
     // wide matrices: 32 features per block, so that half as many blocks pay the start-up latency
     const bool two_tiles = !gated && fx_cdiv(N, 32) * slots >= 2 * 148;
-    dim3 grid((unsigned)fx_cdiv(N, two_tiles ? 32 : 16), slots);
-    if (grid.y > 65535u) return FX_ERR_SIZE;
+    // Two resident blocks per SM walk the tiles (expert slot major, then feature tile); a block fetches its
+    // next tile's weights while it finishes the current one.
+    long tiles = fx_cdiv(N, two_tiles ? 32 : 16) * (long)slots;
+    dim3 grid((unsigned)(tiles < 2 * 148 ? tiles : 2 * 148), 1);
     const int hint = group_offsets ? tokens_hint : n_tokens;
     cudaStream_t s = (cudaStream_t)stream;
     if (gated) return launch_nt<1>(a, hint, grid, s);
