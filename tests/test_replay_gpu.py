@@ -119,3 +119,42 @@ def test_cutting_changes_nothing_beyond_rounding_fp32(folders, name):
     for rid in prompts:
         assert ru.max_rel_err(b[rid], a[rid]) < 2e-6
         assert ru.max_rel_err(c[rid], a[rid]) < 2e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_every_token_decoded_one_by_one(folders, expected, dtype):
+    """Long decoding: pages roll over, and on B the window leaves pages behind many times."""
+    for name in ("A", "B"):
+        eng = engine(folders[name], dtype, page_size=4, n_pages=32, max_slots=2)
+        got = ru.run_tail_decode(eng, prompts_for(name), tail=10 ** 6)
+        compare(got, expected[name], TOL[dtype], f"decode-all/{name}/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tensors_stored_in_32_bits_stay_so(tmp_path, dtype):
+    """A folder whose tensors are float32: the bfloat16 engine keeps them in 32 bits
+    (products then run on the CUDA-core kernel with 32-bit weights)."""
+    folder = make_folder(tmp_path, "B", dtype="float32")
+    prompts = prompts_for("B", n=4)
+    want = ru.Expected(folder, prompts)
+    eng = engine(folder, dtype, page_size=16, n_pages=16, max_slots=4)
+    if dtype == "bfloat16":
+        assert eng.model.layers[1].ffn.w_gu.dtype == torch.float32 and eng.model.embedding.dtype == torch.float32
+    compare(ru.run_portions(eng, prompts), want, TOL[dtype], f"stored32/B/{dtype}")
+
+
+def test_dense_only_model_and_first_tokens(tmp_path):
+    """No experts at all; and the very first positions of a sequence, one token at a time from position 0."""
+    from ferrox_b200 import write_random_model
+    from tiny_configs import TINY_A
+
+    cfg = dict(TINY_A, num_experts=0, num_experts_per_tok=0, moe_intermediate_size=0, shared_expert_intermediate_size=0,
+               intermediate_size=72, hidden_size=48, num_attention_heads=3, num_key_value_heads=3, head_dim=16)
+    folder = write_random_model(str(tmp_path / "dense"), cfg, seed=9, norm_init="around_one")
+    prompts = {"a": [7, 3, 250, 9, 11, 2, 5], "b": [1]}
+    want = ru.Expected(folder, prompts)
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(folder, dtype, page_size=4, n_pages=8, max_slots=2)
+        assert all(type(l.ffn).__name__ == "SwigluMlp" for l in eng.model.layers)
+        compare(ru.run_tail_decode(eng, prompts, tail=10 ** 6), want, TOL[dtype], f"dense/first-tokens/{dtype}")
+        compare(ru.run_whole(eng, prompts), want, TOL[dtype], f"dense/whole/{dtype}")
