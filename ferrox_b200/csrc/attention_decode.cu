@@ -315,6 +315,18 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, const
     constexpr int N = Vec<T>::N;
     if (head_dim % N || head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
     if (ldq % N || (uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16) return FX_ERR_ALIGN;
+    if (sizeof(T) == 2) {
+        // bfloat16: the tensor-core kernel writes the same partial results; the merge below is shared
+        const int rc_mma = fx_decode_split_mma(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions,
+                                               token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads, n_kv_heads,
+                                               head_dim, window, scale, split_len, n_splits, (void*)s);
+        if (rc_mma == FX_OK) {
+            fx_launch_pdl(merge_kernel<T>, dim3(n_tokens, n_heads), 64, 0, s, part_acc, part_ml, positions, (T*)out, ldo,
+                          n_heads, head_dim, n_splits, split_len, window);
+            return fx_launch_status();
+        }
+        if (rc_mma > 0) return rc_mma;   // a CUDA error; a refusal (< 0) falls through to the CUDA-core kernel
+    }
     const int group = n_heads / n_kv_heads;
     int gq = 1;
     while (gq < group && gq < MAXQ) gq <<= 1;
