@@ -54,7 +54,7 @@ int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int
 int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, long ldw, long w_group_stride,
                    const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int n_tokens,
                    int N, int K, int gated, int gate_up_offset, const int* group_offsets, const int* active_groups,
-                   int n_slots, int tokens_hint, void* stream);
+                   int n_slots, int tokens_hint, int c_transposed, void* stream);
 int fx_decode_split_mma(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table,
                         int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot,
                         float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim,

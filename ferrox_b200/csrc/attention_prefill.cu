@@ -24,7 +24,7 @@
 
 namespace {
 
-constexpr int BQ = 64, BKEY = 64, NWARPS = 4, NTHREADS = NWARPS * 32;
+constexpr int BQ = 64, BKEY = 32, NWARPS = 4, NTHREADS = NWARPS * 32;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");

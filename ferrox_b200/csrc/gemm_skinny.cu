@@ -47,6 +47,7 @@ struct SkinnyArgs {
     const bf16* X; long ldx; const int* x_rows;
     const void* bias; int bias_dtype;
     void* C; long ldc; int c_dtype; int accumulate;
+    int c_transposed;              // store C[n][r] instead of C[r][n] (ldc is then the pitch of a feature's row)
     int n_tokens; int N; int K;
     int gate_up_offset;            // gated form: row of `up` matching gate row i is i + gate_up_offset
     const int* group_offsets;      // grouped form: rows [off[e], off[e+1]) belong to expert e
@@ -199,11 +200,12 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
                 if (a.bias) v += load_any(a.bias, a.bias_dtype, n);
                 if (MODE == 1) v = v / (1.0f + expf(-v)) * up;
                 auto store = [&](int col, float val) {
+                    const long at = a.c_transposed ? (long)col * a.ldc + r : (long)r * a.ldc + col;
                     if (a.c_dtype == FX_F32) {
-                        float* c = reinterpret_cast<float*>(a.C) + (long)r * a.ldc + col;
+                        float* c = reinterpret_cast<float*>(a.C) + at;
                         *c = a.accumulate ? *c + val : val;
                     } else {
-                        bf16* c = reinterpret_cast<bf16*>(a.C) + (long)r * a.ldc + col;
+                        bf16* c = reinterpret_cast<bf16*>(a.C) + at;
                         *c = __float2bfloat16_rn(a.accumulate ? __bfloat162float(*c) + val : val);
                     }
                 };
@@ -237,7 +239,7 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
                               const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate,
                               int n_tokens, int N, int K, int gated, int gate_up_offset,
                               const int* group_offsets, const int* active_groups, int n_slots, int tokens_hint,
-                              void* stream)
+                              int c_transposed, void* stream)
 {
     if (n_tokens <= 0 || N <= 0) return FX_OK;
     if (K % 32 != 0 || K <= 0) return FX_ERR_SIZE;
@@ -247,7 +249,7 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
     a.W = (const bf16*)W; a.ldw = ldw; a.w_group_stride = w_group_stride;
     a.X = (const bf16*)X; a.ldx = ldx; a.x_rows = x_rows;
     a.bias = bias; a.bias_dtype = bias_dtype;
-    a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
+    a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate; a.c_transposed = c_transposed;
     a.n_tokens = n_tokens; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset;
     a.group_offsets = group_offsets; a.active_groups = active_groups; a.n_slots = n_slots;
     // grouped: one block row per expert slot (many short blocks hide each other's start-up better than

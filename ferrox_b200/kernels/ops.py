@@ -48,7 +48,7 @@ _SIGNATURES = {
     "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P],
     "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P],
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
-    "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P],
+    "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "fx_decode_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
                             _I, _P],
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
@@ -251,11 +251,11 @@ def skinny_ok(x, w) -> bool:
 
 
 def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=None, group_offsets=None,
-                active_groups=None, tokens_hint=0, stream=None):
+                active_groups=None, tokens_hint=0, transposed_out=False, stream=None):
     """out[rows, N] (+)= x . w^T for few rows: streams ``w`` once.  ``gated``: ``w`` is
     [gate rows ; up rows] (2N rows) and out = silu(gate) * up.  Grouped: ``w`` is
     [G, rows, K], ``group_offsets``/``active_groups`` come from :func:`moe_align`."""
-    rows, N = out.shape
+    rows, N = (out.shape[1], out.shape[0]) if transposed_out else out.shape   # transposed: out is [N, rows]
     K = x.shape[1]
     if group_offsets is not None:
         wrows, wstride, ldw = w.shape[1], w.stride(0), w.stride(1)
@@ -268,7 +268,7 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
     call("fx_gemm_skinny", _ptr(x), _rows(x), _ptr(x_rows), _ptr(w), ldw, wstride, _ptr(bias),
          code(bias) if bias is not None else 0, _ptr(out), code(out), _rows(out), int(accumulate), rows, N, K,
          int(gated), N if gated else 0, _ptr(group_offsets), _ptr(active_groups), n_slots, int(tokens_hint),
-         stream if stream is not None else stream_ptr())
+         int(transposed_out), stream if stream is not None else stream_ptr())
     return out
 
 
@@ -325,6 +325,10 @@ def gather_rows(x, rows, out, stream=None):
 
 def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None):
     """out (+)= x . w^T (+ bias): picks the kernel by size and element type."""
+    if (x.shape[0] > SKINNY_MAX_TOKENS and w.shape[0] <= SKINNY_MAX_TOKENS and bias is None and skinny_ok(w, x)):
+        # many tokens, a narrow output (router logits): the weight-streaming kernel with the roles swapped,
+        # x streamed once as the "matrix", w as the few "tokens", stored transposed
+        return gemm_skinny(w, x, out, accumulate=accumulate, transposed_out=True, stream=stream)
     if x.shape[0] <= SKINNY_MAX_TOKENS and skinny_ok(x, w):
         return gemm_skinny(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
     if x.shape[0] > SKINNY_MAX_TOKENS and tc_ok(x, w):

@@ -534,3 +534,16 @@ def test_prefill_attention_tiles(case):
         s, pos = toks[i]
         want = plain_attention(q[i, : nh * d].float().cpu().reshape(nh, d), ks[s], vs[s], pos, window, scale)
         assert rel(out[i].float().cpu().reshape(nh, d), want) < 1.5e-2, (i, s, pos)
+
+
+def test_gemm_skinny_transposed_store_and_linear_picks_it_for_narrow_outputs():
+    o = ops()
+    T, N, K = 300, 61, 256
+    x, w = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1)
+    want = x.float() @ w.float().T
+    out = torch.full((T, N), 7.0, device=DEV)
+    o.gemm_skinny(w, x, out, transposed_out=True)   # roles swapped: w is the few "tokens", x the streamed matrix
+    assert rel(out, want) < 2e-5
+    wide = torch.full((T, N + 3), 7.0, device=DEV)   # a view with a row pitch of its own
+    o.linear(x, w, wide[:, :N])
+    assert rel(wide[:, :N], want) < 2e-5 and float(wide[:, N:].min()) == 7.0
