@@ -12,6 +12,9 @@ groups of layers with different needs, and slots for per-request state of fixed 
 * A request holds a **slot**: the row of its block tables and the index of its
   state in every :class:`StateSpec` tensor ([max_slots, *shape], zeroed at
   admission).  Freed pages and slots are used again, most recently freed first.
+* The bookkeeping (free lists, tables, held ranges, window release, invariants) is
+  native code (``csrc/host/cache_core.cpp``); this module owns the device tensors and
+  the copies of changed table rows to the device.
 * ``reserve`` either gets every page the request needs up to a new length, in every
   group, or changes nothing and returns False; what to do then is the scheduler's
   decision.
@@ -25,6 +28,7 @@ window release are this engine's own.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
@@ -36,37 +40,6 @@ from .specs import CacheSpec
 
 class CacheError(RuntimeError):
     pass
-
-
-class PagePool:
-    """Page ids 0..n-1 with a LIFO free list.  ``alloc`` is all-or-nothing."""
-
-    def __init__(self, n_pages: int):
-        self.n_pages = int(n_pages)
-        self._free: List[int] = list(range(self.n_pages - 1, -1, -1))  # pop() hands out ascending ids first
-        self._held = bytearray(self.n_pages)
-
-    @property
-    def n_free(self) -> int:
-        return len(self._free)
-
-    def alloc(self, n: int) -> Optional[List[int]]:
-        if n > len(self._free):
-            return None
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            self._held[p] = 1
-        return out
-
-    def free(self, pages: Sequence[int]) -> None:
-        for p in pages:
-            if not 0 <= p < self.n_pages or not self._held[p]:
-                raise CacheError(f"page {p} freed but not held")
-            self._held[p] = 0
-            self._free.append(p)
-
-    def held(self) -> int:
-        return self.n_pages - len(self._free)
 
 
 @dataclass
@@ -82,16 +55,43 @@ class LayerCache:
     window: Optional[int] = None
 
 
+_CHECKS = {
+    1: "a page is mapped outside a live request's held range", 2: "a hole in a request's held range",
+    3: "a page is held twice", 4: "a mapped page is not marked held", 5: "a page is on the free list twice",
+    6: "a mapped page is on the free list", 7: "a page is lost",
+}
+
+
+class _PoolView:
+    """Numbers of one group's page pool (the pool itself lives in the native library)."""
+
+    def __init__(self, mgr, index, n_pages):
+        self._mgr, self._index, self.n_pages = mgr, index, n_pages
+
+    @property
+    def n_free(self) -> int:
+        return self._mgr._lib.fxh_free_pages(self._mgr._h, self._index)
+
+    def held(self) -> int:
+        return self.n_pages - self.n_free
+
+
 class _Group:
-    def __init__(self, window, n_pages, max_slots, width, device):
+    def __init__(self, mgr, index, window, n_pages, max_slots, width, device):
+        self.index = index
         self.window = window
         self.caches: List[int] = []
-        self.pool = PagePool(n_pages)
-        self.table = np.full((max_slots, width), -1, dtype=np.int32)
+        self.pool = _PoolView(mgr, index, n_pages)
         self.table_dev = torch.full((max_slots, width), -1, dtype=torch.int32, device=device)
-        self.first_page = [0] * max_slots  # first logical page still held
-        self.n_logical = [0] * max_slots  # logical pages ever mapped (held or given back)
-        self.dirty = set()
+        self.table: np.ndarray = None  # view of the native table, set once the native object exists
+
+
+class _SeqLens:
+    def __init__(self, mgr):
+        self._mgr = mgr
+
+    def __getitem__(self, slot: int) -> int:
+        return self._mgr._lib.fxh_seq_len(self._mgr._h, int(slot))
 
 
 class CacheManager:
@@ -107,8 +107,11 @@ class CacheManager:
         dtype: torch.dtype,
     ):
         """``n_pages``: pages per group (an int for all groups, or {window: n})."""
+        from ..kernels import hostlib
+
         if page_size <= 0:
             raise CacheError("page_size must be positive")
+        self._lib = hostlib.load()
         self.page_size = int(page_size)
         self.max_slots = int(max_slots)
         self.max_positions = int(max_positions)
@@ -127,7 +130,7 @@ class CacheManager:
                 key = cs.kv.window
                 if key not in self.groups:
                     n = n_pages[key] if isinstance(n_pages, dict) else int(n_pages)
-                    self.groups[key] = _Group(key, n, self.max_slots, self.table_width, self.device)
+                    self.groups[key] = _Group(self, len(self.groups), key, n, self.max_slots, self.table_width, self.device)
                 g = self.groups[key]
                 g.caches.append(idx)
                 shape = (g.pool.n_pages, cs.kv.n_kv_heads, self.page_size, cs.kv.head_dim)
@@ -139,23 +142,37 @@ class CacheManager:
             self._k.append(k)
             self._v.append(v)
             self._state.append(st)
-        self._free_slots: List[int] = list(range(self.max_slots - 1, -1, -1))
-        self._live = bytearray(self.max_slots)
-        self.seq_len = [0] * self.max_slots
-        self.peak_pages = {key: 0 for key in self.groups}
+        order = sorted(self.groups.values(), key=lambda g: g.index)
+        windows = (ctypes.c_int * max(1, len(order)))(*[-1 if g.window is None else int(g.window) for g in order])
+        pages = (ctypes.c_int * max(1, len(order)))(*[g.pool.n_pages for g in order])
+        self._h = self._lib.fxh_cache_create(len(order), windows, pages, self.page_size, self.max_slots, self.table_width,
+                                            self.max_positions)
+        if not self._h:
+            raise CacheError("the native cache object could not be made")
+        for g in order:
+            g.table = np.ctypeslib.as_array(self._lib.fxh_table(self._h, g.index), shape=(self.max_slots, self.table_width))
+        self._order = order
+        self._need = (ctypes.c_int * max(1, len(order)))()
+        self._dirty = (ctypes.c_int * self.max_slots)()
+        self.seq_len = _SeqLens(self)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            for g in getattr(self, "_order", []):
+                g.table = None
+            self._lib.fxh_cache_destroy(h)
 
     # ---- requests -------------------------------------------------------------
     @property
     def n_free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.fxh_free_slots(self._h)
 
     def open_request(self) -> Optional[int]:
         """A slot for a new request (its state zeroed), or None when all are taken."""
-        if not self._free_slots:
+        slot = self._lib.fxh_open(self._h)
+        if slot < 0:
             return None
-        slot = self._free_slots.pop()
-        self._live[slot] = 1
-        self.seq_len[slot] = 0
         for st in self._state:
             if st is not None:
                 st[slot].zero_()
@@ -163,31 +180,24 @@ class CacheManager:
 
     def close_request(self, slot: int) -> None:
         """Give back everything the request holds."""
-        self._check_live(slot)
-        for g in self.groups.values():
-            held = [int(p) for p in g.table[slot, g.first_page[slot]:g.n_logical[slot]] if p >= 0]
-            g.pool.free(held)
-            if g.n_logical[slot]:
-                g.table[slot, :g.n_logical[slot]] = -1
-                g.dirty.add(slot)
-            g.first_page[slot] = 0
-            g.n_logical[slot] = 0
-        self.seq_len[slot] = 0
-        self._live[slot] = 0
-        self._free_slots.append(slot)
+        self._ok(self._lib.fxh_close(self._h, int(slot)), slot)
 
-    def _check_live(self, slot: int) -> None:
-        if not 0 <= slot < self.max_slots or not self._live[slot]:
+    def _ok(self, rc: int, slot=None) -> int:
+        if rc >= 0:
+            return rc
+        if rc == -1:
             raise CacheError(f"slot {slot} is not held by a request")
+        if rc == -2:
+            raise CacheError(f"length exceeds max_positions {self.max_positions}")
+        if rc == -3:
+            raise CacheError("a request's length cannot shrink")
+        raise CacheError("the page bookkeeping is corrupt (a page freed but not held)")
 
     # ---- pages ----------------------------------------------------------------
-    def _pages_for(self, length: int) -> int:
-        return (length + self.page_size - 1) // self.page_size
-
     def pages_needed(self, slot: int, new_len: int) -> Dict[object, int]:
         """Pages each group still has to get so that positions < new_len are mapped."""
-        need = self._pages_for(new_len)
-        return {key: max(0, need - g.n_logical[slot]) for key, g in self.groups.items()}
+        self._ok(self._lib.fxh_pages_needed(self._h, int(slot), int(new_len), self._need), slot)
+        return {g.window: self._need[g.index] for g in self._order}
 
     def free_pages(self) -> Dict[object, int]:
         return {key: g.pool.n_free for key, g in self.groups.items()}
@@ -197,61 +207,36 @@ class CacheManager:
 
     def reserve(self, slot: int, new_len: int) -> bool:
         """Map pages for every position < new_len in every group, or change nothing."""
-        self._check_live(slot)
-        if new_len > self.max_positions:
-            raise CacheError(f"length {new_len} exceeds max_positions {self.max_positions}")
-        wanted = self.pages_needed(slot, new_len)
-        if not self.can_reserve(wanted):
-            return False
-        for key, n in wanted.items():
-            if n == 0:
-                continue
-            g = self.groups[key]
-            pages = g.pool.alloc(n)
-            a = g.n_logical[slot]
-            g.table[slot, a:a + n] = pages
-            g.n_logical[slot] = a + n
-            g.dirty.add(slot)
-            self.peak_pages[key] = max(self.peak_pages[key], g.pool.held())
-        return True
+        return self._ok(self._lib.fxh_reserve(self._h, int(slot), int(new_len)), slot) == 0
 
     def commit(self, slot: int, new_len: int) -> None:
         """The request now holds ``new_len`` positions.  Windowed groups give back the
         pages that no later query can read: the next query, at position new_len,
         reads from new_len - W + 1 on."""
-        self._check_live(slot)
-        if new_len < self.seq_len[slot]:
-            raise CacheError("a request's length cannot shrink")
-        self.seq_len[slot] = new_len
-        for g in self.groups.values():
-            if g.window is None:
-                continue
-            first_needed = max(0, new_len - g.window + 1)
-            upto = min(first_needed // self.page_size, g.n_logical[slot])
-            a = g.first_page[slot]
-            if upto > a:
-                g.pool.free([int(p) for p in g.table[slot, a:upto]])
-                g.table[slot, a:upto] = -1
-                g.first_page[slot] = upto
-                g.dirty.add(slot)
+        self._ok(self._lib.fxh_commit(self._h, int(slot), int(new_len)), slot)
 
     def held_pages(self, slot: int) -> Dict[object, List[int]]:
-        return {
-            key: [int(p) for p in g.table[slot, g.first_page[slot]:g.n_logical[slot]]]
-            for key, g in self.groups.items()
-        }
+        out = {}
+        for g in self._order:
+            a, b = self._lib.fxh_first_page(self._h, g.index, slot), self._lib.fxh_n_logical(self._h, g.index, slot)
+            out[g.window] = [int(p) for p in g.table[slot, a:b]]
+        return out
+
+    @property
+    def peak_pages(self) -> Dict[object, int]:
+        return {g.window: self._lib.fxh_peak_pages(self._h, g.index) for g in self._order}
 
     # ---- device side ----------------------------------------------------------
     def sync_tables(self) -> None:
         """Bring the device copies of the changed block-table rows up to date."""
-        for g in self.groups.values():
-            if not g.dirty:
+        for g in self._order:
+            n = self._lib.fxh_take_dirty(self._h, g.index, self._dirty, self.max_slots)
+            if n == 0:
                 continue
-            rows = sorted(g.dirty)
-            g.dirty.clear()
-            if len(rows) == 1:
+            rows = [self._dirty[i] for i in range(n)]
+            if n == 1:
                 r = rows[0]
-                g.table_dev[r].copy_(torch.from_numpy(g.table[r]), non_blocking=False)
+                g.table_dev[r].copy_(torch.from_numpy(g.table[r].copy()), non_blocking=False)
             else:
                 idx = torch.tensor(rows, dtype=torch.long)
                 g.table_dev[idx.to(self.device)] = torch.from_numpy(g.table[rows]).to(self.device)
@@ -274,25 +259,6 @@ class CacheManager:
     # ---- invariants (tests) -----------------------------------------------------
     def check_invariants(self) -> None:
         """No page lost, held twice or free while mapped."""
-        for key, g in self.groups.items():
-            mapped = []
-            for slot in range(self.max_slots):
-                row = g.table[slot]
-                if not self._live[slot]:
-                    if (row >= 0).any():
-                        raise CacheError(f"group {key}: free slot {slot} still maps pages")
-                    continue
-                mapped += [int(p) for p in row if p >= 0]
-                if (row[:g.first_page[slot]] >= 0).any() or (row[g.n_logical[slot]:] >= 0).any():
-                    raise CacheError(f"group {key}: slot {slot} maps pages outside its held range")
-                if (row[g.first_page[slot]:g.n_logical[slot]] < 0).any():
-                    raise CacheError(f"group {key}: slot {slot} has a hole in its held range")
-            if len(mapped) != len(set(mapped)):
-                raise CacheError(f"group {key}: a page is held twice")
-            free = list(g.pool._free)
-            if len(free) != len(set(free)):
-                raise CacheError(f"group {key}: a page is on the free list twice")
-            if set(free) & set(mapped):
-                raise CacheError(f"group {key}: a mapped page is on the free list")
-            if len(free) + len(mapped) != g.pool.n_pages:
-                raise CacheError(f"group {key}: {g.pool.n_pages - len(free) - len(mapped)} pages lost")
+        rc = self._lib.fxh_check(self._h)
+        if rc:
+            raise CacheError(f"cache invariants broken: {_CHECKS.get(rc, rc)}")

@@ -106,9 +106,10 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
         return e < 0 ? nullptr : a.W + (long)e * a.w_group_stride;
     };
 
-    // The first pass of the first tile: in the plain form it does not depend on the kernel before this one.
+    // The first pass of the first tile: in the plain form W is a weight matrix and does not depend on the
+    // kernel before this one.  (With transposed output the roles are swapped and W holds activations.)
     bool have_first = false;
-    if (!grouped && (int)blockIdx.x < total) { load_pass(a.W, (blockIdx.x % tiles_n) * RPB, 0); have_first = true; }
+    if (!grouped && !a.c_transposed && (int)blockIdx.x < total) { load_pass(a.W, (blockIdx.x % tiles_n) * RPB, 0); have_first = true; }
     fx_pdl_wait();
 
     for (int idx = blockIdx.x; idx < total; idx += gridDim.x) {

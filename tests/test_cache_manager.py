@@ -4,7 +4,7 @@ import random
 import pytest
 import torch
 
-from ferrox_b200.cache.manager import CacheError, CacheManager, PagePool
+from ferrox_b200.cache.manager import CacheError, CacheManager
 from ferrox_b200.cache.specs import CacheSpec, KvCacheSpec, StateSpec
 
 
@@ -20,17 +20,17 @@ def manager(n_pages=8, page_size=4, window=6, max_slots=3, with_state=True):
 
 
 def test_pool_is_all_or_nothing_and_lifo():
-    p = PagePool(4)
-    a = p.alloc(3)
-    assert a == [0, 1, 2] and p.n_free == 1
-    assert p.alloc(2) is None and p.n_free == 1  # nothing taken on failure
-    p.free([1])
-    assert p.alloc(1) == [1]  # most recently freed first
+    m = manager(n_pages=4, page_size=4, window=64, max_slots=3)
+    a, b = m.open_request(), m.open_request()
+    assert m.reserve(a, 12) and m.held_pages(a)[None] == [0, 1, 2] and m.free_pages()[None] == 1
+    assert m.reserve(b, 8) is False and m.free_pages()[None] == 1  # nothing taken on failure
+    m.close_request(a)
+    assert m.reserve(b, 4) and m.held_pages(b)[None] == [2]  # most recently freed first (a's pages went back 0, 1, 2)
     with pytest.raises(CacheError):
-        p.free([3])  # never held
-    p.free([0])
+        m.close_request(a)  # freed twice
     with pytest.raises(CacheError):
-        p.free([0])  # freed twice
+        m.reserve(7, 4)  # never opened
+    m.check_invariants()
 
 
 def test_groups_by_need_and_shapes():
