@@ -158,3 +158,16 @@ def test_dense_only_model_and_first_tokens(tmp_path):
         assert all(type(l.ffn).__name__ == "SwigluMlp" for l in eng.model.layers)
         compare(ru.run_tail_decode(eng, prompts, tail=10 ** 6), want, TOL[dtype], f"dense/first-tokens/{dtype}")
         compare(ru.run_whole(eng, prompts), want, TOL[dtype], f"dense/whole/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_same_trace_twice_gives_the_same_bits(folders, dtype):
+    """Every sum has a fixed order and no kernel reads what an earlier one has not finished writing:
+    a replayed trace reproduces its logits exactly."""
+    prompts = prompts_for("B", n=6, seed=11)
+    runs = []
+    for _ in range(3):
+        eng = engine(folders["B"], dtype, page_size=16, n_pages=24, max_slots=4)
+        runs.append(ru.run_mixed(eng, prompts, seed=4))
+    for rid in prompts:
+        assert torch.equal(runs[0][rid], runs[1][rid]) and torch.equal(runs[0][rid], runs[2][rid])
