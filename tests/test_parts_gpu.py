@@ -296,3 +296,100 @@ def test_toy_mixer_with_state_and_a_layer_run_twice(tmp_path):
     # generation works through the public entry point as well
     out = eng.generate([seqs["b"]], max_new_tokens=4)[0]
     assert out[0] == int(want["b"][-1].argmax())
+
+
+# ------------------------------------------------------------------ more toy parts: a routed feed-forward, another position encoding
+@dataclass(frozen=True)
+class HashRoutedSpec:
+    hidden: int
+    n_branches: int
+    prefix: str
+    kind: str = "toy_hash_routed_ffn"
+
+
+@dataclass(frozen=True)
+class UnrotatedSpec:
+    """A position part of another kind than the rotary one: it leaves queries and keys as projected
+    (order then comes from the causal mask and the window alone)."""
+    kind: str = "toy_unrotated_position"
+
+
+def _register_more_toys():
+    from ferrox_b200 import register_part
+    from ferrox_b200.parts.base import FeedForward, Part
+    from ferrox_b200.weights.loader import TensorDecl
+
+    class HashRouted(FeedForward):
+        """Routing without a router matrix: token t of the step goes to branch (position mod n); each
+        branch is a single matrix.  Shows a feed-forward that needs the batch's positions."""
+
+        def tensor_decls(self):
+            s = self.spec
+            return [TensorDecl(s.prefix + f"branch.{b}.weight", (s.hidden, s.hidden)) for b in range(s.n_branches)]
+
+        def load(self, src, rt):
+            super().load(src, rt)
+            self.w = torch.stack([src.get(self.spec.prefix + f"branch.{b}.weight").float()
+                                  for b in range(self.spec.n_branches)])
+
+        def forward_add(self, x, h, batch):
+            branch = (batch.positions.long() % self.spec.n_branches)
+            h += torch.einsum("th,toh->to", x.float(), self.w[branch])
+
+    class Unrotated(Part):
+        def load(self, src, rt):
+            super().load(src, rt)
+            self.inv_freq = None      # tells the attention kernel not to rotate
+            self.rotary_dim = 0
+
+        def table(self, batch):
+            return None
+
+    register_part("toy_hash_routed_ffn", HashRouted, replace=True)
+    register_part("toy_unrotated_position", Unrotated, replace=True)
+
+
+def test_toy_routed_feed_forward_and_unrotated_attention(tmp_path):
+    """A block made of the framework's attention with a position part that does not rotate, and a toy
+    feed-forward routed by position; built from specs, loaded from a random folder, stepped in two cuts."""
+    import ferrox_b200
+    from ferrox_b200 import Engine, StepEntry, register_architecture
+    from ferrox_b200.parts.specs import AttentionSpec, BlockSpec, ModelSpec, NormSpec, ScheduleEntry
+
+    _register_more_toys()
+    H = 32
+
+    def model_spec(c):
+        p = "model.layers.0."
+        attn = AttentionSpec(hidden=H, n_heads=2, n_kv_heads=2, head_dim=16, qkv_bias=True,
+                             position=UnrotatedSpec(), window=5, prefix=p + "self_attn.")
+        blk = BlockSpec(NormSpec(H, 1e-6, p + "input_layernorm."), attn, NormSpec(H, 1e-6, p + "post_attention_layernorm."),
+                        HashRoutedSpec(H, 3, p + "mlp."))
+        return ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=50, hidden=H, max_positions=64, layers=(blk,),
+                         schedule=(ScheduleEntry(0, 0),), final_norm=NormSpec(H, 1e-6, "model.norm."), head_name=None)
+
+    register_architecture("ToyRoutedForCausalLM", dict, model_spec, replace=True)
+    cfg = dict(architectures=["ToyRoutedForCausalLM"])
+    folder = ferrox_b200.write_random_model(str(tmp_path / "toy2"), cfg, seed=2, std=0.3, norm_init="around_one")
+    w = {k: v.float() for k, v in plain.read_safetensors(folder + "/model.safetensors").items()}
+    toks = [3, 9, 44, 1, 0, 17, 8, 8, 30, 2, 5]
+
+    # plain statement, without rotation
+    x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+    n = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], 1e-6)
+    T = len(toks)
+
+    def proj(name, heads):
+        return (n @ w[f"model.layers.0.self_attn.{name}.weight"].T + w[f"model.layers.0.self_attn.{name}.bias"]).reshape(T, heads, 16)
+
+    o = plain.attention(proj("q_proj", 2), proj("k_proj", 2), proj("v_proj", 2), 5)
+    x = x + o.reshape(T, 32) @ w["model.layers.0.self_attn.o_proj.weight"].T
+    n = plain.rms_norm(x, w["model.layers.0.post_attention_layernorm.weight"], 1e-6)
+    x = x + torch.stack([n[t] @ w[f"model.layers.0.mlp.branch.{t % 3}.weight"].T for t in range(T)])
+    want = plain.rms_norm(x, w["model.norm.weight"], 1e-6) @ w["model.embed_tokens.weight"].T
+
+    eng = Engine.from_folder(folder, dtype="float32", page_size=4, n_pages=8, max_slots=2)
+    s = eng.open_request()
+    a = eng.step([StepEntry(s, toks[:7], want=list(range(7)))]).cpu()
+    b = eng.step([StepEntry(s, toks[7:], want=list(range(4)))]).cpu()
+    assert rel(torch.cat([a, b]), want) < 3e-5
