@@ -21,7 +21,8 @@ import numpy as np
 import torch
 
 
-QUERY_TILE = 64  # query tokens per tile of the prompt attention kernel
+QUERY_TILE = 64  # query tokens per tile of the mma.sync prompt attention kernel
+WIDE_QUERY_TILE = 128  # query tokens per tile of the tcgen05 prompt attention kernel
 
 
 @dataclass
@@ -49,6 +50,7 @@ class StepBatch:
     max_new: int = 0  # most tokens any entry brings
     h2d_bytes: int = 0  # size of the step's host-to-device copy
     q_tiles: torch.Tensor = None  # [n_tiles, 4] int32: (first flat token, rows <= 64, entry, first position)
+    q_tiles_wide: torch.Tensor = None  # the same for tiles of <= 128 rows
     shared: dict = field(default_factory=dict)  # per-step values that several layers share (e.g. rotary tables)
 
 
@@ -57,11 +59,13 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
     B = len(entries)
     W = sum(len(e.want) for e in entries)
     n_tiles = sum(-(-len(e.tokens) // QUERY_TILE) for e in entries)
-    buf = np.empty(3 * T + B + W + 4 * n_tiles, dtype=np.int32)
+    n_wide = sum(-(-len(e.tokens) // WIDE_QUERY_TILE) for e in entries)
+    buf = np.empty(3 * T + B + W + 4 * n_tiles + 4 * n_wide, dtype=np.int32)
     tok, pos, seq = buf[:T], buf[T:2 * T], buf[2 * T:3 * T]
     slots, want = buf[3 * T:3 * T + B], buf[3 * T + B:3 * T + B + W]
-    tiles = buf[3 * T + B + W:].reshape(n_tiles, 4)
-    t = w = ti = 0
+    tiles = buf[3 * T + B + W:3 * T + B + W + 4 * n_tiles].reshape(n_tiles, 4)
+    wide = buf[3 * T + B + W + 4 * n_tiles:].reshape(n_wide, 4)
+    t = w = ti = wi = 0
     max_len = max_new = 0
     for b, e in enumerate(entries):
         n = len(e.tokens)
@@ -77,6 +81,9 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
         for i in range(0, n, QUERY_TILE):
             tiles[ti] = (t + i, min(QUERY_TILE, n - i), b, e.start + i)
             ti += 1
+        for i in range(0, n, WIDE_QUERY_TILE):
+            wide[wi] = (t + i, min(WIDE_QUERY_TILE, n - i), b, e.start + i)
+            wi += 1
         t += n
         max_len = max(max_len, e.start + n)
         max_new = max(max_new, n)
@@ -85,7 +92,8 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
         n_tokens=T, n_seqs=B, n_want=W,
         token_ids=dev[:T], positions=dev[T:2 * T], token_seq=dev[2 * T:3 * T],
         seq_slot=dev[3 * T:3 * T + B], want_rows=dev[3 * T + B:3 * T + B + W],
-        q_tiles=dev[3 * T + B + W:].view(n_tiles, 4),
+        q_tiles=dev[3 * T + B + W:3 * T + B + W + 4 * n_tiles].view(n_tiles, 4),
+        q_tiles_wide=dev[3 * T + B + W + 4 * n_tiles:].view(n_wide, 4),
         status=status, stream=stream, entries=list(entries), max_len=max_len, max_new=max_new,
         h2d_bytes=buf.nbytes,
     )

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P],
+    "fx_prefill_attention_tc": [_P, _L, _I, _P, _P, _I, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P, _P],
     "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P],
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
@@ -223,6 +224,28 @@ def prefill_attention(q, k_pages, v_pages, block_table, page_size, tiles, seq_sl
     call("fx_prefill_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
          block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0], _ptr(seq_slot), _ptr(out), _rows(out), n_heads,
          n_kv_heads, head_dim, int(window or 0), float(scale), stream if stream is not None else stream_ptr())
+    return out
+
+
+WIDE_PREFILL_TILE = 128
+
+
+def prefill_tc_ok(q, out, k_pages, page_size, head_dim) -> bool:
+    """Whether the tcgen05 prompt attention kernel takes these operands."""
+    return (q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and head_dim in (64, 128)
+            and page_size >= 64 and page_size % 64 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
+def prefill_attention_tc(q, k_pages, v_pages, block_table, page_size, tiles, seq_slot, out, n_heads, n_kv_heads,
+                         head_dim, window, scale, status=None, stream=None):
+    """Flash attention of prompt portions on the tcgen05 tensor cores (bfloat16, head_dim 64 or 128, pages of a
+    multiple of 64 positions).  ``tiles``: int32 [n, 4] rows of (first flat token, rows <= 128, entry index,
+    absolute position of the first row)."""
+    call("fx_prefill_attention_tc", _ptr(q), _rows(q), q.shape[0], _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
+         _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0], _ptr(seq_slot), _ptr(out),
+         _rows(out), n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(status),
+         stream if stream is not None else stream_ptr())
     return out
 
 

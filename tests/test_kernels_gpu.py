@@ -536,6 +536,74 @@ def test_prefill_attention_tiles(case):
         assert rel(out[i].float().cpu().reshape(nh, d), want) < 1.5e-2, (i, s, pos)
 
 
+TC_ATT_CASES = [
+    # nh, nkv, d, page, window, lengths
+    (16, 16, 128, 64, 0, [300, 64, 65]),
+    (28, 4, 128, 64, 100, [130, 517]),
+    (6, 2, 64, 128, 0, [700, 129]),
+    (3, 1, 64, 64, 300, [900]),
+    (2, 2, 128, 192, 129, [400, 2, 128]),
+]
+
+
+@pytest.mark.parametrize("case", TC_ATT_CASES)
+def test_prefill_attention_tcgen05(case):
+    """Prompt portions through the tcgen05 kernel (tiles of 128 queries, blocks of 128 keys), whole prompts and
+    continuations after a cached prefix, against the plain per-query statement.  One far key of the longest
+    request is made to stand out for its last query, so that a block that is skipped or masked wrongly shows."""
+    o = ops()
+    nh, nkv, d, ps, window, lens = case
+    dt = torch.bfloat16
+    kp, vp, table, ks, vs = build_cache(dt, lens, nkv, d, ps, n_pages=sum(-(-L // ps) for L in lens) + 3, seed=5)
+    # stale finite values in the unused places of every page, as pages that are used again hold
+    starts = [0 if i % 2 == 0 else min(L - 1, max(1, L // 3)) for i, L in enumerate(lens)]
+    toks, tiles, flat = [], [], 0
+    for s, (L, st) in enumerate(zip(lens, starts)):
+        n = L - st
+        for i in range(0, n, 128):
+            tiles.append((flat + i, min(128, n - i), s, st + i))
+        toks += [(s, p) for p in range(st, L)]
+        flat += n
+    T = len(toks)
+    q = rnd(T, nh * d + 2 * nkv * d, dtype=dt, seed=T)
+    # the last query of request 0 looks hard at one far key that is still inside its window
+    L0 = lens[0]
+    far = max(0, L0 - 1 - (window - 2 if window else L0))
+    last0 = L0 - starts[0] - 1
+    q[last0, :d] = (ks[0][far, 0] * 4).to(dt).to(DEV)
+    tiles_t = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor([s + 1 for s in range(len(lens))], dtype=torch.int32, device=DEV)
+    out = torch.zeros(T, nh * d, dtype=dt, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    assert o.prefill_tc_ok(q, out, kp, ps, d)
+    o.prefill_attention_tc(q, kp, vp, table, ps, tiles_t, seq_slot, out, nh, nkv, d, window, scale, status=status)
+    assert int(status) == 0
+    assert torch.isfinite(out.float()).all()
+    step = max(1, T // 40)  # a spread of tokens, plus tile edges
+    check = sorted(set(list(range(0, T, step)) + [t for t in (0, 1, 63, 64, 127, 128, 129, 255, 256, last0, T - 1) if t < T]))
+    for i in check:
+        s, pos = toks[i]
+        want = plain_attention(q[i, : nh * d].float().cpu().reshape(nh, d), ks[s], vs[s], pos, window, scale)
+        assert rel(out[i].float().cpu().reshape(nh, d), want) < 1.5e-2, (i, s, pos)
+    # the far key carries (nearly) all the weight of that query's first head
+    got = out[last0, :d].float().cpu()
+    assert rel(got, vs[0][far, 0]) < 5e-2
+
+
+def test_prefill_attention_tcgen05_refuses_other_sizes():
+    o = ops()
+    q = rnd(4, 3 * 48, dtype=torch.bfloat16)
+    kp = torch.zeros(2, 1, 64, 48, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(4, 48, dtype=torch.bfloat16, device=DEV)
+    assert not o.prefill_tc_ok(q, out, kp, 64, 48)
+    tiles = torch.tensor([[0, 4, 0, 0]], dtype=torch.int32, device=DEV)
+    table = torch.zeros(1, 2, dtype=torch.int32, device=DEV)
+    slots = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(o.KernelError):
+        o.prefill_attention_tc(q, kp, kp, table, 64, tiles, slots, out, 1, 1, 48, 0, 1.0)
+
+
 def test_gemm_skinny_transposed_store_and_linear_picks_it_for_narrow_outputs():
     o = ops()
     T, N, K = 300, 61, 256
