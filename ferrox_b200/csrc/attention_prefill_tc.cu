@@ -1,25 +1,32 @@
 // Attention for prompt portions on the 5th-generation tensor cores (bfloat16, head_dim 64 or 128,
 // pages of 64 positions or a multiple).
 //
-// One CTA takes a tile of 128 query tokens of one request and one head, and walks that request's keys in
-// blocks of 128 positions (earlier steps' keys and the portion's own alike, found through the block table):
+// One CTA takes up to 256 query tokens of one request and one head, as two sub-tiles of 128 rows, and
+// walks that request's keys in blocks of 128 positions (earlier steps' keys and the portion's own alike,
+// found through the block table).  For each sub-tile t and key block j:
 //
-//   S = Q K^T        tcgen05.mma 128 x 128 x head_dim, Q and K tiles in shared memory (TMA, 128-byte swizzle),
-//                    S in tensor memory (32-bit)
-//   P = exp2(...)    each of the 128 softmax threads owns one query row: tcgen05.ld of its row of S, mask by
-//                    absolute position (query p sees keys max(0, p - W + 1) .. p), running max and sum in
-//                    32 bits, P rounded to bfloat16 and stored, swizzled, as the A operand of the next product
-//   O_blk = P V      tcgen05.mma 128 x head_dim x 128 with V as an N-major B operand, exactly as TMA lays the
-//                    [key][head_dim] rows down; O_blk in tensor memory
-//   O = O * alpha + O_blk   in the softmax threads' registers (a row of O per thread), no read-modify-write
-//                    of tensor memory
+//   S_t = Q_t K_j^T    tcgen05.mma 128 x 128 x head_dim; Q and K tiles in shared memory (TMA, 128-byte
+//                      swizzle), S_t in tensor memory (32-bit)
+//   P_t = exp2(...)    each of the sub-tile's 128 softmax threads owns one query row: tcgen05.ld of its
+//                      row of S, mask by absolute position (query p sees keys max(0, p - W + 1) .. p),
+//                      running max and sum in 32 bits; P rounded to bfloat16 and written back over the
+//                      first columns of S_t (tcgen05.st), where the next product reads it as its A operand
+//   O_t += P_t V_j     tcgen05.mma 128 x head_dim x 128, A from tensor memory, V as an N-major B operand,
+//                      exactly as TMA lays the [key][head_dim] rows down; O_t stays in tensor memory
 //
-// Warp 0 issues the TMA loads (K and V blocks double-buffered), warp 1 issues the tensor-core instructions
-// and owns the tensor-memory allocation, warps 2-5 are the softmax threads.  The product S of block i+1 is
-// issued as soon as P of block i is written, so it overlaps the accumulation of O.  Every wait is bounded
-// (status code 3 on time-out, then the roles leave, tensor memory is freed and the kernel returns).
-// Keys that are masked for every row are still multiplied (with weight 0); the half of a block that lies
-// beyond the request's pages is read from page 0, which always holds finite values.
+// The running maximum of a row is only raised when it grows by more than 2^8 (the weights then stay
+// below 2^8 and the final division by the row sum makes the result the same); when it is raised, the
+// row's thread scales its row of O_t in tensor memory.  This takes the accumulator out of the softmax
+// threads' registers and off their critical path.
+//
+// Warp 0 issues the TMA loads (K and V blocks double-buffered), warp 1 issues the tensor-core
+// instructions and owns the tensor-memory allocation (512 columns: S_0, S_1, O_0, O_1), warps 2-5 are
+// sub-tile 0's softmax threads and warps 6-9 sub-tile 1's.  The products are issued in the order
+// PV_0(j), S_0(j+1), PV_1(j), S_1(j+1): while one sub-tile's threads work on their block the tensor
+// cores work for the other.  Every wait is bounded (status code 3 on time-out, then the roles leave,
+// tensor memory is freed and the kernel returns).  Keys that are masked for every row are still
+// multiplied (with weight 0); the half of a block that lies beyond the request's pages is read from
+// page 0, which always holds finite values.
 //
 // Reference: crates/ferrox-core/src/attention.rs:531-563 (query t over keys 0..=t), :146-175 (online
 // softmax), :484-524 (window), :572-610 (pages), :432-449 (grouped heads).  The mma.sync kernel of
@@ -31,7 +38,8 @@ namespace {
 
 using namespace fxtc;
 
-constexpr int BQ = 128, BKEY = 128, NTHREADS = 192;
+constexpr int BQ = 128, BKEY = 128, NTHREADS = 320, TMEM_COLS = 512;
+constexpr float RAISE_MAX_BY = 8.f;   // in powers of two
 
 __device__ __forceinline__ float fast_exp2(float x) {   // 2^x, approximate; -inf gives 0
     float y;
@@ -51,10 +59,10 @@ struct AttnArgs {
 template <int D>
 struct Smem {
     static constexpr int HALVES = D / 64;                  // 64-element (128-byte) slices of the head dimension
-    static constexpr int SUB = 128 * 128;                  // bytes of a [128 rows x 128 bytes] sub-tile
-    static constexpr int Q_BYTES = HALVES * SUB, KV_BYTES = HALVES * SUB, P_BYTES = 2 * SUB;
-    static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + 2 * KV_BYTES, P_OFF = V_OFF + 2 * KV_BYTES;
-    static constexpr int BAR_OFF = P_OFF + P_BYTES;
+    static constexpr int SUB = 128 * 128;                  // bytes of a [128 rows x 128 bytes] piece
+    static constexpr int Q_BYTES = HALVES * SUB, KV_BYTES = HALVES * SUB;
+    static constexpr int Q_OFF = 0, K_OFF = 2 * Q_BYTES, V_OFF = K_OFF + 2 * KV_BYTES;
+    static constexpr int BAR_OFF = V_OFF + 2 * KV_BYTES;
     static constexpr int TOTAL = BAR_OFF + 128 + 1024;     // barriers, alignment slack
 };
 
@@ -76,54 +84,67 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
     const int head = blockIdx.y;
     const int kvh = head / (a.n_heads / a.n_kv_heads);
     const int last_pos = pos0 + rows - 1;
-    const int key_lo = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
-    const int kb_begin = (key_lo / BKEY) * BKEY;
-    const int n_blocks = (last_pos - kb_begin) / BKEY + 1;
+    // sub-tile t: rows_of(t) rows from position pos0 + 128 t; it needs the key blocks blk_lo(t) .. blk_hi(t)
+    const int nt = rows > BQ ? 2 : 1;
+    auto rows_of = [&](int t) { return min(BQ, rows - t * BQ); };
+    auto blk_lo = [&](int t) {
+        const int p = pos0 + t * BQ;
+        return (a.window > 0 && p - a.window + 1 > 0 ? p - a.window + 1 : 0) / BKEY;
+    };
+    auto blk_hi = [&](int t) { return (pos0 + t * BQ + rows_of(t) - 1) / BKEY; };
+    const int first_blk = blk_lo(0), last_blk = blk_hi(nt - 1);
+    auto active = [&](int t, int j) { return t < nt && j >= blk_lo(t) && j <= blk_hi(t); };
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bar0 = base + L::BAR_OFF;
-    const uint32_t q_full = bar0, s_full = bar0 + 8, p_full = bar0 + 16, o_full = bar0 + 24;
-    auto k_full = [&](int b) { return bar0 + 32 + 8u * b; };
-    auto v_full = [&](int b) { return bar0 + 48 + 8u * b; };
-    auto kv_empty = [&](int b) { return bar0 + 64 + 8u * b; };
+    const uint32_t q_full = bar0;
+    auto s_full = [&](int t) { return bar0 + 8 + 8u * t; };
+    auto p_full = [&](int t) { return bar0 + 24 + 8u * t; };
+    auto o_done = [&](int t) { return bar0 + 40 + 8u * t; };
+    auto k_full = [&](int b) { return bar0 + 56 + 8u * b; };
+    auto v_full = [&](int b) { return bar0 + 72 + 8u * b; };
+    auto kv_empty = [&](int b) { return bar0 + 88 + 8u * b; };
     volatile int* abort_flag = &abort_flag_s;
 
     if (threadIdx.x == 0) {
         abort_flag_s = 0;
-        mbar_init(q_full, 1); mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(o_full, 1);
-        for (int b = 0; b < 2; ++b) { mbar_init(k_full(b), 1); mbar_init(v_full(b), 1); mbar_init(kv_empty(b), 1); }
+        mbar_init(q_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_full(b), 1); mbar_init(p_full(b), 4); mbar_init(o_done(b), 1);
+            mbar_init(k_full(b), 1); mbar_init(v_full(b), 1); mbar_init(kv_empty(b), 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {   // tensor memory: S (128 columns) and O_blk (D columns)
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_s)), "r"(256u) : "memory");
+                     ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+    auto tmem_s = [&](int t) { return tmem_base + 128u * t; };        // S_t, and P_t over its first 64 columns
+    auto tmem_o = [&](int t) { return tmem_base + 256u + 128u * t; };
 
     if (warp == 0) {
         // ---------------- producer: Q once, then K and V blocks ----------------
         if (lane == 0) {
-            mbar_expect_tx(q_full, L::Q_BYTES);
-            for (int h = 0; h < L::HALVES; ++h)
-                tma_load_2d(base + L::Q_OFF + h * L::SUB, &map_q, head * D + h * 64, tok0, q_full);
+            mbar_expect_tx(q_full, nt * L::Q_BYTES);
+            for (int t = 0; t < nt; ++t)
+                for (int h = 0; h < L::HALVES; ++h)
+                    tma_load_2d(base + L::Q_OFF + t * L::Q_BYTES + h * L::SUB, &map_q, head * D + h * 64, tok0 + t * BQ, q_full);
             const int* table = a.block_table + (long)a.seq_slot[entry] * a.table_width;
             int issued = 0;
-            for (int i = 0; i < n_blocks; ++i) {
-                const int b = i & 1;
+            for (int j = first_blk; j <= last_blk; ++j) {
+                const int i = j - first_blk, b = i & 1;
                 if (!mbar_wait(kv_empty(b), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag)) break;
-                const int kb = kb_begin + i * BKEY;
                 int page[2], off[2];
                 for (int hk = 0; hk < 2; ++hk) {   // the two runs of 64 keys of the block
-                    const int key = kb + hk * 64;
-                    int p = key <= last_pos ? table[key / a.page_size] : -1;
-                    page[hk] = p >= 0 ? p : 0;      // beyond the request's pages: any finite data will do (masked)
+                    const int key = j * BKEY + hk * 64;
+                    const int p = key <= last_pos ? table[key / a.page_size] : -1;
+                    page[hk] = p >= 0 ? p : 0;      // no page (beyond the request, or before its window): masked anyway
                     off[hk] = p >= 0 ? key % a.page_size : 0;
                 }
                 mbar_expect_tx(k_full(b), L::KV_BYTES);
@@ -149,135 +170,172 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc_ex(BQ, BKEY, 0);   // S: B = K tile, K-major
             constexpr uint32_t idesc_o = instr_desc_ex(BQ, D, 1);      // O: B = V tile, N-major
-            auto issue_s = [&](int i) {
-                const int b = i & 1;
-                if (!mbar_wait(k_full(b), (uint32_t)((i >> 1) & 1), abort_flag)) return false;
-                tc_fence_after();
+            int k_ready = first_blk - 1;   // the last block whose K is known to have landed
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            auto issue_s = [&](int t, int j) {
+                const int i = j - first_blk, b = i & 1;
+                if (k_ready < j) {
+                    if (!mbar_wait(k_full(b), (uint32_t)((i >> 1) & 1), abort_flag)) return false;
+                    k_ready = j;
+                    tc_fence_after();
+                }
 #pragma unroll
                 for (int h = 0; h < L::HALVES; ++h) {
-                    const uint64_t dq = smem_desc(base + L::Q_OFF + h * L::SUB);
+                    const uint64_t dq = smem_desc(base + L::Q_OFF + t * L::Q_BYTES + h * L::SUB);
                     const uint64_t dk = smem_desc(base + L::K_OFF + b * L::KV_BYTES + h * L::SUB);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) tc_mma(tmem_s, dq + 2u * k, dk + 2u * k, idesc_s, (h | k) != 0);
+                    for (int k = 0; k < 4; ++k) tc_mma(tmem_s(t), dq + 2u * k, dk + 2u * k, idesc_s, (h | k) != 0);
                 }
-                tc_commit(s_full);
+                tc_commit(s_full(t));
                 return true;
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag);
-            if (ok) ok = issue_s(0);
-            for (int i = 0; i < n_blocks && ok; ++i) {
-                const int b = i & 1;
-                ok = mbar_wait(p_full, (uint32_t)(i & 1), abort_flag) && mbar_wait(v_full(b), (uint32_t)((i >> 1) & 1), abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                // O_blk = P V: 8 steps of 16 keys.  A = P, K-major (keys contiguous), two sub-tiles of 64 keys.
-                // B = V, N-major: a step covers two 8-key groups (1024 bytes each, stride operand); the two
-                // 64-element slices of the head dimension lie SUB bytes apart (leading operand).
+            for (int t = 0; t < nt && ok; ++t)
+                if (active(t, first_blk)) ok = issue_s(t, first_blk);
+            int n_p[2] = {0, 0};   // blocks of each sub-tile whose P has been taken
+            for (int j = first_blk; j <= last_blk && ok; ++j) {
+                const int i = j - first_blk, b = i & 1;
+                bool v_ready = false;
+                for (int t = 0; t < nt && ok; ++t) {
+                    if (active(t, j)) {
+                        ok = mbar_wait(p_full(t), (uint32_t)(n_p[t] & 1), abort_flag);
+                        if (ok && !v_ready) { ok = mbar_wait(v_full(b), (uint32_t)((i >> 1) & 1), abort_flag); v_ready = true; }
+                        if (!ok) break;
+                        tc_fence_after();
+                        // O_t += P V: 8 steps of 16 keys.  A = P from tensor memory, 8 columns a step.  B = V,
+                        // N-major: a step covers two 8-key groups (1024 bytes each, the stride operand); the two
+                        // 64-element slices of the head dimension lie SUB bytes apart (the leading operand).
 #pragma unroll
-                for (int ks = 0; ks < BKEY / 16; ++ks) {
-                    const uint64_t dp = smem_desc(base + L::P_OFF + (ks >> 2) * L::SUB) + 2u * (ks & 3);
-                    const uint64_t dv = smem_desc_lbo_sbo(base + L::V_OFF + b * L::KV_BYTES + ks * 2048, L::SUB, 1024);
-                    tc_mma(tmem_o, dp, dv, idesc_o, ks != 0);
+                        for (int ks = 0; ks < BKEY / 16; ++ks) {
+                            const uint64_t dv = smem_desc_lbo_sbo(base + L::V_OFF + b * L::KV_BYTES + ks * 2048, L::SUB, 1024);
+                            tc_mma_ts(tmem_o(t), tmem_s(t) + 8u * ks, dv, idesc_o, (n_p[t] | ks) != 0);
+                        }
+                        ++n_p[t];
+                        if (j == blk_hi(t)) tc_commit(o_done(t));
+                    }
+                    if (t == nt - 1) tc_commit(kv_empty(b));   // every product that reads this stage has been issued
+                    if (active(t, j + 1)) ok = issue_s(t, j + 1);
                 }
-                tc_commit(o_full);
-                tc_commit(kv_empty(b));
-                if (i + 1 < n_blocks) ok = issue_s(i + 1);
             }
         }
     } else {
-        // ---------------- softmax and accumulation: one query row per thread ----------------
-        const int quad = warp & 3;
+        // ---------------- softmax: one query row per thread ----------------
+        const int t = (warp - 2) >> 2;
+        const int quad = warp & 3;                       // the lanes of tensor memory this warp may touch
         const int r = quad * 32 + lane;
-        const int p_r = pos0 + r;                                   // absolute position of this row
-        const int lo_r = a.window > 0 ? p_r - a.window + 1 : 0;
-        const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-        float o[D];
+        if (t < nt) {
+            const int rows_t = rows_of(t);
+            const int pos0_t = pos0 + t * BQ;
+            const int p_r = pos0_t + r;                  // absolute position of this row
+            const int lo_r = a.window > 0 ? p_r - a.window + 1 : 0;
+            const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+            const uint32_t ts = tmem_s(t) + lane_off, to = tmem_o(t) + lane_off;
+            const float sl2 = a.scale_log2e;
+            float m = -INFINITY, l = 0.f;
+            bool ok = true;
+            int cnt = 0;
+            const int hi = blk_hi(t);
+            for (int j = blk_lo(t); j <= hi; ++j, ++cnt) {
+                ok = __all_sync(0xffffffffu, mbar_wait(s_full(t), (uint32_t)(cnt & 1), abort_flag));
+                if (!ok) break;
+                tc_fence_after();
+                const int kb = j * BKEY;
+                // every key of the block visible to every row of the sub-tile: no masking (most blocks)
+                const bool interior = kb + BKEY - 1 <= pos0_t && (a.window <= 0 || kb >= pos0_t + BQ - a.window);
+                uint32_t s[64];
+                // first pass over the row of S, in halves of 64 columns: its maximum
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < D; ++j) o[j] = 0.f;
-        float m = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int i = 0; i < n_blocks; ++i) {
-            ok = __all_sync(0xffffffffu, mbar_wait(s_full, (uint32_t)(i & 1), abort_flag));
-            if (!ok) break;
-            tc_fence_after();
-            const int kb = kb_begin + i * BKEY;
-            // every key of the block visible to every row of the tile: no masking (most blocks)
-            const bool interior = kb + BKEY - 1 <= pos0 && (a.window <= 0 || kb >= pos0 + BQ - 1 - a.window + 1);
-            // pass 1: the row's maximum
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BKEY / 32; ++c) {
-                uint32_t s[32];
-                tc_ld32(tmem_s + lane_off + c * 32, s);
-                tc_ld_wait();
+                for (int hf = 0; hf < 2; ++hf) {
+                    tc_ld32(ts + hf * 64, s);
+                    tc_ld32(ts + hf * 64 + 32, s + 32);
+                    tc_ld_wait();
+                    if (!interior) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int key = kb + c * 32 + j;
-                    const bool vis = interior || (key <= p_r && key >= lo_r);
-                    if (vis) mx = fmaxf(mx, __uint_as_float(s[j]));
+                        for (int k = 0; k < 64; ++k) {
+                            const int key = kb + hf * 64 + k;
+                            if (key > p_r || key < lo_r) s[k] = 0xff800000u;   // -inf
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 64; k += 4) {
+                        mx0 = fmaxf(mx0, __uint_as_float(s[k])); mx1 = fmaxf(mx1, __uint_as_float(s[k + 1]));
+                        mx2 = fmaxf(mx2, __uint_as_float(s[k + 2])); mx3 = fmaxf(mx3, __uint_as_float(s[k + 3]));
+                    }
                 }
-            }
-            const float mn = fmaxf(m, mx);
-            const float ref = mn == -INFINITY ? 0.f : mn * a.scale_log2e;
-            const float alpha = m == -INFINITY ? 0.f : fast_exp2(m * a.scale_log2e - ref);
-            // pass 2: P = exp2(S * scale - ref), rounded to bfloat16, into shared memory (128-byte swizzle)
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BKEY / 32; ++c) {
-                uint32_t s[32];
-                tc_ld32(tmem_s + lane_off + c * 32, s);
-                tc_ld_wait();
-                uint32_t pk[16];
+                const float mn = fmaxf(fmaxf(m, fmaxf(mx0, mx1)), fmaxf(mx2, mx3));
+                const bool raise = mn > m && (m == -INFINITY || (mn - m) * sl2 > RAISE_MAX_BY);
+                if (__any_sync(0xffffffffu, raise)) {
+                    const float alpha = m == -INFINITY ? 0.f : fast_exp2((m - mn) * sl2);
+                    l *= alpha;
+                    m = mn;
+                    if (cnt > 0) {   // the sums so far of this row, in tensor memory, take the new reference too
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int key = kb + c * 32 + j;
-                    const bool v0 = interior || (key <= p_r && key >= lo_r);
-                    const bool v1 = interior || (key + 1 <= p_r && key + 1 >= lo_r);
-                    const float e0 = v0 ? fast_exp2(__uint_as_float(s[j]) * a.scale_log2e - ref) : 0.f;
-                    const float e1 = v1 ? fast_exp2(__uint_as_float(s[j + 1]) * a.scale_log2e - ref) : 0.f;
-                    sum += e0 + e1;
-                    __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-                    pk[j >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t ob[32];
+                            tc_ld32(to + c * 32, ob);
+                            tc_ld_wait();
+#pragma unroll
+                            for (int k = 0; k < 32; ++k) ob[k] = __float_as_uint(__uint_as_float(ob[k]) * alpha);
+                            tc_st32(to + c * 32, ob);
+                        }
+                    }
                 }
-                // keys c*32 .. c*32+31 of row r: sub-tile c/2, 16-byte chunks (c%2)*4 .. +3, swizzled by the row
-                uint8_t* prow = base_ptr + L::P_OFF + (c >> 1) * L::SUB + r * 128;
+                // second pass: P = exp2(S * scale - reference), as bfloat16 pairs over the first 64 columns of S
+                // (columns 0-31 are written after columns 0-63 were read, columns 32-63 after 64-127)
+                const float ref = m == -INFINITY ? 0.f : m * sl2;
+                float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int ch = ((c & 1) * 4 + q4) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(prow + ch * 16) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+                for (int hf = 0; hf < 2; ++hf) {
+                    tc_ld32(ts + hf * 64, s);
+                    tc_ld32(ts + hf * 64 + 32, s + 32);
+                    tc_ld_wait();
+                    if (!interior) {
+#pragma unroll
+                        for (int k = 0; k < 64; ++k) {
+                            const int key = kb + hf * 64 + k;
+                            if (key > p_r || key < lo_r) s[k] = 0xff800000u;
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 64; k += 2) {
+                        const float e0 = fast_exp2(fmaf(__uint_as_float(s[k]), sl2, -ref));
+                        const float e1 = fast_exp2(fmaf(__uint_as_float(s[k + 1]), sl2, -ref));
+                        sum0 += e0; sum1 += e1;
+                        __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+                        s[k >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+                    }
+                    tc_st32(ts + hf * 32, s);
                 }
+                l += sum0 + sum1;
+                tc_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full(t));
             }
-            l = l * alpha + sum;
-            m = mn;
-            // P is written with ordinary stores and read by the tensor cores: make it visible to that proxy
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
-            // O = O * alpha + O_blk
-            ok = __all_sync(0xffffffffu, mbar_wait(o_full, (uint32_t)(i & 1), abort_flag));
-            if (!ok) break;
-            tc_fence_after();
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done(t), 0, abort_flag));
+            if (ok) {
+                tc_fence_after();
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                bf16* dst = a.out + (long)(tok0 + t * BQ + r) * a.ldo + (long)head * D;
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t ob[32];
-                tc_ld32(tmem_o + lane_off + c * 32, ob);
-                tc_ld_wait();
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t ob[32];
+                    tc_ld32(to + c * 32, ob);
+                    tc_ld_wait();
+                    if (r < rows_t) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + __uint_as_float(ob[j]);
-            }
-        }
-        if (ok && r < rows) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = a.out + (long)(tok0 + r) * a.ldo + (long)head * D;
-#pragma unroll
-            for (int j = 0; j < D; j += 8) {
-                uint4 v;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(o[j] * inv, o[j + 1] * inv), p1 = __floats2bfloat162_rn(o[j + 2] * inv, o[j + 3] * inv);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(o[j + 4] * inv, o[j + 5] * inv), p3 = __floats2bfloat162_rn(o[j + 6] * inv, o[j + 7] * inv);
-                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
-                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
-                *reinterpret_cast<uint4*>(dst + j) = v;
+                        for (int k = 0; k < 32; k += 8) {
+                            uint4 v;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(ob[k]) * inv, __uint_as_float(ob[k + 1]) * inv);
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(ob[k + 2]) * inv, __uint_as_float(ob[k + 3]) * inv);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(ob[k + 4]) * inv, __uint_as_float(ob[k + 5]) * inv);
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(ob[k + 6]) * inv, __uint_as_float(ob[k + 7]) * inv);
+                            v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                            v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                            *reinterpret_cast<uint4*>(dst + c * 32 + k) = v;
+                        }
+                    }
+                }
             }
         }
     }
@@ -287,7 +345,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && abort_flag_s && a.status) atomicExch(a.status, STATUS_TC_TIMEOUT);
 }
@@ -318,7 +376,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 
 }  // namespace
 
-// tiles: int32 [n_tiles, 4] = (first flat token, rows <= 128, entry index, absolute position of the first row).
+// tiles: int32 [n_tiles, 4] = (first flat token, rows <= 256, entry index, absolute position of the first row).
 // q is the fused [tokens, ldq] buffer whose rows start with the query heads; n_tokens its number of rows.
 // Refuses (FX_ERR_SIZE / FX_ERR_ALIGN) what it does not take; the caller then uses the mma.sync kernel.
 extern "C" int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages,

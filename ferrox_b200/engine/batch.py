@@ -22,7 +22,7 @@ import torch
 
 
 QUERY_TILE = 64  # query tokens per tile of the mma.sync prompt attention kernel
-WIDE_QUERY_TILE = 128  # query tokens per tile of the tcgen05 prompt attention kernel
+WIDE_QUERY_TILE = 256  # query tokens per tile of the tcgen05 prompt attention kernel (two sub-tiles of 128)
 
 
 @dataclass
@@ -50,7 +50,7 @@ class StepBatch:
     max_new: int = 0  # most tokens any entry brings
     h2d_bytes: int = 0  # size of the step's host-to-device copy
     q_tiles: torch.Tensor = None  # [n_tiles, 4] int32: (first flat token, rows <= 64, entry, first position)
-    q_tiles_wide: torch.Tensor = None  # the same for tiles of <= 128 rows
+    q_tiles_wide: torch.Tensor = None  # the same for tiles of <= 256 rows
     shared: dict = field(default_factory=dict)  # per-step values that several layers share (e.g. rotary tables)
 
 

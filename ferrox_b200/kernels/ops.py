@@ -227,7 +227,7 @@ def prefill_attention(q, k_pages, v_pages, block_table, page_size, tiles, seq_sl
     return out
 
 
-WIDE_PREFILL_TILE = 128
+WIDE_PREFILL_TILE = 256
 
 
 def prefill_tc_ok(q, out, k_pages, page_size, head_dim) -> bool:
@@ -240,7 +240,7 @@ def prefill_tc_ok(q, out, k_pages, page_size, head_dim) -> bool:
 def prefill_attention_tc(q, k_pages, v_pages, block_table, page_size, tiles, seq_slot, out, n_heads, n_kv_heads,
                          head_dim, window, scale, status=None, stream=None):
     """Flash attention of prompt portions on the tcgen05 tensor cores (bfloat16, head_dim 64 or 128, pages of a
-    multiple of 64 positions).  ``tiles``: int32 [n, 4] rows of (first flat token, rows <= 128, entry index,
+    multiple of 64 positions).  ``tiles``: int32 [n, 4] rows of (first flat token, rows <= 256, entry index,
     absolute position of the first row)."""
     call("fx_prefill_attention_tc", _ptr(q), _rows(q), q.shape[0], _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
          _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0], _ptr(seq_slot), _ptr(out),

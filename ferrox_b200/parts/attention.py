@@ -103,7 +103,7 @@ class GqaAttention(Mixer):
                 part_acc, part_ml, stream=batch.stream,
             )
         elif batch.q_tiles_wide is not None and ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
-            # prompt portions: tiles of 128 queries, tcgen05
+            # prompt portions: tiles of 256 queries, tcgen05
             ops.prefill_attention_tc(
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.q_tiles_wide, batch.seq_slot, attn,
                 s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, status=batch.status, stream=batch.stream,

@@ -548,7 +548,7 @@ TC_ATT_CASES = [
 
 @pytest.mark.parametrize("case", TC_ATT_CASES)
 def test_prefill_attention_tcgen05(case):
-    """Prompt portions through the tcgen05 kernel (tiles of 128 queries, blocks of 128 keys), whole prompts and
+    """Prompt portions through the tcgen05 kernel (tiles of 256 queries, blocks of 128 keys), whole prompts and
     continuations after a cached prefix, against the plain per-query statement.  One far key of the longest
     request is made to stand out for its last query, so that a block that is skipped or masked wrongly shows."""
     o = ops()
@@ -560,8 +560,8 @@ def test_prefill_attention_tcgen05(case):
     toks, tiles, flat = [], [], 0
     for s, (L, st) in enumerate(zip(lens, starts)):
         n = L - st
-        for i in range(0, n, 128):
-            tiles.append((flat + i, min(128, n - i), s, st + i))
+        for i in range(0, n, o.WIDE_PREFILL_TILE):
+            tiles.append((flat + i, min(o.WIDE_PREFILL_TILE, n - i), s, st + i))
         toks += [(s, p) for p in range(st, L)]
         flat += n
     T = len(toks)
