@@ -21,6 +21,9 @@ from ..weights.loader import TensorDecl
 from .base import FeedForward, register_part
 from .mlp import pack_gate_up
 
+# Up to this many tokens the shared expert runs on a second stream beside the routed experts.
+OVERLAP_SHARED_MAX_TOKENS = 32   # measured: a gain up to 32 tokens, a small loss at 64
+
 
 class SoftmaxTopkMoe(FeedForward):
     graph_safe = True
@@ -71,6 +74,26 @@ class SoftmaxTopkMoe(FeedForward):
             dtr = torch.float32 if torch.float32 in (self.w_router.dtype, self.w_shared_gate.dtype) else self.w_router.dtype
             self.w_route = torch.cat([self.w_router.to(dtr), self.w_shared_gate.to(dtr)], dim=0).contiguous()
         self._scratch = torch.zeros(2 * E, dtype=torch.int32, device=rt.device)
+        if self.w_shared_gu is not None and rt.device.type == "cuda":
+            self._side = torch.cuda.Stream(device=rt.device)
+            self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+
+    def _shared_expert(self, x, batch, st):
+        """silu(gate) * up, then down, of the expert that every token visits: [T, H]."""
+        s, rt = self.spec, self.rt
+        T, Is = x.shape[0], s.shared_intermediate
+        sact = rt.empty(T, Is)
+        if T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_shared_gu):
+            ops.gemm_skinny(x, self.w_shared_gu, sact, gated=True, stream=st)
+        elif T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_shared_gu):
+            ops.gemm_tc(x, self.w_shared_gu, sact, gated=True, status=batch.status, stream=st)
+        else:
+            sgu = rt.empty(T, 2 * Is)
+            ops.gemm(x, self.w_shared_gu, sgu, stream=st)
+            ops.silu_mul(sgu, sact, stream=st)
+        shared = rt.empty(T, s.hidden)
+        ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
+        return shared
 
     def forward_add(self, x, h, batch):
         s, rt, st = self.spec, self.rt, batch.stream
@@ -79,6 +102,17 @@ class SoftmaxTopkMoe(FeedForward):
         small = T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
         big = T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_gu) and I % 8 == 0
         n_route = self.w_route.shape[0]      # E router logits, then the shared expert's gate logit if it has one
+        # Few tokens: the shared expert's two products run on a second stream beside the routing and the routed
+        # experts (short kernels that leave most of the machine idle); both meet again at the combination.
+        shared = None
+        overlap = self.w_shared_gu is not None and T <= OVERLAP_SHARED_MAX_TOKENS
+        if overlap:
+            main = torch.cuda.current_stream()
+            self._fork.record(main)
+            self._side.wait_event(self._fork)
+            with torch.cuda.stream(self._side):
+                shared = self._shared_expert(x, batch, self._side.cuda_stream)
+                self._join.record(self._side)
         logits = rt.empty(T, n_route, dtype=torch.float32)
         ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
         ids = rt.empty(T, K, dtype=i32)
@@ -113,20 +147,12 @@ class SoftmaxTopkMoe(FeedForward):
             ops.silu_mul(gu, act, stream=st)
             ops.gemm(act, self.w_down, y, group_offsets=offsets, stream=st)
 
-        shared = gate_logit = None
+        gate_logit = None
         if self.w_shared_gu is not None:
-            Is = s.shared_intermediate
-            sact = rt.empty(T, Is)
-            if T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_shared_gu):
-                ops.gemm_skinny(x, self.w_shared_gu, sact, gated=True, stream=st)
-            elif T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_shared_gu):
-                ops.gemm_tc(x, self.w_shared_gu, sact, gated=True, status=batch.status, stream=st)
+            if overlap:
+                torch.cuda.current_stream().wait_event(self._join)
             else:
-                sgu = rt.empty(T, 2 * Is)
-                ops.gemm(x, self.w_shared_gu, sgu, stream=st)
-                ops.silu_mul(sgu, sact, stream=st)
-            shared = rt.empty(T, H)
-            ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
+                shared = self._shared_expert(x, batch, st)
             if self.w_shared_gate is not None:
                 gate_logit = logits[:, E:]      # [T, 1] view with the logits' row stride
         ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st)
