@@ -50,6 +50,10 @@ int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* sc
 int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, const void* bias,
                int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
                int gate_up_offset, const int* group_offsets, int n_groups, int* status, void* stream);
+int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, const void* bias,
+                    int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
+                    int gate_up_offset, const int* group_offsets, int n_groups, int tokens_per_tile, int* status,
+                    void* stream);
 int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo, int dtype, int n_rows, int width,
                    void* stream);
 int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_rope_table": [_P, _P, _I, _I, _P, _P],
     "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
+    "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P],
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
     "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P],
@@ -340,23 +341,68 @@ def gemm_tc(x, w, out, *, bias=None, accumulate=False, gated=False, group_offset
     return out
 
 
+def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_offsets=None, tokens_per_tile=0,
+                 status=None, stream=None):
+    """The same product as :func:`gemm_tc` with the roles swapped: 128 features of ``w`` fill the lanes of a tile,
+    the tokens its columns (multiples of 16 up to ``tokens_per_tile``: 32, 64 or 128; 0 = chosen from the sizes).
+    For few tokens per weight matrix: decode batches beyond the weight-streaming kernel's, experts of a prompt."""
+    M, N = out.shape
+    K = x.shape[1]
+    if group_offsets is not None:
+        G, wrows, ldw, wstride = w.shape[0], w.shape[1], w.stride(1), w.stride(0)
+    else:
+        G, wrows, ldw, wstride = 0, w.shape[0], w.stride(0), 0
+    if wrows != (2 * N if gated else N) or w.shape[-1] != K or x.shape[0] != M:
+        raise KernelError(f"gemm_tc_swap shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    call("fx_gemm_tc_swap", _ptr(x), _rows(x), _ptr(w), ldw, wstride, wrows, _ptr(bias), code(bias) if bias is not None else 0,
+         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0,
+         _ptr(group_offsets), G, int(tokens_per_tile), _ptr(status), stream if stream is not None else stream_ptr())
+    return out
+
+
 def gather_rows(x, rows, out, stream=None):
     call("fx_gather_rows", _ptr(x), _rows(x), _ptr(rows), _ptr(out), _rows(out), code(x), out.shape[0], x.shape[1],
          stream if stream is not None else stream_ptr())
     return out
 
 
+def swap_better(T: int, N: int, K: int) -> bool:
+    """Few tokens against a weight matrix: whether the tcgen05 kernel with the roles swapped (features in the
+    lanes, tokens in the columns, weights by TMA) beats the weight-streaming mma.sync kernel.  Measured on a
+    B200: beyond 32 tokens for matrices of a few thousand rows, from 8 tokens on for very large ones (the
+    vocabulary head); matrices of few rows give the swapped kernel too few tiles."""
+    return (T > 32 and N >= 4096) or (T >= 8 and N * K >= (1 << 27))
+
+
 def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None):
     """out (+)= x . w^T (+ bias): picks the kernel by size and element type."""
-    if (x.shape[0] > SKINNY_MAX_TOKENS and w.shape[0] <= SKINNY_MAX_TOKENS and bias is None and skinny_ok(w, x)):
+    T = x.shape[0]
+    if (T > SKINNY_MAX_TOKENS and w.shape[0] <= SKINNY_MAX_TOKENS and bias is None and skinny_ok(w, x)):
         # many tokens, a narrow output (router logits): the weight-streaming kernel with the roles swapped,
         # x streamed once as the "matrix", w as the few "tokens", stored transposed
         return gemm_skinny(w, x, out, accumulate=accumulate, transposed_out=True, stream=stream)
-    if x.shape[0] <= SKINNY_MAX_TOKENS and skinny_ok(x, w):
+    if T <= SKINNY_MAX_TOKENS and tc_ok(x, w) and swap_better(T, w.shape[0], w.shape[1]):
+        return gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
+    if T <= SKINNY_MAX_TOKENS and skinny_ok(x, w):
         return gemm_skinny(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
-    if x.shape[0] > SKINNY_MAX_TOKENS and tc_ok(x, w):
+    if T > SKINNY_MAX_TOKENS and tc_ok(x, w):
         return gemm_tc(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
     return gemm(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
+
+
+def gated_linear(x, w_gu, out, *, status=None, stream=None):
+    """out = silu(x . gate^T) * (x . up^T) with ``w_gu`` = [gate rows ; up rows]: picks the kernel as
+    :func:`linear` does; the gate|up intermediate reaches memory only on the CUDA-core path."""
+    T, I = out.shape
+    if T <= SKINNY_MAX_TOKENS and tc_ok(x, w_gu) and swap_better(T, 2 * I, x.shape[1]):
+        return gemm_tc_swap(x, w_gu, out, gated=True, status=status, stream=stream)
+    if T <= SKINNY_MAX_TOKENS and skinny_ok(x, w_gu):
+        return gemm_skinny(x, w_gu, out, gated=True, stream=stream)
+    if T > SKINNY_MAX_TOKENS and tc_ok(x, w_gu):
+        return gemm_tc(x, w_gu, out, gated=True, status=status, stream=stream)
+    gu = torch.empty(T, 2 * I, dtype=out.dtype, device=out.device)
+    gemm(x, w_gu, gu, stream=stream)
+    return silu_mul(gu, out, stream=stream)
 
 
 def moe_combine(h, y, inv_perm, topk_w, shared=None, shared_gate_logit=None, stream=None):

@@ -34,14 +34,7 @@ class SwigluMlp(FeedForward):
     def forward_add(self, x, h, batch):
         T, I = x.shape[0], self.spec.intermediate
         act = self.rt.empty(T, I)
-        if T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu):
-            ops.gemm_skinny(x, self.w_gu, act, gated=True, stream=batch.stream)  # silu(gate) * up in the epilogue
-        elif T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_gu):
-            ops.gemm_tc(x, self.w_gu, act, gated=True, status=batch.status, stream=batch.stream)
-        else:
-            gu = self.rt.empty(T, 2 * I)
-            ops.gemm(x, self.w_gu, gu, stream=batch.stream)
-            ops.silu_mul(gu, act, stream=batch.stream)
+        ops.gated_linear(x, self.w_gu, act, status=batch.status, stream=batch.stream)  # silu(gate) * up in the epilogue
         ops.linear(act, self.w_down, h, accumulate=True, status=batch.status, stream=batch.stream)
 
 

@@ -22,6 +22,27 @@ from .base import FeedForward, register_part
 from .mlp import pack_gate_up
 
 # Up to this many tokens the shared expert runs on a second stream beside the routed experts.
+# From this many tokens on the routed experts go through the tcgen05 kernel with swapped roles (measured).
+SWAP_MIN_TOKENS = 8
+
+
+def expert_tile_tokens(T: int, K: int, E: int):
+    """Tokens per tile of the swapped-role kernel for the (gate-up, down) products of the routed experts, by the
+    mean number of rows an expert gets; None where the 128-row tiles of the plain tcgen05 kernel are as good.
+    (Measured on a B200 with 60 experts: the smallest tile that holds most experts' rows in one pass wins; with
+    256 columns the gated form cannot double-buffer its accumulators and loses.)"""
+    r = T * K / max(E, 1)
+    if r <= 20:
+        return 32, 32
+    if r <= 40:
+        return 64, 64
+    if r <= 80:
+        return 128, 128
+    if r <= 160:
+        return 128, 256
+    return None
+
+
 OVERLAP_SHARED_MAX_TOKENS = 32   # measured: a gain up to 32 tokens, a small loss at 64
 
 
@@ -83,14 +104,7 @@ class SoftmaxTopkMoe(FeedForward):
         s, rt = self.spec, self.rt
         T, Is = x.shape[0], s.shared_intermediate
         sact = rt.empty(T, Is)
-        if T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_shared_gu):
-            ops.gemm_skinny(x, self.w_shared_gu, sact, gated=True, stream=st)
-        elif T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_shared_gu):
-            ops.gemm_tc(x, self.w_shared_gu, sact, gated=True, status=batch.status, stream=st)
-        else:
-            sgu = rt.empty(T, 2 * Is)
-            ops.gemm(x, self.w_shared_gu, sgu, stream=st)
-            ops.silu_mul(sgu, sact, stream=st)
+        ops.gated_linear(x, self.w_shared_gu, sact, status=batch.status, stream=st)
         shared = rt.empty(T, s.hidden)
         ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
         return shared
@@ -99,8 +113,10 @@ class SoftmaxTopkMoe(FeedForward):
         s, rt, st = self.spec, self.rt, batch.stream
         T, E, K, I, H = x.shape[0], s.n_experts, s.top_k, s.expert_intermediate, s.hidden
         i32 = torch.int32
-        small = T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
-        big = T > ops.SKINNY_MAX_TOKENS and ops.tc_ok(x, self.w_gu) and I % 8 == 0
+        tc = ops.tc_ok(x, self.w_gu) and I % 8 == 0
+        tiles = expert_tile_tokens(T, K, E) if tc and T >= SWAP_MIN_TOKENS else None
+        small = tiles is None and T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
+        big = T > ops.SKINNY_MAX_TOKENS and tc
         n_route = self.w_route.shape[0]      # E router logits, then the shared expert's gate logit if it has one
         # Few tokens: the shared expert's two products run on a second stream beside the routing and the routed
         # experts (short kernels that leave most of the machine idle); both meet again at the combination.
@@ -130,8 +146,17 @@ class SoftmaxTopkMoe(FeedForward):
 
         act = rt.empty(T * K, I)
         y = rt.empty(T * K, H)
-        if small:
-            # few tokens: every expert that was chosen is streamed once, gate/up fused with SiLU
+        if tiles is not None:
+            # a few rows for each expert: rows in expert order, then features in the lanes of the tensor-core tiles
+            # and the expert's rows in their columns
+            xp = rt.empty(T * K, H)
+            ops.gather_rows(x, src_token, xp, stream=st)
+            ops.gemm_tc_swap(xp, self.w_gu, act, gated=True, group_offsets=offsets, tokens_per_tile=tiles[0],
+                             status=batch.status, stream=st)
+            ops.gemm_tc_swap(act, self.w_down, y, group_offsets=offsets, tokens_per_tile=tiles[1],
+                             status=batch.status, stream=st)
+        elif small:
+            # very few tokens: every expert that was chosen is streamed once, gate/up fused with SiLU
             ops.gemm_skinny(x, self.w_gu, act, gated=True, x_rows=src_token, group_offsets=offsets,
                             active_groups=active, tokens_hint=T, stream=st)
             ops.gemm_skinny(act, self.w_down, y, group_offsets=offsets, active_groups=active, tokens_hint=T, stream=st)

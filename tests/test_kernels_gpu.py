@@ -491,6 +491,66 @@ def test_gemm_tc_grouped(counts):
         r += c
 
 
+@pytest.mark.parametrize("M,N,K,tnb", [(40, 300, 136, 0), (17, 128, 64, 32), (64, 2048, 5632, 0), (130, 520, 264, 0),
+                                       (300, 200, 96, 64), (5, 61, 2048, 0)])
+def test_gemm_tc_swap(M, N, K, tnb):
+    """Features in the lanes, tokens in the columns: plain, with bias, accumulating, into a strided view."""
+    o = ops()
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.2)
+    bias = rnd(N, seed=5)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = x.float() @ w.float().T
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc_swap(x, w, out, bias=bias, tokens_per_tile=tnb, status=status)
+    assert int(status) == 0
+    assert rel(out, want + bias) < TOL["bfloat16"]
+    acc = rnd(M, N, seed=3)
+    base = acc.clone()
+    o.gemm_tc_swap(x, w, acc, accumulate=True, tokens_per_tile=tnb, status=status)
+    assert int(status) == 0 and rel(acc, base + want) < 2e-5
+    wide = torch.full((M, N + 5), 7.0, device=DEV)
+    o.gemm_tc_swap(x, w, wide[:, :N], tokens_per_tile=tnb, status=status)
+    assert rel(wide[:, :N], want) < 2e-5 and float(wide[:, N:].min()) == 7.0
+
+
+@pytest.mark.parametrize("M,I,K", [(48, 100, 96), (64, 5632, 2048), (33, 1408, 256), (200, 300, 136)])
+def test_gemm_tc_swap_gated(M, I, K):
+    o = ops()
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(2 * I, K, dtype=torch.bfloat16, scale=0.2)
+    gate, up = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
+    out = torch.empty(M, I, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.gemm_tc_swap(x, w, out, gated=True, status=status)
+    assert int(status) == 0 and rel(out, gate / (1 + torch.exp(-gate)) * up) < 3e-5
+
+
+@pytest.mark.parametrize("counts", [[0, 130, 1, 0, 128, 255], [3, 0, 0, 0, 0, 700], [16, 17, 15, 64, 129, 1],
+                                    [137, 0, 512, 9] * 15])
+def test_gemm_tc_swap_grouped(counts):
+    o = ops()
+    G = len(counts)
+    I, H = (96, 128) if G < 10 else (320, 520)
+    R = sum(counts)
+    x = rnd(R, H, dtype=torch.bfloat16)
+    w_gu, w_down = rnd(G, 2 * I, H, dtype=torch.bfloat16, scale=0.1), rnd(G, H, I, dtype=torch.bfloat16, scale=0.1)
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    act = torch.full((R, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc_swap(x, w_gu, act, gated=True, group_offsets=offsets, status=status)
+    y = torch.empty(R, H, dtype=torch.float32, device=DEV)
+    o.gemm_tc_swap(act, w_down, y, group_offsets=offsets, status=status)
+    assert int(status) == 0
+    r = 0
+    for g, c in enumerate(counts):
+        if c == 0:
+            continue
+        gu = x[r:r + c].float() @ w_gu[g].float().T
+        want = gu[:, :I] / (1 + torch.exp(-gu[:, :I])) * gu[:, I:]
+        assert rel(act[r:r + c], want) < TOL["bfloat16"], g
+        assert rel(y[r:r + c], act[r:r + c].float() @ w_down[g].float().T) < 2e-5, g
+        r += c
+
+
 def test_gather_rows():
     o = ops()
     x = rnd(9, 72, dtype=torch.bfloat16)
