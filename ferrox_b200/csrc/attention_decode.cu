@@ -3,8 +3,9 @@
 // context keeps many SMs busy; a second kernel merges the ranges.
 //
 //   grid = (kv head [x head chunk], query token, split)
-//   split s covers the absolute key positions [s * split_len, (s+1) * split_len),
-//   clipped to the token's visible range [max(0, p - W + 1), p].
+//   split s covers the token's visible keys [max(0, p - W + 1), p] cut into n_splits runs of equal length
+//   (split_len 0), or the absolute key positions [s * split_len, (s+1) * split_len) clipped to the
+//   visible range (split_len > 0): fx_split_range in common.cuh.
 //
 // A block reads each key and value of its range once for all query heads that
 // share the kv head (up to 8; more are handled by further head chunks).  Threads
@@ -13,8 +14,8 @@
 // scores it with a group-wide sum and keeps a running (m, l, acc) per query head.
 // The groups are merged in fixed order through shared memory, the block writes
 // (m, l, acc) for its split to scratch memory, and `merge` combines the splits in
-// order.  All sums are 32-bit.  split_len depends on the step's size and the
-// context limit, never on the requests' current lengths.
+// order.  All sums are 32-bit.  The number of runs depends on the step's size and the
+// context limit; where a token's runs are cut depends on its own position only.
 //
 // Reference: one warp per head over a contiguous cache
 // (crates/ferrox-cuda/src/attn.rs:22-79); online softmax
@@ -77,8 +78,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
     const int tkn = blockIdx.y, split = blockIdx.z;
     const int pos = positions[tkn];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int k_begin = max(lo, split * split_len);
-    const int k_end = min(pos + 1, (split + 1) * split_len);
+    int k_begin, k_end;
+    fx_split_range(pos, lo, split, n_splits, split_len, k_begin, k_end);
     if (k_begin >= k_end) return;   // nothing of this range is visible: `merge` skips it by the same rule
     const int grp = threadIdx.x / LPK, ln = threadIdx.x % LPK;
 
@@ -259,12 +260,14 @@ __global__ void merge_kernel(const float* __restrict__ part_acc, const float* __
     // the splits that hold visible keys of this token (the others were not written)
     const int pos = positions[tkn];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int s_lo = lo / split_len, s_hi = min(n_splits - 1, pos / split_len);
+    auto has_keys = [&](int s) { int b, e; fx_split_range(pos, lo, s, n_splits, split_len, b, e); return b < e; };
     float mm = -INFINITY;
-    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    for (int s = 0; s < n_splits; ++s)
+        if (has_keys(s)) mm = fmaxf(mm, part_ml[(base + s) * 2]);
     for (int e = threadIdx.x; e < head_dim; e += blockDim.x) {
         float ll = 0.f, a = 0.f;
-        for (int s = s_lo; s <= s_hi; ++s) {
+        for (int s = 0; s < n_splits; ++s) {
+            if (!has_keys(s)) continue;
             const float ms = part_ml[(base + s) * 2];
             if (ms == -INFINITY) continue;
             const float w = fx_exp<T>(ms - mm);
@@ -362,7 +365,7 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
                                    float scale, int split_len, int n_splits, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
-    if (split_len <= 0 || n_splits <= 0) return FX_ERR_SIZE;
+    if (split_len < 0 || n_splits <= 0) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
@@ -399,7 +402,7 @@ extern "C" int fx_decode_attention_noalloc(const void* q, long ldq, const void* 
                                            int window, float scale, int split_len, int n_splits, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
-    if (split_len <= 0 || n_splits <= 0 || n_heads <= 0 || head_dim <= 0) return FX_ERR_SIZE;
+    if (split_len < 0 || n_splits <= 0 || n_heads <= 0 || head_dim <= 0) return FX_ERR_SIZE;
     // partial sums [tokens, heads, splits, head_dim] followed by (max, sum) pairs [tokens, heads, splits, 2]
     const long slots = (long)n_tokens * n_heads * n_splits;
     const long need = slots * head_dim + slots * 2;

@@ -64,8 +64,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     const int tkn = blockIdx.y, split = blockIdx.z;
     const int pos = positions[tkn];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int k_begin = max(lo, split * split_len);
-    const int k_end = min(pos + 1, (split + 1) * split_len);
+    int k_begin, k_end;
+    fx_split_range(pos, lo, split, n_splits, split_len, k_begin, k_end);
     if (k_begin >= k_end) return;   // nothing of this range is visible: `merge` skips it by the same rule
 
     extern __shared__ __align__(16) uint8_t smem[];

@@ -65,6 +65,22 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     return scratch[32];
 }
 
+// Key range [k_begin, k_end) of run `split` of a decoding token at position pos whose first visible key is lo.
+// split_len > 0: runs of split_len keys counted from position 0.  split_len == 0: the token's own visible keys,
+// counted from the multiple of 64 at or below lo, cut into n_splits runs of equal length (a multiple of 64), so
+// that every run has work whatever the context length is.  An empty range (k_begin >= k_end) has no block
+// result and is skipped when the runs are merged.
+__device__ __forceinline__ void fx_split_range(int pos, int lo, int split, int n_splits, int split_len, int& k_begin,
+                                               int& k_end) {
+    int base = 0, len = split_len;
+    if (split_len <= 0) {
+        base = lo & ~63;
+        len = (((pos + 1 - base) + n_splits - 1) / n_splits + 63) & ~63;
+    }
+    k_begin = max(lo, base + split * len);
+    k_end = min(pos + 1, base + (split + 1) * len);
+}
+
 // Programmatic dependent launch.  A kernel launched with fx_launch_pdl may be set up
 // on the GPU while the kernel before it on the stream is still running; it must
 // call fx_pdl_wait() before it touches anything that kernel wrote (here: first

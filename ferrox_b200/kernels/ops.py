@@ -296,15 +296,25 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
     return out
 
 
+DECODE_BLOCK_SLOTS = 148 * 3      # blocks of the decode attention kernel that run at the same time
+DECODE_BLOCK_OVERHEAD = 256       # start-up and merge of a block, in keys' worth of time
+DECODE_MAX_SPLITS = 16
+
+
 def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int):
-    """(split_len, n_splits) for :func:`decode_attention`: enough blocks to fill the
-    GPU, as a function of the step's size and the context limit only."""
-    target = 148 * 6
-    want = max(1, -(-target // max(1, n_tokens * n_kv_blocks)))
-    split_len = max(64, -(-max_positions // want))
-    split_len = -(-split_len // 64) * 64
-    n_splits = max(1, -(-max_positions // split_len))
-    return split_len, n_splits
+    """(split_len, n_splits) for :func:`decode_attention`.  split_len 0: every token's visible keys are cut
+    into n_splits runs of equal length, so that all blocks have work whatever the context length is.
+    n_splits is a function of the step's size and the context limit only (a CUDA graph keeps its grid): the
+    number of runs that minimises (waves of blocks) x (keys of a run + a block's fixed cost); a few blocks
+    beyond a whole wave cost a wave of their own, and many short runs pay the fixed cost too often."""
+    blocks = max(1, n_tokens * n_kv_blocks)
+    best, best_cost = 1, None
+    for n in range(1, min(DECODE_MAX_SPLITS, max(1, -(-max_positions // 64))) + 1):
+        waves = -(-blocks * n // DECODE_BLOCK_SLOTS)
+        cost = waves * (max_positions / n + DECODE_BLOCK_OVERHEAD)
+        if best_cost is None or cost < best_cost * 0.98:   # more runs only for a clear gain
+            best, best_cost = n, cost
+    return 0, best
 
 
 def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,

@@ -284,7 +284,7 @@ def test_attention_over_pages(dtype, case, kernel):
     if kernel == "generic":
         o.paged_attention(q, kp, vp, table, ps, positions, token_seq, seq_slot, out, nh, nkv, d, window, scale)
     else:
-        for split_len, n_splits in ((64, 5), (128, 3), (4096, 1)):
+        for split_len, n_splits in ((64, 5), (128, 3), (4096, 1), (0, 1), (0, 3), (0, 7)):
             pa = torch.empty(T, nh, n_splits, d, device=DEV)
             pm = torch.empty(T, nh, n_splits, 2, device=DEV)
             out.zero_()
