@@ -256,13 +256,20 @@ def main() -> int:
     e2e = None
     if not args.no_e2e:
         prompts = [random_prompt(PREFILL_TOKENS) for _ in range(args.batch)]
-        n_new = args.warmup + args.steps
+        # warm-up through the same entry point, twice: a batch size is run eagerly when it is first seen and
+        # captured as a CUDA graph the second time, and the requests, admitted one prompt a step, also end one
+        # after the other, so that every smaller batch size occurs once in each call
+        for _ in range(2):
+            eng.generate(prompts, max_new_tokens=max(3, args.warmup), temperature=0.0, ignore_eos=True,
+                         max_batch_tokens=PREFILL_TOKENS + args.batch)
+        n_new = args.steps + 1
         outs, stats = eng.generate(prompts, max_new_tokens=n_new, temperature=0.0, ignore_eos=True,
                                    max_batch_tokens=PREFILL_TOKENS + args.batch, return_stats=True)
         assert all(len(o) == n_new for o in outs)
         e2e = {"value": stats["decode_tokens"] / stats["decode_seconds"] if stats["decode_seconds"] > 0 else None,
                "unit": "tokens/s", "h2d_bytes_per_step": stats["h2d_bytes_per_decode_step"],
-               "d2h_bytes_per_step": stats["d2h_bytes_per_decode_step"], "decode_steps": stats["decode_steps"]}
+               "d2h_bytes_per_step": stats["d2h_bytes_per_decode_step"], "decode_steps": stats["decode_steps"],
+               "steps_issued_ahead": stats["ahead_steps"]}
 
     line = {
         "metric": "decode tokens/s at batch %d (Qwen1.5-MoE-A2.7B shape, context %d)" % (args.batch, CONTEXT),

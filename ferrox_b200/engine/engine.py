@@ -109,6 +109,15 @@ class Engine:
         """Run the entries' tokens as one batch; [wanted, vocab] float32 logits."""
         return _step(self.model, self.cache, entries, check=check, graphs=self.graphs)
 
+    def decode_ahead(self, slots, tokens):
+        """Greedy decoding of these requests issued one step ahead of the host (see
+        :class:`~ferrox_b200.engine.step.DecodeAhead`), or None while no graph of this batch size exists."""
+        from .step import DecodeAhead
+
+        if not DecodeAhead.ready(self.graphs, len(slots)):
+            return None
+        return DecodeAhead(self.model, self.cache, self.graphs, slots, tokens)
+
     # ---- generation -------------------------------------------------------------
     def generate(self, prompts, max_new_tokens=128, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
                  seed=0, ignore_eos=False, eos_token_id=None, max_batch_tokens=2048, return_stats=False):
@@ -138,6 +147,7 @@ class Engine:
             return outs, {
                 "steps": c.steps, "prefill_tokens": c.prefill_tokens, "decode_tokens": c.decode_step_tokens,
                 "decode_steps": c.decode_steps, "decode_seconds": c.decode_seconds, "preemptions": c.preemptions,
+                "ahead_steps": c.ahead_steps,
                 "h2d_bytes_per_decode_step": c.decode_h2d_bytes / n, "d2h_bytes_per_decode_step": c.decode_d2h_bytes / n,
             }
         return outs

@@ -89,6 +89,7 @@ class Counters:
     decode_seconds: float = 0.0  # host wall time of those steps, sampling and read-back included
     decode_h2d_bytes: int = 0
     decode_d2h_bytes: int = 0
+    ahead_steps: int = 0  # decode steps issued before the host had read the step before them
 
 
 class Scheduler:
@@ -263,21 +264,10 @@ class Scheduler:
             ids = self.sampler.sample(logits, [r.params for r in sampled_from], [r.rng for r in sampled_from],
                                       [r.generated for r in sampled_from])
             for r, tok in zip(sampled_from, ids):
-                if tok in r.eos_ids:
-                    r.finish_reason = "stop"
-                else:
-                    r.generated.append(int(tok))
-                    if len(r.generated) >= r.max_new:
-                        r.finish_reason = "length"
-                    elif len(r.prompt) + len(r.generated) >= self.cache.max_positions:
-                        r.finish_reason = "context"
+                self._take_token(r, int(tok))
                 if r.finish_reason:
                     finished.append(r)
-        for r in finished:
-            self.cache.close_request(r.slot)
-            self.running.remove(r)
-            r.slot = None
-            self.counters.finished += 1
+        self._retire(finished)
         if all_decode:
             from . import step as _stepmod
 
@@ -291,4 +281,88 @@ class Scheduler:
 
     def run(self) -> None:
         while not self.idle:
-            self.step()
+            if not self._decode_ahead():
+                self.step()
+
+    # ---- decoding issued ahead of the host ----------------------------------------------
+    def _decode_ahead(self) -> bool:
+        """While nothing waits, every running request is decoding greedily and a CUDA graph of this batch size
+        exists, steps are issued one ahead: the host reads a step's tokens while the next step runs.  Only
+        lengths decide how many steps may be issued (no request reaches its limit inside the run); an end-of-
+        sequence token shows one step late, the step issued meanwhile for that request is thrown away.  Pages
+        that run out end the run before the step that lacks them: the ordinary step then decides.
+        Returns False when it did nothing."""
+        issue = getattr(self.engine, "decode_ahead", None)
+        if issue is None or self.waiting or not self.running or len(self.running) > self.max_batch_tokens:
+            return False
+        reqs = sorted(self.running, key=lambda q: q.admitted_at)
+        for r in reqs:
+            if r.pending != 1 or not r.generated or not (r.params.greedy and r.params.repetition_penalty == 1.0):
+                return False
+        ctx = self.cache.max_positions
+        n_safe = min(min(r.max_new - len(r.generated), ctx - len(r.prompt) - len(r.generated)) for r in reqs)
+        if n_safe < 2:
+            return False
+        run = issue([r.slot for r in reqs], [r.generated[-1] for r in reqs])
+        if run is None:
+            return False
+        from .step import OutOfPages
+
+        t0 = time.perf_counter()
+        stop = False
+        h2d = 0
+        while run.issued < n_safe and not stop:
+            try:
+                run.issue()
+            except OutOfPages:
+                break
+            from . import step as _stepmod
+
+            h2d += _stepmod.last_h2d_bytes
+            for r in reqs:
+                r.fed += 1
+            if run.issued - run.collected == 2:
+                stop = self._absorb(reqs, run.collect())
+        if run.issued == 0:
+            return False
+        while run.collected < run.issued:
+            self._absorb(reqs, run.collect())
+        run.close()
+        c = self.counters
+        c.steps += run.issued
+        c.decode_steps += run.issued
+        c.ahead_steps += run.issued
+        c.decode_seconds += time.perf_counter() - t0
+        c.decode_h2d_bytes += h2d
+        c.decode_d2h_bytes += 4 * len(reqs) * run.issued
+        self._retire([r for r in reqs if r.finish_reason])
+        return True
+
+    def _absorb(self, reqs, tokens) -> bool:
+        """Takes one step's chosen tokens; True when a request ended with them."""
+        ended = False
+        for r, tok in zip(reqs, tokens):
+            if r.finish_reason:
+                continue   # ended a step ago: this token came from the step issued meanwhile
+            self.counters.decode_tokens += 1
+            self.counters.decode_step_tokens += 1
+            self._take_token(r, int(tok))
+            ended = ended or bool(r.finish_reason)
+        return ended
+
+    def _take_token(self, r: Request, tok: int) -> None:
+        if tok in r.eos_ids:
+            r.finish_reason = "stop"
+        else:
+            r.generated.append(tok)
+            if len(r.generated) >= r.max_new:
+                r.finish_reason = "length"
+            elif len(r.prompt) + len(r.generated) >= self.cache.max_positions:
+                r.finish_reason = "context"
+
+    def _retire(self, finished) -> None:
+        for r in finished:
+            self.cache.close_request(r.slot)
+            self.running.remove(r)
+            r.slot = None
+            self.counters.finished += 1

@@ -144,6 +144,7 @@ class GraphedDecode:
             arr[b], arr[B + b], arr[3 * B + b] = e.tokens[0], e.start, e.slot
         buf = torch.empty(n, dtype=torch.int32, device=dev)
         buf.copy_(host)
+        chosen = torch.zeros(B, dtype=torch.int32, device=dev)   # arg max of each row of the logits, for steps issued ahead
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
@@ -154,5 +155,96 @@ class GraphedDecode:
                 entries=list(entries), max_len=self.cache.max_positions, max_new=1, h2d_bytes=4 * n,
             )
             logits = self.model.forward(batch, lambda entry: self.cache.layer_cache(entry.cache, entry.writes_cache))
+            ops.argmax(logits, chosen)
         self.kernels_per_replay[B] = ops.launch_count() - before
-        self.graphs[B] = {"graph": graph, "host": host, "dev": buf, "logits": logits, "event": torch.cuda.Event()}
+        self.graphs[B] = {
+            "graph": graph, "host": host, "dev": buf, "logits": logits, "event": torch.cuda.Event(), "chosen": chosen,
+            # steps issued ahead: two pinned buffers each way, used in turn
+            "ahead_in": [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(2)],
+            "ahead_in_done": [torch.cuda.Event() for _ in range(2)],
+            "ahead_out": [torch.empty(B, dtype=torch.int32).pin_memory() for _ in range(2)],
+            "ahead_out_done": [torch.cuda.Event() for _ in range(2)],
+        }
+        for h in self.graphs[B]["ahead_in"]:
+            h.copy_(host)
+
+    # ---- steps issued ahead of the host ------------------------------------------------
+    def replay_ahead(self, B, starts, slots, tokens, turn: int) -> None:
+        """Replay the graph of size B without waiting for anything.  ``tokens`` None: the step's tokens are the
+        ones the previous replay of this size chose (arg max), which never left the device.  The chosen tokens
+        of this replay travel to pinned memory behind it; :meth:`chosen_tokens` waits for them."""
+        g = self.graphs[B]
+        g["ahead_in_done"][turn].synchronize()
+        host = g["ahead_in"][turn]
+        arr = host.numpy()
+        arr[B:2 * B] = starts
+        arr[3 * B:4 * B] = slots
+        if tokens is not None:
+            arr[:B] = tokens
+            g["dev"].copy_(host, non_blocking=True)
+        else:
+            g["dev"][B:].copy_(host[B:], non_blocking=True)
+            g["dev"][:B].copy_(g["chosen"], non_blocking=True)
+        g["ahead_in_done"][turn].record()
+        g["graph"].replay()
+        ops.count_launches(self.kernels_per_replay[B])
+        g["ahead_out"][turn].copy_(g["chosen"], non_blocking=True)
+        g["ahead_out_done"][turn].record()
+
+    def chosen_tokens(self, B, turn: int):
+        g = self.graphs[B]
+        g["ahead_out_done"][turn].synchronize()
+        return g["ahead_out"][turn].tolist()
+
+
+class DecodeAhead:
+    """Greedy decode steps of a fixed set of requests, issued one step ahead of the host: step k+1 is on the
+    stream before the host has read what step k chose.  The chosen token of a request is fed to its next step
+    on the device; the host reads it one step later, from pinned memory.  A step maps its pages and advances
+    the requests' lengths when it is issued (both depend on counts only, not on the tokens)."""
+
+    def __init__(self, model, cache, graphs, slots, tokens):
+        self.model, self.cache, self.graphs = model, cache, graphs
+        self.slots, self.first_tokens = list(slots), list(tokens)
+        self.B = len(self.slots)
+        self.issued = self.collected = 0
+
+    @staticmethod
+    def ready(graphs, n: int) -> bool:
+        return graphs is not None and n in graphs.graphs
+
+    def issue(self) -> None:
+        """Maps a page where a request needs one (all requests or none: OutOfPages before any change), then
+        replays the step."""
+        global last_h2d_bytes
+        cache = self.cache
+        starts = [cache.seq_len[s] for s in self.slots]
+        wanted = {}
+        for s, st in zip(self.slots, starts):
+            for key, n in cache.pages_needed(s, st + 1).items():
+                wanted[key] = wanted.get(key, 0) + n
+        if not cache.can_reserve(wanted):
+            raise OutOfPages(f"step needs {wanted} pages, free: {cache.free_pages()}")
+        for s, st in zip(self.slots, starts):
+            ok = cache.reserve(s, st + 1)
+            assert ok
+        cache.sync_tables()
+        first = self.issued == 0
+        self.graphs.replay_ahead(self.B, starts, self.slots, self.first_tokens if first else None, self.issued & 1)
+        last_h2d_bytes = (20 if first else 16) * self.B
+        for s, st in zip(self.slots, starts):
+            cache.commit(s, st + 1)
+        self.issued += 1
+
+    def collect(self):
+        """The tokens chosen by the oldest step not read yet (waits for it)."""
+        toks = self.graphs.chosen_tokens(self.B, self.collected & 1)
+        self.collected += 1
+        return toks
+
+    def close(self) -> None:
+        status = _status(self.model.rt.device)
+        code = int(status.item())
+        if code:
+            status.zero_()
+            raise StepFault(f"a step issued ahead met fault code {code}")

@@ -54,6 +54,31 @@ def test_generation_with_preemption_gives_the_same_tokens(folders):
     assert outs == want
 
 
+def test_decoding_issued_ahead_gives_the_same_tokens(folders):
+    """Greedy decode steps run one ahead of the host once a graph of the batch size exists: same tokens; an
+    end-of-sequence token that shows one step late ends its request at the right place; limits that differ."""
+    cfg, w = plain.load_model(folders["A"])
+    prompts = [[5, 9, 200, 31], [7, 8], list(range(40, 60))]
+    free = [plain.greedy(cfg, w, p, 24) for p in prompts]
+    eng = engine(folders["A"])
+    outs, stats = eng.generate(prompts, max_new_tokens=24, return_stats=True)
+    assert outs == free and stats["ahead_steps"] >= 10
+    eos = free[1][15]
+    want = [f[:f.index(eos)] if eos in f else f for f in free]
+    outs, stats = eng.generate(prompts, max_new_tokens=24, eos_token_id=eos, return_stats=True)
+    assert outs == want and stats["ahead_steps"] >= 5
+    eng.cache.check_invariants()
+    assert eng.cache.n_free_slots == 4
+    # few pages: the run ends where a page is missing and the ordinary step preempts
+    small = engine(folders["A"], page_size=4, n_pages=16, max_slots=4)
+    outs, stats = small.generate(prompts, max_new_tokens=24, return_stats=True)
+    assert outs == free and stats["preemptions"] >= 1
+    small.cache.check_invariants()
+    # bfloat16 through the same path: as many tokens as asked for
+    outs, stats = engine(folders["A"], "bfloat16").generate(prompts, max_new_tokens=24, return_stats=True)
+    assert [len(o) for o in outs] == [24, 24, 24] and stats["ahead_steps"] >= 10
+
+
 def test_long_decoding_stays_on_the_plain_implementation(folders):
     """One token at a time up to the context's end (pages and, for B, the window roll over many times)."""
     for name in ("A", "B"):
