@@ -169,3 +169,119 @@ def test_random_load_with_window_group_and_tight_pool(seed):
         assert s.result(i) == alone(p, n)
     assert all(v == eng.cache.groups[k].pool.n_pages for k, v in eng.cache.free_pages().items())
     assert eng.cache.n_free_slots == eng.cache.max_slots
+
+
+# ---- decoding issued one step ahead of the host ---------------------------------------------------
+class FakeAheadRun:
+    """What DecodeAhead does on the GPU, on the CPU: a step is 'issued' (pages mapped, lengths advanced,
+    the token chosen by the 'device' kept there) and its tokens are handed out later, oldest first."""
+
+    def __init__(self, eng, slots, tokens):
+        self.eng, self.slots = eng, list(slots)
+        self.device_tokens = list(tokens)
+        self.queue = []
+        self.issued = self.collected = 0
+
+    def issue(self):
+        from ferrox_b200.engine.step import OutOfPages
+
+        cache = self.eng.cache
+        wanted = {}
+        for s in self.slots:
+            for key, n in cache.pages_needed(s, cache.seq_len[s] + 1).items():
+                wanted[key] = wanted.get(key, 0) + n
+        if not cache.can_reserve(wanted):
+            raise OutOfPages("no page")
+        chosen = []
+        for s, t in zip(self.slots, self.device_tokens):
+            start = cache.seq_len[s]
+            assert len(self.eng.history[s]) == start
+            assert cache.reserve(s, start + 1)
+            self.eng.history[s].append(t)
+            chosen.append(next_token(self.eng.history[s]))
+            cache.commit(s, start + 1)
+        cache.check_invariants()
+        self.device_tokens = chosen
+        self.queue.append(chosen)
+        self.issued += 1
+        assert self.issued - self.collected <= 2, "more than one step ahead of the host"
+
+    def collect(self):
+        self.collected += 1
+        return self.queue.pop(0)
+
+    def close(self):
+        assert not self.queue
+
+
+class FakeAheadEngine(FakeEngine):
+    def __init__(self, *a, ready_after=2, **kw):
+        super().__init__(*a, **kw)
+        self.sizes_seen = {}
+        self.ready_after = ready_after
+        self.ahead_runs = 0
+
+    def step(self, entries):
+        if all(len(e.tokens) == 1 for e in entries):
+            self.sizes_seen[len(entries)] = self.sizes_seen.get(len(entries), 0) + 1
+        return super().step(entries)
+
+    def decode_ahead(self, slots, tokens):
+        if self.sizes_seen.get(len(slots), 0) < self.ready_after:   # "no graph of this size yet"
+            return None
+        self.ahead_runs += 1
+        return FakeAheadRun(self, slots, tokens)
+
+
+def make_greedy(engine, budget=16):
+    # the real sampler's plain path is an arg max too; the requests' parameters must say "greedy"
+    return Scheduler(engine, max_batch_tokens=budget, sampler=ArgmaxSampler())
+
+
+def test_steps_issued_ahead_give_the_same_tokens_and_respect_limits():
+    eng = FakeAheadEngine(n_pages=32, page_size=4, max_slots=3)
+    s = make_greedy(eng)
+    prompts = [[3, 1, 4], [1, 5, 9, 2, 6], [5, 3]]
+    limits = [20, 9, 14]
+    ids = [s.add_request(p, n) for p, n in zip(prompts, limits)]
+    s.run()
+    assert [s.result(i) for i in ids] == [alone(p, n) for p, n in zip(prompts, limits)]
+    assert eng.ahead_runs >= 2 and s.counters.ahead_steps >= 8
+    assert s.cache.n_free_slots == 3
+    eng.cache.check_invariants()
+
+
+def test_end_of_sequence_shows_one_step_late_and_the_extra_step_is_dropped():
+    prompts = [[3, 1, 4], [1, 5, 9, 2, 6]]
+    free = [alone(p, 16) for p in prompts]
+    eos = free[0][9]
+    want = [f[:f.index(eos)] if eos in f else f for f in free]
+    eng = FakeAheadEngine(n_pages=32, page_size=4, max_slots=2)
+    s = make_greedy(eng)
+    ids = [s.add_request(p, 16, eos_ids=(eos,)) for p in prompts]
+    s.run()
+    assert [s.result(i) for i in ids] == want
+    assert s.requests[ids[0]].finish_reason == "stop"
+    assert eng.ahead_runs >= 1 and s.cache.n_free_slots == 2
+    eng.cache.check_invariants()
+
+
+def test_pages_run_out_inside_a_run_issued_ahead():
+    prompts = [[1, 2, 3], [4, 5, 6], [7, 8, 9]]
+    want = [alone(p, 14) for p in prompts]
+    eng = FakeAheadEngine(n_pages=9, page_size=4, max_slots=3)   # 3 x 16 positions do not fit 36
+    s = make_greedy(eng)
+    ids = [s.add_request(p, 14) for p in prompts]
+    s.run()
+    assert [s.result(i) for i in ids] == want
+    assert s.counters.preemptions >= 1 and eng.ahead_runs >= 1
+    eng.cache.check_invariants()
+
+
+def test_sampled_requests_are_never_issued_ahead():
+    eng = FakeAheadEngine(n_pages=32, page_size=4, max_slots=2, ready_after=0)
+    s = make_greedy(eng)
+    s.add_request([1, 2, 3], 8, SamplingParams(temperature=0.7, seed=1))
+    s.add_request([4, 5], 8)
+    s.run()
+    assert eng.ahead_runs == 0
