@@ -241,27 +241,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
                 const int kb = j * BKEY;
                 // every key of the block visible to every row of the sub-tile: no masking (most blocks)
                 const bool interior = kb + BKEY - 1 <= pos0_t && (a.window <= 0 || kb >= pos0_t + BQ - a.window);
-                uint32_t s[64];
-                // first pass over the row of S, in halves of 64 columns: its maximum
+                // The row of S is read in chunks of 32 columns into two register buffers in turn: the load of the
+                // next chunk is in flight while the current one is worked on.
+                uint32_t ca[32], cb[32], pk[32];
+                auto mask = [&](uint32_t* c, int chunk) {
+                    if (interior) return;
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) {
+                        const int key = kb + chunk * 32 + k;
+                        if (key > p_r || key < lo_r) c[k] = 0xff800000u;   // -inf
+                    }
+                };
+                // first pass: the row's maximum
                 float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                auto take_max = [&](uint32_t* c, int chunk) {
+                    mask(c, chunk);
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    tc_ld32(ts + hf * 64, s);
-                    tc_ld32(ts + hf * 64 + 32, s + 32);
-                    tc_ld_wait();
-                    if (!interior) {
-#pragma unroll
-                        for (int k = 0; k < 64; ++k) {
-                            const int key = kb + hf * 64 + k;
-                            if (key > p_r || key < lo_r) s[k] = 0xff800000u;   // -inf
-                        }
+                    for (int k = 0; k < 32; k += 4) {
+                        mx0 = fmaxf(mx0, __uint_as_float(c[k])); mx1 = fmaxf(mx1, __uint_as_float(c[k + 1]));
+                        mx2 = fmaxf(mx2, __uint_as_float(c[k + 2])); mx3 = fmaxf(mx3, __uint_as_float(c[k + 3]));
                     }
-#pragma unroll
-                    for (int k = 0; k < 64; k += 4) {
-                        mx0 = fmaxf(mx0, __uint_as_float(s[k])); mx1 = fmaxf(mx1, __uint_as_float(s[k + 1]));
-                        mx2 = fmaxf(mx2, __uint_as_float(s[k + 2])); mx3 = fmaxf(mx3, __uint_as_float(s[k + 3]));
-                    }
-                }
+                };
+                tc_ld32(ts, ca);
+                tc_ld_wait_for(ca);
+                tc_ld32(ts + 32, cb); take_max(ca, 0); tc_ld_wait_for(cb);
+                tc_ld32(ts + 64, ca); take_max(cb, 1); tc_ld_wait_for(ca);
+                tc_ld32(ts + 96, cb); take_max(ca, 2); tc_ld_wait_for(cb);
+                tc_ld32(ts, ca);      take_max(cb, 3);   // chunk 0 again, for the second pass
                 const float mn = fmaxf(fmaxf(m, fmaxf(mx0, mx1)), fmaxf(mx2, mx3));
                 const bool raise = mn > m && (m == -INFINITY || (mn - m) * sl2 > RAISE_MAX_BY);
                 if (__any_sync(0xffffffffu, raise)) {
@@ -271,41 +277,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
                     if (cnt > 0) {   // the sums so far of this row, in tensor memory, take the new reference too
 #pragma unroll
                         for (int c = 0; c < D / 32; ++c) {
-                            uint32_t ob[32];
-                            tc_ld32(to + c * 32, ob);
-                            tc_ld_wait();
+                            tc_ld32(to + c * 32, cb);
+                            tc_ld_wait_for(cb);
 #pragma unroll
-                            for (int k = 0; k < 32; ++k) ob[k] = __float_as_uint(__uint_as_float(ob[k]) * alpha);
-                            tc_st32(to + c * 32, ob);
+                            for (int k = 0; k < 32; ++k) cb[k] = __float_as_uint(__uint_as_float(cb[k]) * alpha);
+                            tc_st32(to + c * 32, cb);
                         }
                     }
                 }
                 // second pass: P = exp2(S * scale - reference), as bfloat16 pairs over the first 64 columns of S
-                // (columns 0-31 are written after columns 0-63 were read, columns 32-63 after 64-127)
+                // (columns 0-31 are written after columns 0-63 were read, columns 32-63 after all were)
                 const float ref = m == -INFINITY ? 0.f : m * sl2;
                 float sum0 = 0.f, sum1 = 0.f;
+                auto take_exp = [&](uint32_t* c, int chunk, uint32_t* out) {
+                    mask(c, chunk);
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    tc_ld32(ts + hf * 64, s);
-                    tc_ld32(ts + hf * 64 + 32, s + 32);
-                    tc_ld_wait();
-                    if (!interior) {
-#pragma unroll
-                        for (int k = 0; k < 64; ++k) {
-                            const int key = kb + hf * 64 + k;
-                            if (key > p_r || key < lo_r) s[k] = 0xff800000u;
-                        }
-                    }
-#pragma unroll
-                    for (int k = 0; k < 64; k += 2) {
-                        const float e0 = fast_exp2(fmaf(__uint_as_float(s[k]), sl2, -ref));
-                        const float e1 = fast_exp2(fmaf(__uint_as_float(s[k + 1]), sl2, -ref));
+                    for (int k = 0; k < 32; k += 2) {
+                        const float e0 = fast_exp2(fmaf(__uint_as_float(c[k]), sl2, -ref));
+                        const float e1 = fast_exp2(fmaf(__uint_as_float(c[k + 1]), sl2, -ref));
                         sum0 += e0; sum1 += e1;
                         __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-                        s[k >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+                        out[k >> 1] = *reinterpret_cast<uint32_t*>(&pr);
                     }
-                    tc_st32(ts + hf * 32, s);
-                }
+                };
+                tc_ld_wait_for(ca);
+                tc_ld32(ts + 32, cb); take_exp(ca, 0, pk);      tc_ld_wait_for(cb);
+                tc_ld32(ts + 64, ca); take_exp(cb, 1, pk + 16); tc_ld_wait_for(ca);
+                tc_ld32(ts + 96, cb);
+                tc_st32(ts, pk);                                 // the loads of columns 0-63 have completed
+                take_exp(ca, 2, pk);
+                tc_ld_wait_for(cb);
+                take_exp(cb, 3, pk + 16);
+                tc_st32(ts + 32, pk);
                 l += sum0 + sum1;
                 tc_st_wait();
                 tc_fence_before();
