@@ -165,7 +165,9 @@ def compute(ref_root):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of the reference>")
+    root = sys.argv[1]
     res = compute(root)
     for k, v in res.items():
         err = max(abs(a - b) for a, b in zip(v["plain_logits"], v["reference_logits"]))
