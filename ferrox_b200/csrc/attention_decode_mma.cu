@@ -121,8 +121,12 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             if (ch == 0) fl[r] = ok ? 1 : 0;
         }
     };
-    load_tile(0, 0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    // the ring: STAGES - 1 tiles are in flight beside the one being worked on
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        if (i < n_tiles) load_tile(i, i);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
 
     constexpr int KS = DMAX / 16, ON = DMAX / 8;
     const int ks_n = head_dim / 16;
@@ -133,10 +137,10 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g + 8
 
     for (int tile = 0; tile < n_tiles; ++tile) {
-        const int buf = tile & 1;
-        if (tile + 1 < n_tiles) load_tile(tile + 1, buf ^ 1);
+        const int buf = tile % STAGES;
+        if (tile + STAGES - 1 < n_tiles) load_tile(tile + STAGES - 1, (tile + STAGES - 1) % STAGES);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
         __syncthreads();
         if (tile == 0) {
 #pragma unroll
