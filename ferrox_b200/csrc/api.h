@@ -54,6 +54,9 @@ int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw, long w_gro
                     int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
                     int gate_up_offset, const int* group_offsets, int n_groups, int tokens_per_tile, int* status,
                     void* stream);
+int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int w_rows, const void* bias, int bias_dtype, void* C,
+                int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated, int gate_up_offset, int* status,
+                void* stream);
 int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo, int dtype, int n_rows, int width,
                    void* stream);
 int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,

@@ -226,16 +226,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                     bias_s[quad][j] = tc.n0 + j < a.N ? load_any(a.bias, a.bias_dtype, tc.n0 + j) : 0.f;
                 __syncwarp();
             }
+            // Accumulating into 32-bit rows: the values already there are fetched one chunk ahead, the first chunk
+            // before the wait for the accumulator, so that their latency hides behind the products.
+            const bool row_ok = row < tc.row_end;
+            const bool acc_ahead = !GATED && a.accumulate && a.c_dtype == FX_F32 && a.ldc % 4 == 0 && row_ok;
+            float4 pre[8], nxt[8];
+            auto fetch_c = [&](int c, float4* buf4) {
+                const int nb = tc.n0 + c * 32;
+                if (acc_ahead && c < OUT_N / 32 && nb + 32 <= a.N) {
+                    const float4* cp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.C) + (long)row * a.ldc + nb);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) buf4[j] = cp[j];
+                }
+            };
+            fetch_c(0, pre);
             const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (uint32_t)((it >> 1) & 1), abort_flag));
             if (!ok) break;
             tc_fence_after();
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
-            const bool row_ok = row < tc.row_end;
 #pragma unroll 1
             for (int c = 0; c < OUT_N / 32; ++c) {
                 uint32_t r[32], u[32];
                 tc_ld32(lane_addr + c * 32, r);
                 if (GATED) tc_ld32(lane_addr + BN / 2 + c * 32, u);
+                fetch_c(c + 1, nxt);
                 tc_ld_wait();
                 if (c == OUT_N / 32 - 1) {
                     // everything of this accumulator is in registers: hand it back to the tensor cores
@@ -261,7 +275,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                         for (int j = 0; j < 32; j += 4) {
                             float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                             if (a.accumulate) {
-                                const float4 p = *reinterpret_cast<const float4*>(cp + j);
+                                const float4 p = acc_ahead ? pre[j >> 2] : *reinterpret_cast<const float4*>(cp + j);
                                 o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
                             }
                             *reinterpret_cast<float4*>(cp + j) = o;
@@ -288,6 +302,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                             cp[j] = __float2bfloat16_rn(a.accumulate ? __bfloat162float(cp[j]) + v[j] : v[j]);
                     }
                 }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pre[j] = nxt[j];
             }
         }
     }

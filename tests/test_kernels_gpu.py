@@ -453,6 +453,38 @@ def test_gemm_tc_dense(M, N, K):
     assert rel(out32, wide[:, :K].float() @ w.float().T) < 2e-5
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 136), (2048, 2048, 2048), (70, 100, 96), (1000, 6144, 264)])
+def test_gemm_tc2_pairs_of_sms(M, N, K):
+    """The dense product on pairs of SMs (cta_group::2): plain with bias, accumulating, into a strided view."""
+    o = ops()
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.2)
+    bias = rnd(N, seed=5)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = x.float() @ w.float().T
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc2(x, w, out, bias=bias, status=status)
+    assert int(status) == 0
+    assert rel(out, want + bias) < TOL["bfloat16"]
+    acc = rnd(M, N, seed=3)
+    base = acc.clone()
+    o.gemm_tc2(x, w, acc, accumulate=True, status=status)
+    assert int(status) == 0 and rel(acc, base + want) < 2e-5
+    wide = torch.full((M, N + 5), 7.0, device=DEV)
+    o.gemm_tc2(x, w, wide[:, :N], status=status)
+    assert rel(wide[:, :N], want) < 2e-5 and float(wide[:, N:].min()) == 7.0
+
+
+@pytest.mark.parametrize("M,I,K", [(256, 128, 64), (200, 1408, 256), (70, 100, 96), (2048, 5632, 2048)])
+def test_gemm_tc2_gated(M, I, K):
+    o = ops()
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(2 * I, K, dtype=torch.bfloat16, scale=0.2)
+    gate, up = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
+    out = torch.empty(M, I, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.gemm_tc2(x, w, out, gated=True, status=status)
+    assert int(status) == 0 and rel(out, gate / (1 + torch.exp(-gate)) * up) < 3e-5
+
+
 @pytest.mark.parametrize("M,I,K", [(128, 64, 64), (200, 1408, 256), (70, 100, 96), (2048, 5632, 2048), (700, 300, 136)])
 def test_gemm_tc_gated(M, I, K):
     o = ops()
