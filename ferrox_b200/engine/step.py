@@ -64,7 +64,8 @@ def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True, grap
     if logits is None:
         batch = flatten(entries, model.rt.device, status, ops.stream_ptr())
         last_h2d_bytes = batch.h2d_bytes
-        logits = model.forward(batch, lambda entry: cache.layer_cache(entry.cache, entry.writes_cache))
+        with ops.stream_scope(batch.stream):
+            logits = model.forward(batch, lambda entry: cache.layer_cache(entry.cache, entry.writes_cache))
     for e in entries:
         cache.commit(e.slot, e.start + len(e.tokens))
     if check:
@@ -154,8 +155,9 @@ class GraphedDecode:
                 seq_slot=buf[3 * B:4 * B], want_rows=buf[4 * B:], status=status, stream=ops.stream_ptr(),
                 entries=list(entries), max_len=self.cache.max_positions, max_new=1, h2d_bytes=4 * n,
             )
-            logits = self.model.forward(batch, lambda entry: self.cache.layer_cache(entry.cache, entry.writes_cache))
-            ops.argmax(logits, chosen)
+            with ops.stream_scope(batch.stream):
+                logits = self.model.forward(batch, lambda entry: self.cache.layer_cache(entry.cache, entry.writes_cache))
+                ops.argmax(logits, chosen)
         self.kernels_per_replay[B] = ops.launch_count() - before
         self.graphs[B] = {
             "graph": graph, "host": host, "dev": buf, "logits": logits, "event": torch.cuda.Event(), "chosen": chosen,

@@ -103,8 +103,31 @@ def call(name: str, *args) -> None:
         raise KernelError(f"{name}: refused: {_ERRORS.get(rc, rc)}")
 
 
+_scoped_stream = None
+
+
 def stream_ptr() -> int:
+    """The stream kernels go to when none is named: the one a step has announced, else torch's current stream."""
+    if _scoped_stream is not None:
+        return _scoped_stream
     return torch.cuda.current_stream().cuda_stream
+
+
+class stream_scope:
+    """While a step runs, its stream is known: asking torch for the current stream costs more than a launch."""
+
+    def __init__(self, ptr: int):
+        self.ptr = ptr
+
+    def __enter__(self):
+        global _scoped_stream
+        self.prev, _scoped_stream = _scoped_stream, self.ptr
+        return self
+
+    def __exit__(self, *exc):
+        global _scoped_stream
+        _scoped_stream = self.prev
+        return False
 
 
 def code(t: torch.Tensor) -> int:

@@ -173,7 +173,7 @@ class SoftmaxTopkMoe(FeedForward):
         gate_logit = None
         if self.w_shared_gu is not None:
             if overlap:
-                torch.cuda.current_stream().wait_event(self._join)
+                main.wait_event(self._join)
             else:
                 shared = self._shared_expert(x, batch, st)
             if self.w_shared_gate is not None:
