@@ -181,6 +181,7 @@ template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, long ldx, const int* __restrict__ rows,
                                    T* __restrict__ out, long ldo, int width, int vec_ok)
 {
+    fx_pdl_wait();
     const int r = blockIdx.x;
     const T* src = x + (long)rows[r] * ldx;
     T* dst = out + (long)r * ldo;
@@ -517,9 +518,9 @@ extern "C" int fx_gather_rows(const void* x, long ldx, const int* rows, void* ou
     const int vec_ok = (width * es) % 16 == 0 && (ldx * es) % 16 == 0 && (ldo * es) % 16 == 0 &&
                        (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0;
     if (dtype == FX_F32)
-        gather_rows_kernel<float><<<n_rows, 128, 0, s>>>((const float*)x, ldx, rows, (float*)out, ldo, width, vec_ok);
+        fx_launch_pdl(gather_rows_kernel<float>, n_rows, 128, 0, s, (const float*)x, ldx, rows, (float*)out, ldo, width, vec_ok);
     else if (dtype == FX_BF16)
-        gather_rows_kernel<bf16><<<n_rows, 128, 0, s>>>((const bf16*)x, ldx, rows, (bf16*)out, ldo, width, vec_ok);
+        fx_launch_pdl(gather_rows_kernel<bf16>, n_rows, 128, 0, s, (const bf16*)x, ldx, rows, (bf16*)out, ldo, width, vec_ok);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

@@ -97,21 +97,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_swap_kernel(const __grid_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (a.N + BF - 1) / BF;
-    int t_tiles = (a.M + TNB - 1) / TNB;
-    if (a.group_offsets) {
-        for (int e = threadIdx.x; e < a.n_groups; e += NTHREADS)
-            cum_s[e + 1] = (a.group_offsets[e + 1] - a.group_offsets[e] + TNB - 1) / TNB;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int run = 0;
-            for (int e = 0; e < a.n_groups; ++e) { const int n = cum_s[e + 1]; cum_s[e] = run; run += n; }
-            cum_s[a.n_groups] = run;
-        }
-        __syncthreads();
-        t_tiles = cum_s[a.n_groups];
-    }
-    const int total = t_tiles * n_tiles;
-    if ((int)blockIdx.x >= total) return;
     const int k_blocks = (a.K + BK - 1) / BK;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -138,6 +123,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_swap_kernel(const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+
+    // Everything above touched nothing that the kernel before this one on the stream writes; the rest does (the
+    // experts' row offsets, the rows themselves).
+    fx_pdl_wait();
+    int t_tiles = (a.M + TNB - 1) / TNB;
+    if (a.group_offsets) {
+        for (int e = threadIdx.x; e < a.n_groups; e += NTHREADS)
+            cum_s[e + 1] = (a.group_offsets[e + 1] - a.group_offsets[e] + TNB - 1) / TNB;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int run = 0;
+            for (int e = 0; e < a.n_groups; ++e) { const int n = cum_s[e + 1]; cum_s[e] = run; run += n; }
+            cum_s[a.n_groups] = run;
+        }
+        __syncthreads();
+        t_tiles = cum_s[a.n_groups];
+    }
+    const int total = t_tiles * n_tiles;   // a CTA beyond the tiles has nothing to do and goes straight to the end
 
     if (warp == 0) {
         // ---------------- producer ----------------
@@ -296,7 +299,7 @@ int launch(const void* X, long ldx, const void* W, long ldw, long w_group_stride
     const long t_tiles = a.group_offsets ? fx_cdiv(a.M, TNB) + a.n_groups : fx_cdiv(a.M, TNB);   // an upper bound when grouped
     const long max_tiles = t_tiles * fx_cdiv(a.N, BF);
     const unsigned grid = (unsigned)(max_tiles < sm_count() ? max_tiles : sm_count());
-    kern<<<grid, NTHREADS, Cfg<TNB, GATED>::SMEM, s>>>(mw, mx, a);
+    fx_launch_pdl(kern, grid, NTHREADS, Cfg<TNB, GATED>::SMEM, s, mw, mx, a);
     return fx_launch_status();
 }
 
