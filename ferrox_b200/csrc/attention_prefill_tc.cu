@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    fx_pdl_wait();   // set up while the kernel before this one drains; its results (q, the pages) from here on
     auto tmem_s = [&](int t) { return tmem_base + 128u * t; };        // S_t, and P_t over its first 64 columns
     auto tmem_o = [&](int t) { return tmem_base + 256u + 128u * t; };
 
@@ -373,7 +374,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    kern<<<grid, NTHREADS, Smem<D>::TOTAL, s>>>(mq, mk, mv, a);
+    fx_launch_pdl(kern, grid, NTHREADS, Smem<D>::TOTAL, s, mq, mk, mv, a);
     return fx_launch_status();
 }
 

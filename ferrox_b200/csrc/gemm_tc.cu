@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (a.N + OUT_N - 1) / OUT_N;
     int m_tiles = (a.M + BM - 1) / BM;
+    if (a.group_offsets) fx_pdl_wait();   // the offsets come from the kernel before this one
     if (a.group_offsets) {
         for (int e = threadIdx.x; e < a.n_groups; e += NTHREADS)     // row tiles of each group, loaded in parallel
             cum_s[e + 1] = (a.group_offsets[e + 1] - a.group_offsets[e] + BM - 1) / BM;
@@ -148,6 +149,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    if (!a.group_offsets) fx_pdl_wait();   // set up while the kernel before this one drains; its results from here on
 
     if (warp == 0) {
         // ---------------- producer ----------------
@@ -356,7 +358,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, long m
         configured = true;
     }
     const unsigned grid = (unsigned)(max_tiles < sm_count() ? max_tiles : sm_count());
-    kern<<<grid, NTHREADS, Cfg<BN>::SMEM, s>>>(ma, mb, a);
+    fx_launch_pdl(kern, grid, NTHREADS, Cfg<BN>::SMEM, s, ma, mb, a);
     return fx_launch_status();
 }
 

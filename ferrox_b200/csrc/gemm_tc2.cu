@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
     cluster_sync();   // the peer's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    fx_pdl_wait();    // set up while the kernel before this one drains; its results from here on
 
     if (warp == 0) {
         // ---------------- producer (both CTAs) ----------------
@@ -332,11 +333,13 @@ extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int
     cfg.blockDim = dim3(NTHREADS);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_fx_pdl_enabled ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, ma, mb, a);
     if (e != cudaSuccess) return (int)e;
     return fx_launch_status();
