@@ -1,0 +1,37 @@
+"""The host-side choices between kernels and launch shapes (pure functions of sizes; no GPU)."""
+from ferrox_b200.kernels import ops
+from ferrox_b200.parts.moe import expert_tile_tokens
+
+
+def test_decode_split_plan_depends_on_sizes_only_and_stays_in_bounds():
+    for tokens in (1, 2, 3, 8, 16, 33, 64, 200):
+        for kv_blocks in (1, 4, 16, 28):
+            for ctx in (64, 500, 4096, 32768):
+                split_len, n = ops.decode_split_plan(tokens, kv_blocks, ctx)
+                assert split_len == 0 and 1 <= n <= ops.DECODE_MAX_SPLITS
+                assert n <= max(1, -(-ctx // 64))          # no run shorter than one tile of keys
+                assert (split_len, n) == ops.decode_split_plan(tokens, kv_blocks, ctx)
+    # one wave of blocks beats a wave and a bit: 8 tokens x 16 kv heads -> 3 runs (384 blocks), not 4 (512 > 444)
+    assert ops.decode_split_plan(8, 16, 4096) == (0, 3)
+    # a single request: many runs, but bounded
+    assert ops.decode_split_plan(1, 16, 4096)[1] == ops.DECODE_MAX_SPLITS
+    # many requests already fill the machine
+    assert ops.decode_split_plan(200, 16, 4096)[1] <= 2
+
+
+def test_which_product_kernel_takes_which_sizes():
+    # few tokens against a big matrix: swapped roles only where measured faster
+    assert not ops.swap_better(8, 6144, 2048) and ops.swap_better(40, 6144, 2048)
+    assert ops.swap_better(8, 151936, 2048) and not ops.swap_better(4, 151936, 2048)
+    assert not ops.swap_better(64, 2048, 5632)              # few rows of W: too few tiles
+    # pairs of SMs need two rounds of 256 x 256 tiles for 74 pairs
+    assert ops.pairs_better(2048, 6144) and not ops.pairs_better(2048, 2048) and not ops.pairs_better(512, 6144)
+    assert ops.pairs_better(2048, 5632, gated=True)
+
+
+def test_expert_tile_tokens_by_rows_per_expert():
+    assert expert_tile_tokens(8, 4, 60) == (32, 32)
+    assert expert_tile_tokens(64, 4, 60) == (32, 32)
+    assert expert_tile_tokens(200, 4, 60) == (64, 64)
+    assert expert_tile_tokens(2048, 4, 60) is None
+    assert expert_tile_tokens(16, 8, 10) == (64, 64)       # few experts: more rows each
