@@ -28,7 +28,7 @@ using namespace fxtc;
 constexpr int BF = 128;          // features per tile = TMEM lanes
 constexpr int BK = 64;           // bfloat16 elements per stage along K = one 128-byte swizzle row
 constexpr int NTHREADS = 192;
-constexpr int MAX_GROUPS = 1024;
+constexpr int MAX_GROUPS = 512;
 
 constexpr int pow2_at_least(int x) { int p = 32; while (p < x) p *= 2; return p; }
 
@@ -37,7 +37,11 @@ template <int TNB, bool GATED> struct Cfg {
     static constexpr int A_BYTES = BF * BK * 2;
     static constexpr int B_BYTES = TNB * BK * 2;
     static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES;
-    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES < 8 ? (200 * 1024) / STAGE_BYTES : 8;
+    // Tiles of up to 32 tokens: two CTAs an SM (their tiles then spread over 296 CTAs instead of 148, and one CTA's
+    // epilogue and tile change hide behind the other's stream); wider tiles: one CTA with the whole ring.
+    static constexpr int CTAS_PER_SM = TNB <= 32 ? 2 : 1;
+    static constexpr int RING_BYTES = CTAS_PER_SM == 2 ? 108 * 1024 : 200 * 1024;
+    static constexpr int STAGES = RING_BYTES / STAGE_BYTES < 8 ? RING_BYTES / STAGE_BYTES : 8;
     static constexpr int ACC_COLS = NA * TNB;                   // one accumulator set
     static constexpr int NBUF = 2 * ACC_COLS <= 512 ? 2 : 1;    // accumulator sets: two when they fit tensor memory
     static constexpr int TMEM_COLS = pow2_at_least(NBUF * ACC_COLS);
@@ -85,7 +89,7 @@ __device__ __forceinline__ int cols_of(const Tile& t) {   // columns of the tile
 }
 
 template <int TNB, bool GATED>
-__global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                    const __grid_constant__ CUtensorMap map_x, SwArgs a)
 {
     using C = Cfg<TNB, GATED>;
@@ -298,7 +302,8 @@ int launch(const void* X, long ldx, const void* W, long ldw, long w_group_stride
     }
     const long t_tiles = a.group_offsets ? fx_cdiv(a.M, TNB) + a.n_groups : fx_cdiv(a.M, TNB);   // an upper bound when grouped
     const long max_tiles = t_tiles * fx_cdiv(a.N, BF);
-    const unsigned grid = (unsigned)(max_tiles < sm_count() ? max_tiles : sm_count());
+    const long slots = (long)sm_count() * Cfg<TNB, GATED>::CTAS_PER_SM;
+    const unsigned grid = (unsigned)(max_tiles < slots ? max_tiles : slots);
     fx_launch_pdl(kern, grid, NTHREADS, Cfg<TNB, GATED>::SMEM, s, mw, mx, a);
     return fx_launch_status();
 }
