@@ -56,6 +56,7 @@ struct SwArgs {
     int gate_up_offset;
     const int* group_offsets;
     int n_groups;
+    int weights_first;
     int* status;
 };
 
@@ -128,9 +129,13 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
-    // Everything above touched nothing that the kernel before this one on the stream writes; the rest does (the
-    // experts' row offsets, the rows themselves).
-    fx_pdl_wait();
+    // Everything above touched nothing that the kernel before this one on the stream writes.  What follows reads the
+    // experts' row offsets and the rows.  weights_first: the caller says that only the rows (X, and the rows of C that
+    // are added to) come from the kernel directly before this one; the offsets are older.  Then the thread that
+    // issues the loads asks for the weights of its first stages before it waits for that kernel: they stream while
+    // it drains.
+    const bool early = a.weights_first != 0;
+    if (!early) fx_pdl_wait();
     int t_tiles = (a.M + TNB - 1) / TNB;
     if (a.group_offsets) {
         for (int e = threadIdx.x; e < a.n_groups; e += NTHREADS)
@@ -145,15 +150,36 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
         t_tiles = cum_s[a.n_groups];
     }
     const int total = t_tiles * n_tiles;   // a CTA beyond the tiles has nothing to do and goes straight to the end
+    if (early && threadIdx.x != 0) fx_pdl_wait();
 
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
             long issued = 0;
             bool ok = true;
+            int pre = 0;   // stages of the first tile whose weights were asked for before the dependency wait
+            if (early) {
+                if ((int)blockIdx.x < total) {
+                    const Tile t = tile_of<TNB>(blockIdx.x, a, t_tiles, n_tiles, cum_s);
+                    pre = k_blocks < STAGES ? k_blocks : STAGES;
+                    for (int kb = 0; kb < pre; ++kb) {   // fresh barriers: every stage is free
+                        const uint32_t sw = base + kb * C::STAGE_BYTES;
+                        mbar_expect_tx(full_bar(kb), C::STAGE_BYTES);
+                        tma_load_3d(sw, &map_w, kb * BK, t.n0, t.group, full_bar(kb));
+                        if (GATED) tma_load_3d(sw + C::A_BYTES, &map_w, kb * BK, a.gate_up_offset + t.n0, t.group, full_bar(kb));
+                    }
+                }
+                fx_pdl_wait();
+                if ((int)blockIdx.x < total) {
+                    const Tile t = tile_of<TNB>(blockIdx.x, a, t_tiles, n_tiles, cum_s);
+                    for (int kb = 0; kb < pre; ++kb)
+                        tma_load_2d(base + kb * C::STAGE_BYTES + C::NA * C::A_BYTES, &map_x, kb * BK, t.r0, full_bar(kb));
+                }
+                issued = pre;
+            }
             for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
                 const Tile t = tile_of<TNB>(id, a, t_tiles, n_tiles, cum_s);
-                for (int kb = 0; kb < k_blocks; ++kb, ++issued) {
+                for (int kb = (id == (int)blockIdx.x ? pre : 0); kb < k_blocks; ++kb, ++issued) {
                     const int s = (int)(issued % STAGES);
                     const uint32_t parity = (uint32_t)((issued / STAGES) & 1) ^ 1u;
                     if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
@@ -318,13 +344,14 @@ int run_tnb(const void* X, long ldx, const void* W, long ldw, long w_group_strid
 
 }  // namespace
 
-// Same operands as fx_gemm_tc.  tokens_per_tile: 32, 64, 128 or 256 columns of a tile (0: chosen from M; grouped: 128).
+// Same operands as fx_gemm_tc.  weights_first: group_offsets (if any) were NOT written by the kernel directly before
+// this one on the stream, so that the weights may be fetched before that kernel has finished.  tokens_per_tile: 32, 64, 128 or 256 columns of a tile (0: chosen from M; grouped: 128).
 // With 256 columns the gated form has room for one set of accumulators only: its epilogue and the next tile's
 // products do not overlap.
 extern "C" int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows,
                                const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate,
                                int M, int N, int K, int gated, int gate_up_offset, const int* group_offsets, int n_groups,
-                               int tokens_per_tile, int* status, void* stream)
+                               int tokens_per_tile, int weights_first, int* status, void* stream)
 {
     if (M <= 0 || N <= 0) return FX_OK;
     if (K <= 0 || K % 8) return FX_ERR_SIZE;
@@ -335,7 +362,7 @@ extern "C" int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw,
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset;
-    a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status;
+    a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status; a.weights_first = weights_first;
     cudaStream_t s = (cudaStream_t)stream;
     int tnb = tokens_per_tile;
     if (tnb == 0) tnb = group_offsets ? 128 : (M <= 32 ? 32 : M <= 64 ? 64 : 128);

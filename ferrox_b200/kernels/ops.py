@@ -40,7 +40,7 @@ _SIGNATURES = {
     "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_rope_table": [_P, _P, _I, _I, _P, _P],
     "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
-    "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P],
+    "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _P, _P],
     "fx_gemm_tc2": [_P, _L, _P, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
     "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
@@ -376,10 +376,13 @@ def gemm_tc(x, w, out, *, bias=None, accumulate=False, gated=False, group_offset
 
 
 def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_offsets=None, tokens_per_tile=0,
-                 status=None, stream=None):
+                 weights_first=None, status=None, stream=None):
     """The same product as :func:`gemm_tc` with the roles swapped: 128 features of ``w`` fill the lanes of a tile,
     the tokens its columns (multiples of 16 up to ``tokens_per_tile``: 32, 64 or 128; 0 = chosen from the sizes).
-    For few tokens per weight matrix: decode batches beyond the weight-streaming kernel's, experts of a prompt."""
+    For few tokens per weight matrix: decode batches beyond the weight-streaming kernel's, experts of a prompt.
+    ``weights_first``: the kernel may fetch its first weights before the kernel launched just before it has finished;
+    true by default for dense products, and for grouped ones only if the caller says that ``group_offsets`` is older
+    than that kernel."""
     M, N = out.shape
     K = x.shape[1]
     if group_offsets is not None:
@@ -390,7 +393,9 @@ def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_o
         raise KernelError(f"gemm_tc_swap shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_tc_swap", _ptr(x), _rows(x), _ptr(w), ldw, wstride, wrows, _ptr(bias), code(bias) if bias is not None else 0,
          _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0,
-         _ptr(group_offsets), G, int(tokens_per_tile), _ptr(status), stream if stream is not None else stream_ptr())
+         _ptr(group_offsets), G, int(tokens_per_tile),
+         int(group_offsets is None if weights_first is None else weights_first), _ptr(status),
+         stream if stream is not None else stream_ptr())
     return out
 
 

@@ -149,10 +149,11 @@ class SoftmaxTopkMoe(FeedForward):
             # and the expert's rows in their columns
             xp = rt.empty(T * K, H)
             ops.gather_rows(x, src_token, xp, stream=st)
+            # (the offsets were written by the routing, before the gather: both products may fetch weights early)
             ops.gemm_tc_swap(xp, self.w_gu, act, gated=True, group_offsets=offsets, tokens_per_tile=tiles[0],
-                             status=batch.status, stream=st)
+                             weights_first=True, status=batch.status, stream=st)
             ops.gemm_tc_swap(act, self.w_down, y, group_offsets=offsets, tokens_per_tile=tiles[1],
-                             status=batch.status, stream=st)
+                             weights_first=True, status=batch.status, stream=st)
         elif small:
             # very few tokens: every expert that was chosen is streamed once, gate/up fused with SiLU
             ops.gemm_skinny(x, self.w_gu, act, gated=True, x_rows=src_token, group_offsets=offsets,
