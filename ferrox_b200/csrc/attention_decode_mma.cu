@@ -16,6 +16,10 @@
 // in warp order at the end.  Scores, softmax and sums are 32-bit; P is rounded to
 // bfloat16 for the second product, as in the prompt kernel.
 //
+// Launched as a dependent of the kernel that wrote the step's queries and newest keys, a block fetches its
+// first tile of older keys before it waits for that kernel; the caller must not have more than 64 new positions
+// of a request written by the kernel directly before this one (the engine sends at most 8 this way).
+//
 // Reference: crates/ferrox-core/src/attention.rs:146-175 (online softmax), :484-524
 // (window), :572-610 (pages).
 #include "common.cuh"
@@ -24,6 +28,7 @@
 namespace {
 
 constexpr int NTHREADS = 128, TK = 64, STAGES = 2, MAXQ = 16;
+constexpr int NEWEST_POSITIONS = 64;   // a launch may follow the write of at most this many new positions of a request
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -55,7 +60,6 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     float* __restrict__ part_acc, float* __restrict__ part_ml,
     int n_heads, int n_kv_heads, int head_dim, int window, float scale_log2e, float scale, int split_len, int n_splits)
 {
-    fx_pdl_wait();
     const int group_size = n_heads / n_kv_heads;
     const int chunks = (group_size + MAXQ - 1) / MAXQ;
     const int kvh = blockIdx.x / chunks;
@@ -83,11 +87,13 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     const int n_tiles = (k_end - k_begin + TK - 1) / TK;
 
     // query rows of this block (zero beyond the group)
-    for (int c = threadIdx.x; c < 16 * chunks_row; c += NTHREADS) {
-        const int r = c / chunks_row, ch = c - r * chunks_row;
-        const bf16* src = q + (long)tkn * ldq + (long)(h0 + min(r, nq - 1)) * head_dim + ch * 8;
-        cp_async16(q_u + r * pitch + ch * 16, src, r < nq ? 16 : 0);
-    }
+    auto load_q = [&]() {
+        for (int c = threadIdx.x; c < 16 * chunks_row; c += NTHREADS) {
+            const int r = c / chunks_row, ch = c - r * chunks_row;
+            const bf16* src = q + (long)tkn * ldq + (long)(h0 + min(r, nq - 1)) * head_dim + ch * 8;
+            cp_async16(q_u + r * pitch + ch * 16, src, r < nq ? 16 : 0);
+        }
+    };
     const bool lanes_fit = chunks_row <= NTHREADS && NTHREADS % chunks_row == 0;
     const int my_ch = lanes_fit ? threadIdx.x % chunks_row : 0;
     const int my_r0 = lanes_fit ? threadIdx.x / chunks_row : 0;
@@ -121,9 +127,18 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             if (ch == 0) fl[r] = ok ? 1 : 0;
         }
     };
+    // The kernel before this one on the stream wrote the queries and the keys and values of the step's own positions
+    // (at most NEWEST_POSITIONS of a request, its last ones); everything read so far, and every older key, is older.
+    // A block whose first tile ends before those positions asks for it before it waits for that kernel.
+    const bool early = k_begin + TK <= pos + 1 - NEWEST_POSITIONS;
+    if (early) load_tile(0, 0);
+    fx_pdl_wait();
+    load_q();
+    if (!early) load_tile(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
     // the ring: STAGES - 1 tiles are in flight beside the one being worked on
 #pragma unroll
-    for (int i = 0; i < STAGES - 1; ++i) {
+    for (int i = 1; i < STAGES - 1; ++i) {
         if (i < n_tiles) load_tile(i, i);
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
