@@ -53,7 +53,7 @@ int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long w_group_st
 int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, const void* bias,
                     int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
                     int gate_up_offset, const int* group_offsets, int n_groups, int tokens_per_tile, int weights_first,
-                    int* status, void* stream);
+                    int k_splits, float* partials, int* status, void* stream);
 int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int w_rows, const void* bias, int bias_dtype, void* C,
                 int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated, int gate_up_offset, int* status,
                 void* stream);

@@ -57,16 +57,28 @@ struct SwArgs {
     const int* group_offsets;
     int n_groups;
     int weights_first;
+    int k_splits;          // > 1 (dense only): K is cut into this many runs, each tile and run writes 32-bit partial sums
+    float* partials;       // [k_splits, M, N], summed by splitk_reduce_kernel
     int* status;
 };
 
-struct Tile { int group, r0, row_end, n0; };
+struct Tile { int group, r0, row_end, n0, split, kb0, kb1; };
 
 template <int TNB>
 __device__ __forceinline__ Tile tile_of(int id, const SwArgs& a, int t_tiles, int n_tiles, const int* cum) {
     Tile t;
+    const int k_blocks = (a.K + BK - 1) / BK;
+    t.split = 0; t.kb0 = 0; t.kb1 = k_blocks;
     if (!a.group_offsets) {
-        // token tiles of one feature tile are neighbours: CTAs working at the same time share a slice of W
+        // the runs of K of one tile are neighbours, then the token tiles of one feature tile: CTAs working at the same
+        // time share a slice of W
+        if (a.k_splits > 1) {
+            const int per = (k_blocks + a.k_splits - 1) / a.k_splits;
+            t.split = id % a.k_splits;
+            id /= a.k_splits;
+            t.kb0 = t.split * per;
+            t.kb1 = t.kb0 + per < k_blocks ? t.kb0 + per : k_blocks;
+        }
         t.group = 0;
         t.n0 = (id / t_tiles) * BF;
         t.r0 = (id % t_tiles) * TNB;
@@ -102,7 +114,6 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (a.N + BF - 1) / BF;
-    const int k_blocks = (a.K + BK - 1) / BK;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = base + STAGES * C::STAGE_BYTES;
@@ -149,7 +160,8 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
         __syncthreads();
         t_tiles = cum_s[a.n_groups];
     }
-    const int total = t_tiles * n_tiles;   // a CTA beyond the tiles has nothing to do and goes straight to the end
+    // a CTA beyond the tiles has nothing to do and goes straight to the end
+    const int total = t_tiles * n_tiles * (a.group_offsets || a.k_splits < 1 ? 1 : a.k_splits);
     if (early && threadIdx.x != 0) fx_pdl_wait();
 
     if (warp == 0) {
@@ -161,25 +173,26 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
             if (early) {
                 if ((int)blockIdx.x < total) {
                     const Tile t = tile_of<TNB>(blockIdx.x, a, t_tiles, n_tiles, cum_s);
-                    pre = k_blocks < STAGES ? k_blocks : STAGES;
-                    for (int kb = 0; kb < pre; ++kb) {   // fresh barriers: every stage is free
-                        const uint32_t sw = base + kb * C::STAGE_BYTES;
-                        mbar_expect_tx(full_bar(kb), C::STAGE_BYTES);
-                        tma_load_3d(sw, &map_w, kb * BK, t.n0, t.group, full_bar(kb));
-                        if (GATED) tma_load_3d(sw + C::A_BYTES, &map_w, kb * BK, a.gate_up_offset + t.n0, t.group, full_bar(kb));
+                    pre = t.kb1 - t.kb0 < STAGES ? t.kb1 - t.kb0 : STAGES;
+                    for (int i = 0; i < pre; ++i) {   // fresh barriers: every stage is free
+                        const int kb = t.kb0 + i;
+                        const uint32_t sw = base + i * C::STAGE_BYTES;
+                        mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
+                        tma_load_3d(sw, &map_w, kb * BK, t.n0, t.group, full_bar(i));
+                        if (GATED) tma_load_3d(sw + C::A_BYTES, &map_w, kb * BK, a.gate_up_offset + t.n0, t.group, full_bar(i));
                     }
                 }
                 fx_pdl_wait();
                 if ((int)blockIdx.x < total) {
                     const Tile t = tile_of<TNB>(blockIdx.x, a, t_tiles, n_tiles, cum_s);
-                    for (int kb = 0; kb < pre; ++kb)
-                        tma_load_2d(base + kb * C::STAGE_BYTES + C::NA * C::A_BYTES, &map_x, kb * BK, t.r0, full_bar(kb));
+                    for (int i = 0; i < pre; ++i)
+                        tma_load_2d(base + i * C::STAGE_BYTES + C::NA * C::A_BYTES, &map_x, (t.kb0 + i) * BK, t.r0, full_bar(i));
                 }
                 issued = pre;
             }
             for (int id = blockIdx.x; id < total && ok; id += gridDim.x) {
                 const Tile t = tile_of<TNB>(id, a, t_tiles, n_tiles, cum_s);
-                for (int kb = (id == (int)blockIdx.x ? pre : 0); kb < k_blocks; ++kb, ++issued) {
+                for (int kb = t.kb0 + (id == (int)blockIdx.x ? pre : 0); kb < t.kb1; ++kb, ++issued) {
                     const int s = (int)(issued % STAGES);
                     const uint32_t parity = (uint32_t)((issued / STAGES) & 1) ^ 1u;
                     if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
@@ -212,7 +225,7 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + (uint32_t)(buf * C::ACC_COLS);
-                for (int kb = 0; kb < k_blocks; ++kb, ++used) {
+                for (int kb = t.kb0; kb < t.kb1; ++kb, ++used) {
                     const int s = (int)(used % STAGES);
                     ok = mbar_wait(full_bar(s), (uint32_t)((used / STAGES) & 1), abort_flag);
                     if (!ok) break;
@@ -221,8 +234,8 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
                     const uint64_t dw = smem_desc(sw), du = smem_desc(sw + C::A_BYTES), dx = smem_desc(sx);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
-                        tc_mma(acc, dw + 2u * k, dx + 2u * k, idesc, (kb | k) != 0);
-                        if (GATED) tc_mma(acc + TNB, du + 2u * k, dx + 2u * k, idesc, (kb | k) != 0);
+                        tc_mma(acc, dw + 2u * k, dx + 2u * k, idesc, kb > t.kb0 || k > 0);
+                        if (GATED) tc_mma(acc + TNB, du + 2u * k, dx + 2u * k, idesc, kb > t.kb0 || k > 0);
                     }
                     tc_commit(empty_bar(s));
                 }
@@ -238,7 +251,7 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
             const int buf = it % C::NBUF;
             const int f = t.n0 + quad * 32 + lane;
             const bool f_ok = f < a.N;
-            const float bias = (a.bias && f_ok) ? load_any(a.bias, a.bias_dtype, f) : 0.f;
+            const float bias = (a.bias && f_ok && a.k_splits <= 1) ? load_any(a.bias, a.bias_dtype, f) : 0.f;
             const int n_chunks = (cols_of<TNB>(t) + 31) / 32;
             const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (uint32_t)((it / C::NBUF) & 1), abort_flag));
             if (!ok) break;
@@ -257,15 +270,26 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
                 }
                 if (!f_ok) continue;
                 const int row0 = t.r0 + c * 32;
+                const bool add32 = a.accumulate && a.c_dtype == FX_F32 && a.k_splits <= 1;
+                float old[32];
+                if (add32) {   // what is added to, fetched together: one round trip for the chunk, not one per token
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        old[j] = row0 + j < t.row_end ? reinterpret_cast<const float*>(a.C)[(long)(row0 + j) * a.ldc + f] : 0.f;
+                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     if (row0 + j >= t.row_end) break;
                     float x = __uint_as_float(r[j]) + bias;
                     if (GATED) x = x / (1.0f + __expf(-x)) * __uint_as_float(u[j]);
+                    if (a.k_splits > 1) {   // a run of K: the plain partial sum
+                        a.partials[((long)t.split * a.M + row0 + j) * a.N + f] = __uint_as_float(r[j]);
+                        continue;
+                    }
                     const long at = (long)(row0 + j) * a.ldc + f;
                     if (a.c_dtype == FX_F32) {
                         float* cp = reinterpret_cast<float*>(a.C) + at;
-                        *cp = a.accumulate ? *cp + x : x;
+                        *cp = add32 ? old[j] + x : x;
                     } else {
                         bf16* cp = reinterpret_cast<bf16*>(a.C) + at;
                         *cp = __float2bfloat16_rn(a.accumulate ? __bfloat162float(*cp) + x : x);
@@ -282,6 +306,27 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && abort_flag_s && a.status) atomicExch(a.status, STATUS_TC_TIMEOUT);
+}
+
+// C[r, n] (+)= sum over the runs of K, in run order (+ bias[n])
+__global__ void splitk_reduce_kernel(const float* __restrict__ partials, int k_splits, int M, int N, void* C, long ldc,
+                                     int c_dtype, int accumulate, const void* bias, int bias_dtype)
+{
+    fx_pdl_wait();
+    const long total = (long)M * N;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / N; const int n = (int)(i - r * N);
+        float v = 0.f;
+        for (int s2 = 0; s2 < k_splits; ++s2) v += partials[(long)s2 * total + i];
+        if (bias) v += load_any(bias, bias_dtype, n);
+        if (c_dtype == FX_F32) {
+            float* cp = reinterpret_cast<float*>(C) + r * ldc + n;
+            *cp = accumulate ? *cp + v : v;
+        } else {
+            bf16* cp = reinterpret_cast<bf16*>(C) + r * ldc + n;
+            *cp = __float2bfloat16_rn(accumulate ? __bfloat162float(*cp) + v : v);
+        }
+    }
 }
 
 // bf16 tensor [d2][d1][K] (row pitch ld1 elements, matrix pitch ld2 elements), box {64, box1, 1}
@@ -327,10 +372,16 @@ int launch(const void* X, long ldx, const void* W, long ldw, long w_group_stride
         configured = true;
     }
     const long t_tiles = a.group_offsets ? fx_cdiv(a.M, TNB) + a.n_groups : fx_cdiv(a.M, TNB);   // an upper bound when grouped
-    const long max_tiles = t_tiles * fx_cdiv(a.N, BF);
+    const long max_tiles = t_tiles * fx_cdiv(a.N, BF) * (a.k_splits > 1 ? a.k_splits : 1);
     const long slots = (long)sm_count() * Cfg<TNB, GATED>::CTAS_PER_SM;
     const unsigned grid = (unsigned)(max_tiles < slots ? max_tiles : slots);
     fx_launch_pdl(kern, grid, NTHREADS, Cfg<TNB, GATED>::SMEM, s, mw, mx, a);
+    if (a.k_splits > 1) {
+        long blocks = fx_cdiv((long)a.M * a.N, 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        fx_launch_pdl(splitk_reduce_kernel, (unsigned)blocks, 256, 0, s, (const float*)a.partials, a.k_splits, a.M, a.N, a.C,
+                      a.ldc, a.c_dtype, a.accumulate, a.bias, a.bias_dtype);
+    }
     return fx_launch_status();
 }
 
@@ -344,6 +395,9 @@ int run_tnb(const void* X, long ldx, const void* W, long ldw, long w_group_strid
 
 }  // namespace
 
+// k_splits > 1 (plain dense products only): K is cut into runs that separate CTAs take, partial sums [k_splits, M, N]
+// (float32, caller's scratch) are added up in run order by a second kernel: for matrices with too few rows to fill the
+// machine with tiles.
 // Same operands as fx_gemm_tc.  weights_first: group_offsets (if any) were NOT written by the kernel directly before
 // this one on the stream, so that the weights may be fetched before that kernel has finished.  tokens_per_tile: 32, 64, 128 or 256 columns of a tile (0: chosen from M; grouped: 128).
 // With 256 columns the gated form has room for one set of accumulators only: its epilogue and the next tile's
@@ -351,7 +405,8 @@ int run_tnb(const void* X, long ldx, const void* W, long ldw, long w_group_strid
 extern "C" int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows,
                                const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate,
                                int M, int N, int K, int gated, int gate_up_offset, const int* group_offsets, int n_groups,
-                               int tokens_per_tile, int weights_first, int* status, void* stream)
+                               int tokens_per_tile, int weights_first, int k_splits, float* partials, int* status,
+                               void* stream)
 {
     if (M <= 0 || N <= 0) return FX_OK;
     if (K <= 0 || K % 8) return FX_ERR_SIZE;
@@ -363,6 +418,8 @@ extern "C" int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw,
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset;
     a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status; a.weights_first = weights_first;
+    a.k_splits = k_splits > 1 ? k_splits : 1; a.partials = partials;
+    if (a.k_splits > 1 && (group_offsets || gated || !partials || a.k_splits > (K + BK - 1) / BK)) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     int tnb = tokens_per_tile;
     if (tnb == 0) tnb = group_offsets ? 128 : (M <= 32 ? 32 : M <= 64 ? 64 : 128);

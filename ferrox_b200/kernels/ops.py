@@ -40,7 +40,7 @@ _SIGNATURES = {
     "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_rope_table": [_P, _P, _I, _I, _P, _P],
     "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
-    "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _P, _P],
+    "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _P, _P, _P],
     "fx_gemm_tc2": [_P, _L, _P, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
     "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
@@ -62,7 +62,7 @@ _SIGNATURES = {
 _fn = {}
 
 # kernels launched by one call of an entry point (fx_moe_align: count, scan, place)
-_KERNELS = {"fx_moe_align": 3, "fx_decode_attention": 2}
+_KERNELS = {"fx_moe_align": 3, "fx_decode_attention": 2}   # (a split-K product adds a second kernel; not counted)
 _launches = 0
 
 
@@ -376,13 +376,14 @@ def gemm_tc(x, w, out, *, bias=None, accumulate=False, gated=False, group_offset
 
 
 def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_offsets=None, tokens_per_tile=0,
-                 weights_first=None, status=None, stream=None):
+                 weights_first=None, k_splits=1, status=None, stream=None):
     """The same product as :func:`gemm_tc` with the roles swapped: 128 features of ``w`` fill the lanes of a tile,
     the tokens its columns (multiples of 16 up to ``tokens_per_tile``: 32, 64 or 128; 0 = chosen from the sizes).
     For few tokens per weight matrix: decode batches beyond the weight-streaming kernel's, experts of a prompt.
     ``weights_first``: the kernel may fetch its first weights before the kernel launched just before it has finished;
     true by default for dense products, and for grouped ones only if the caller says that ``group_offsets`` is older
-    than that kernel."""
+    than that kernel.  ``k_splits`` > 1 (plain dense products): K is cut into runs taken by separate CTAs and a second
+    kernel adds the partial sums in run order, for matrices of too few rows to fill the machine with tiles."""
     M, N = out.shape
     K = x.shape[1]
     if group_offsets is not None:
@@ -394,8 +395,9 @@ def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_o
     call("fx_gemm_tc_swap", _ptr(x), _rows(x), _ptr(w), ldw, wstride, wrows, _ptr(bias), code(bias) if bias is not None else 0,
          _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0,
          _ptr(group_offsets), G, int(tokens_per_tile),
-         int(group_offsets is None if weights_first is None else weights_first), _ptr(status),
-         stream if stream is not None else stream_ptr())
+         int(group_offsets is None if weights_first is None else weights_first), int(k_splits),
+         _ptr(torch.empty(k_splits, M, N, dtype=torch.float32, device=out.device)) if k_splits > 1 else None,
+         _ptr(status), stream if stream is not None else stream_ptr())
     return out
 
 
@@ -434,6 +436,17 @@ def pairs_better(M: int, N: int, gated: bool = False) -> bool:
     return M >= 1024 and tiles >= 148
 
 
+def swap_k_splits(T: int, N: int, K: int) -> int:
+    """Runs of K for the swapped-role kernel on a plain dense product of few tokens, or 0 where the weight-streaming
+    kernel is as good.  A matrix of N rows gives N / 128 tiles; with fewer than the machine has SMs, K is cut so that
+    some 150 to 300 CTAs stream it.  Measured on a B200 (decode batches of 32 and 64): ahead from 33 tokens on, and from
+    17 tokens for matrices of 8M elements and more."""
+    if T > 32 or (T > 16 and N * K >= (1 << 23)):
+        tiles = -(-N // 128) * -(-T // (32 if T <= 32 else 64))
+        return max(1, min(8, K // 256, round(192 / tiles)))
+    return 0
+
+
 def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None):
     """out (+)= x . w^T (+ bias): picks the kernel by size and element type."""
     T = x.shape[0]
@@ -441,8 +454,13 @@ def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None):
         # many tokens, a narrow output (router logits): the weight-streaming kernel with the roles swapped,
         # x streamed once as the "matrix", w as the few "tokens", stored transposed
         return gemm_skinny(w, x, out, accumulate=accumulate, transposed_out=True, stream=stream)
-    if T <= SKINNY_MAX_TOKENS and tc_ok(x, w) and swap_better(T, w.shape[0], w.shape[1]):
-        return gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
+    if T <= SKINNY_MAX_TOKENS and w.dim() == 2 and tc_ok(x, w):
+        N, K = w.shape
+        if T >= 8 and N * K >= (1 << 27):   # the vocabulary head: tiles enough without cutting K
+            return gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
+        ks = swap_k_splits(T, N, K)
+        if ks:
+            return gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, k_splits=ks, status=status, stream=stream)
     if T <= SKINNY_MAX_TOKENS and skinny_ok(x, w):
         return gemm_skinny(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
     if T > SKINNY_MAX_TOKENS and tc_ok(x, w):

@@ -24,6 +24,11 @@ def test_which_product_kernel_takes_which_sizes():
     assert not ops.swap_better(8, 6144, 2048) and ops.swap_better(40, 6144, 2048)
     assert ops.swap_better(8, 151936, 2048) and not ops.swap_better(4, 151936, 2048)
     assert not ops.swap_better(64, 2048, 5632)              # few rows of W: too few tiles
+    # plain dense products of few tokens: runs of K so that 150 to 300 CTAs stream the matrix
+    assert ops.swap_k_splits(64, 2048, 2048) == 8 and ops.swap_k_splits(64, 2048, 5632) == 8
+    assert ops.swap_k_splits(64, 6144, 2048) == 4 and ops.swap_k_splits(8, 2048, 2048) == 0
+    assert ops.swap_k_splits(32, 2048, 5632) > 0 and ops.swap_k_splits(32, 2048, 2048) == 0
+    assert ops.swap_k_splits(64, 2048, 256) == 1      # never more runs than K allows
     # pairs of SMs need two rounds of 256 x 256 tiles for 74 pairs
     assert ops.pairs_better(2048, 6144) and not ops.pairs_better(2048, 2048) and not ops.pairs_better(512, 6144)
     assert ops.pairs_better(2048, 5632, gated=True)

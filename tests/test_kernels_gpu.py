@@ -545,6 +545,34 @@ def test_gemm_tc_swap(M, N, K, tnb):
     assert rel(wide[:, :N], want) < 2e-5 and float(wide[:, N:].min()) == 7.0
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(64, 2048, 5632, 8), (40, 300, 136, 3), (17, 128, 64, 1), (5, 61, 2048, 4)])
+def test_gemm_tc_swap_runs_of_k(M, N, K, splits):
+    """K cut into runs taken by separate CTAs, partial sums added in run order: bias, accumulation, a strided view;
+    the same bits every time."""
+    o = ops()
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.2)
+    bias = rnd(N, seed=5)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    want = x.float() @ w.float().T
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc_swap(x, w, out, bias=bias, k_splits=splits, status=status)
+    assert int(status) == 0 and rel(out, want + bias) < TOL["bfloat16"]
+    acc = rnd(M, N, seed=3)
+    base = acc.clone()
+    o.gemm_tc_swap(x, w, acc, accumulate=True, k_splits=splits, status=status)
+    assert int(status) == 0 and rel(acc, base + want) < 2e-5
+    wide = torch.full((M, N + 5), 7.0, device=DEV)
+    o.gemm_tc_swap(x, w, wide[:, :N], k_splits=splits, status=status)
+    first = wide.clone()
+    assert rel(wide[:, :N], want) < 2e-5 and float(wide[:, N:].min()) == 7.0
+    for _ in range(3):
+        o.gemm_tc_swap(x, w, wide[:, :N], k_splits=splits, status=status)
+        assert torch.equal(wide, first)
+    if splits > 1:
+        with pytest.raises(o.KernelError):   # more runs than there are k-blocks
+            o.gemm_tc_swap(x, w, out, k_splits=K // 64 + 2, status=status)
+
+
 @pytest.mark.parametrize("M,I,K", [(48, 100, 96), (64, 5632, 2048), (33, 1408, 256), (200, 300, 136)])
 def test_gemm_tc_swap_gated(M, I, K):
     o = ops()
