@@ -270,13 +270,6 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
                 }
                 if (!f_ok) continue;
                 const int row0 = t.r0 + c * 32;
-                const bool add32 = a.accumulate && a.c_dtype == FX_F32 && a.k_splits <= 1;
-                float old[32];
-                if (add32) {   // what is added to, fetched together: one round trip for the chunk, not one per token
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        old[j] = row0 + j < t.row_end ? reinterpret_cast<const float*>(a.C)[(long)(row0 + j) * a.ldc + f] : 0.f;
-                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     if (row0 + j >= t.row_end) break;
@@ -289,7 +282,7 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
                     const long at = (long)(row0 + j) * a.ldc + f;
                     if (a.c_dtype == FX_F32) {
                         float* cp = reinterpret_cast<float*>(a.C) + at;
-                        *cp = add32 ? old[j] + x : x;
+                        *cp = a.accumulate ? *cp + x : x;
                     } else {
                         bf16* cp = reinterpret_cast<bf16*>(a.C) + at;
                         *cp = __float2bfloat16_rn(a.accumulate ? __bfloat162float(*cp) + x : x);
