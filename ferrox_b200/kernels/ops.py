@@ -351,6 +351,10 @@ def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, tok
     return out
 
 
+TC_MAX_GROUPS = 1024        # experts the grouped tcgen05 kernel keeps its tile table for (gemm_tc.cu)
+TC_SWAP_MAX_GROUPS = 512    # and the swapped-role kernel (gemm_tc_swap.cu)
+
+
 def tc_ok(x, w) -> bool:
     """Whether the tcgen05 kernel takes these operands (bfloat16, 16-byte aligned rows)."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0

@@ -111,8 +111,8 @@ class SoftmaxTopkMoe(FeedForward):
         s, rt, st = self.spec, self.rt, batch.stream
         T, E, K, I, H = x.shape[0], s.n_experts, s.top_k, s.expert_intermediate, s.hidden
         i32 = torch.int32
-        tc = ops.tc_ok(x, self.w_gu) and I % 8 == 0
-        tiles = expert_tile_tokens(T, K, E) if tc and T >= SWAP_MIN_TOKENS else None
+        tc = ops.tc_ok(x, self.w_gu) and I % 8 == 0 and E <= ops.TC_MAX_GROUPS
+        tiles = expert_tile_tokens(T, K, E) if tc and T >= SWAP_MIN_TOKENS and E <= ops.TC_SWAP_MAX_GROUPS else None
         small = tiles is None and T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
         big = T > ops.SKINNY_MAX_TOKENS and tc
         n_route = self.w_route.shape[0]      # E router logits, then the shared expert's gate logit if it has one
