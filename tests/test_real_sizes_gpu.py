@@ -66,3 +66,47 @@ def test_real_layer_sizes_under_three_cuts(model, dtype, tol):
     check(ru.run_tail_decode(eng, prompts, tail=24), want, tol, dtype == "bfloat16")
     check(ru.run_mixed(eng, prompts, seed=2, max_live=2, max_portion=40), want, tol, dtype == "bfloat16")
     assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())
+
+
+def test_long_prompt_cut_three_ways_agrees_with_itself():
+    """6,000 tokens at the real layer sizes, too long for the plain implementation: the logits at the last positions
+    must not depend on whether the prompt came whole (pairs of SMs, 256-query attention tiles, 128-row expert tiles),
+    in portions, or with its last tokens decoded one by one (split-key attention over 47 blocks of keys, few rows an
+    expert).  The keys far back must count: the comparison would fail if a block of keys were dropped."""
+    from ferrox_b200 import Engine, StepEntry, write_random_model
+    import tempfile
+
+    cfg = dict(A27B_LAYER, max_position_embeddings=8192, vocab_size=1000)
+    with tempfile.TemporaryDirectory() as tmp:
+        folder = write_random_model(tmp + "/m", cfg, seed=7, std=0.02, norm_init="around_one")
+        eng = Engine.from_folder(folder, dtype="bfloat16", page_size=64, n_pages=96, max_slots=2)
+    rng = random.Random(3)
+    toks = [rng.randrange(cfg["vocab_size"]) for _ in range(6000)]
+    tail = 6
+
+    def last_logits(cuts):
+        slot = eng.open_request()
+        outs, at = [], 0
+        for n in cuts:
+            want = [i - at for i in range(max(at, len(toks) - tail), at + n)]
+            lg = eng.step([StepEntry(slot, toks[at:at + n], want=want)])
+            if want:
+                outs.append(lg.float().cpu())
+            at += n
+        eng.close_request(slot)
+        assert at == len(toks)
+        return torch.cat(outs)
+
+    whole = last_logits([6000])
+    portions = last_logits([2048, 1000, 2500, 452])
+    decoded = last_logits([6000 - tail] + [1] * tail)
+    assert whole.shape == portions.shape == decoded.shape == (tail, cfg["vocab_size"])
+    scale = float(whole.abs().max())
+    assert float((whole - portions).abs().max()) / scale < 3e-2
+    assert float((whole - decoded).abs().max()) / scale < 3e-2
+    # and the far keys matter: the same tail after a different first half gives other logits
+    other = [rng.randrange(cfg["vocab_size"]) for _ in range(3000)] + toks[3000:]
+    slot = eng.open_request()
+    lg = eng.step([StepEntry(slot, other, want=list(range(6000 - tail, 6000)))]).float().cpu()
+    eng.close_request(slot)
+    assert float((whole - lg).abs().max()) / scale > 1e-2
