@@ -310,19 +310,26 @@ int launch_split(int gq, A... args)
 }
 
 template <typename T>
-int run(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table, int table_width,
-        int page_size, const int* positions, const int* token_seq, const int* seq_slot, void* out, long ldo,
-        float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
-        float scale, int split_len, int n_splits, cudaStream_t s)
+int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages, const int* block_table,
+        int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot, void* out,
+        long ldo, float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
+        float scale, int split_len, int n_splits, int* status, cudaStream_t s)
 {
     constexpr int N = Vec<T>::N;
     if (head_dim % N || head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
     if (ldq % N || (uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16) return FX_ERR_ALIGN;
     if (sizeof(T) == 2) {
-        // bfloat16: the tensor-core kernel writes the same partial results; the merge below is shared
-        const int rc_mma = fx_decode_split_mma(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions,
-                                               token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads, n_kv_heads,
-                                               head_dim, window, scale, split_len, n_splits, (void*)s);
+        // bfloat16: the tensor-core kernels write the same partial results; the merge below is shared.  The one
+        // that streams whole pages by TMA first (head sizes in steps of 64, pages of a multiple of 64 positions).
+        int rc_mma = FX_ERR_SIZE;
+        if (n_pages > 0)
+            rc_mma = fx_decode_split_tma(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size,
+                                         positions, token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads,
+                                         n_kv_heads, head_dim, window, scale, split_len, n_splits, status, (void*)s);
+        if (rc_mma < 0)
+            rc_mma = fx_decode_split_mma(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions,
+                                         token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads, n_kv_heads,
+                                         head_dim, window, scale, split_len, n_splits, (void*)s);
         if (rc_mma == FX_OK) {
             fx_launch_pdl(merge_kernel<T>, dim3(n_tokens, n_heads), 64, 0, s, part_acc, part_ml, positions, (T*)out, ldo,
                           n_heads, head_dim, n_splits, split_len, window);
@@ -358,23 +365,24 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, const
 }  // namespace
 
 // Scratch: part_acc [n_tokens, n_heads, n_splits, head_dim] and part_ml [n_tokens, n_heads, n_splits, 2], float32.
-extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
-                                   const int* block_table, int table_width, int page_size, const int* positions,
-                                   const int* token_seq, const int* seq_slot, void* out, long ldo, float* part_acc,
-                                   float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
-                                   float scale, int split_len, int n_splits, void* stream)
+extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages,
+                                   int dtype, const int* block_table, int table_width, int page_size,
+                                   const int* positions, const int* token_seq, const int* seq_slot, void* out, long ldo,
+                                   float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
+                                   int head_dim, int window, float scale, int split_len, int n_splits, int* status,
+                                   void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (split_len < 0 || n_splits <= 0) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FX_F32)
-        return run<float>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
-                          out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, s);
+        return run<float>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
+                          seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
+                          split_len, n_splits, status, s);
     if (dtype == FX_BF16)
-        return run<bf16>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
-                         out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, s);
+        return run<bf16>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
+                         seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
+                         split_len, n_splits, status, s);
     return FX_ERR_DTYPE;
 }
 
@@ -425,12 +433,12 @@ extern "C" int fx_decode_attention_noalloc(const void* q, long ldq, const void* 
     // Every slot that the merge reads is written by the split kernel of the same call
     // (empty splits write max = -inf, sum = 0), so nothing has to be cleared first.
     if (dtype == FX_F32)
-        return run<float>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
+        return run<float>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                           out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, s);
+                          split_len, n_splits, nullptr, s);
     if (dtype == FX_BF16)
-        return run<bf16>(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot,
+        return run<bf16>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                          out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, s);
+                         split_len, n_splits, nullptr, s);
     return FX_ERR_DTYPE;
 }

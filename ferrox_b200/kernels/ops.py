@@ -52,8 +52,8 @@ _SIGNATURES = {
     "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P],
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
-    "fx_decode_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                            _I, _P],
+    "fx_decode_attention": [_P, _L, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
+                            _I, _P, _P],
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
     "fx_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "fx_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
@@ -320,12 +320,24 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
     return out
 
 
-DECODE_BLOCK_SLOTS = 148 * 3      # blocks of the decode attention kernel that run at the same time
+DECODE_BLOCK_SLOTS = 148 * 3      # blocks of the decode attention kernel that run at the same time (cp.async kernel)
 DECODE_BLOCK_OVERHEAD = 256       # start-up and merge of a block, in keys' worth of time
 DECODE_MAX_SPLITS = 16
 
 
-def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int):
+def decode_tma_blocks_per_sm(dtype, head_dim: int, page_size: int) -> int:
+    """Blocks an SM holds of the decode attention kernel that streams pages by TMA (attention_decode_tma.cu);
+    0 where it does not apply (then the cp.async kernel runs, three blocks an SM).  Mirrors the kernel's ring:
+    stages of 2 x head_dim x 64 x 2 bytes, as many as fit 96 KB (at least 3, at most 8)."""
+    if dtype != torch.bfloat16 or head_dim <= 0 or head_dim % 64 or head_dim > 256 or page_size < 64 or page_size % 64:
+        return 0
+    stage = 2 * (head_dim // 64) * 8192
+    stages = max(3, min(8, (96 * 1024) // stage))
+    smem = 1024 + max(stages * stage, 4 * 16 * head_dim * 4) + 16 * (head_dim * 2 + 16)
+    return min(2, (227 * 1024) // (smem + 1024))
+
+
+def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int, blocks_per_sm: int = 3):
     """(split_len, n_splits) for :func:`decode_attention`.  split_len 0: every token's visible keys are cut
     into n_splits runs of equal length, so that all blocks have work whatever the context length is.
     n_splits is a function of the step's size and the context limit only (a CUDA graph keeps its grid): the
@@ -334,7 +346,7 @@ def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int):
     blocks = max(1, n_tokens * n_kv_blocks)
     best, best_cost = 1, None
     for n in range(1, min(DECODE_MAX_SPLITS, max(1, -(-max_positions // 64))) + 1):
-        waves = -(-blocks * n // DECODE_BLOCK_SLOTS)
+        waves = -(-blocks * n // (148 * blocks_per_sm))
         cost = waves * (max_positions / n + DECODE_BLOCK_OVERHEAD)
         if best_cost is None or cost < best_cost * 0.98:   # more runs only for a clear gain
             best, best_cost = n, cost
@@ -342,12 +354,13 @@ def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int):
 
 
 def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,
-                     n_kv_heads, head_dim, window, scale, split_len, n_splits, part_acc, part_ml, stream=None):
+                     n_kv_heads, head_dim, window, scale, split_len, n_splits, part_acc, part_ml, status=None,
+                     stream=None):
     T = q.shape[0]
-    call("fx_decode_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), code(q), _ptr(block_table),
-         block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out), _rows(out),
-         _ptr(part_acc), _ptr(part_ml), T, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), split_len,
-         n_splits, stream if stream is not None else stream_ptr())
+    call("fx_decode_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], code(q),
+         _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
+         _ptr(out), _rows(out), _ptr(part_acc), _ptr(part_ml), T, n_heads, n_kv_heads, head_dim, int(window or 0),
+         float(scale), split_len, n_splits, _ptr(status), stream if stream is not None else stream_ptr())
     return out
 
 

@@ -94,13 +94,17 @@ class GqaAttention(Mixer):
             # few query tokens: split each request's keys over many blocks
             group = s.n_heads // s.n_kv_heads
             kv_blocks = s.n_kv_heads * -(-group // 8)
-            split_len, n_splits = ops.decode_split_plan(T, kv_blocks, cache.block_table.shape[1] * cache.page_size)
+            per_sm = ops.decode_tma_blocks_per_sm(qkv.dtype, s.head_dim, cache.page_size)
+            if per_sm:
+                kv_blocks = s.n_kv_heads * -(-group // 16)
+            split_len, n_splits = ops.decode_split_plan(T, kv_blocks, cache.block_table.shape[1] * cache.page_size,
+                                                        per_sm or 3)
             part_acc = self.rt.empty(T, s.n_heads, n_splits, s.head_dim, dtype=torch.float32)
             part_ml = self.rt.empty(T, s.n_heads, n_splits, 2, dtype=torch.float32)
             ops.decode_attention(
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, split_len, n_splits,
-                part_acc, part_ml, stream=batch.stream,
+                part_acc, part_ml, status=batch.status, stream=batch.stream,
             )
         elif batch.q_tiles_wide is not None and ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
             # prompt portions: tiles of 256 queries, tcgen05

@@ -259,6 +259,12 @@ ATT_CASES = [
     (28, 4, 128, 64, 100, [130]),
     (3, 3, 256, 16, 0, [50]),
     (12, 1, 32, 16, 0, [90]),
+    # head sizes in steps of 64 on pages of a multiple of 64: in bfloat16 the decode kernel that streams pages by TMA
+    (8, 2, 64, 64, 0, [200, 129, 1]),
+    (6, 2, 192, 128, 150, [318, 70]),
+    (40, 2, 64, 128, 0, [150, 260]),
+    (4, 4, 256, 64, 33, [140, 64]),
+    (16, 16, 128, 64, 70, [319]),
 ]
 
 
