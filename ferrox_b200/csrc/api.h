@@ -74,14 +74,14 @@ int fx_decode_split_tma(const void* q, long ldq, const void* k_pages, const void
                         const int* block_table, int table_width, int page_size, const int* positions,
                         const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml, int n_tokens,
                         int n_heads, int n_kv_heads, int head_dim, int window, float scale, int split_len,
-                        int n_splits, int* status, void* stream);
+                        int n_splits, int* status, void* out, long ldo, int* counters, void* stream);
 // n_pages > 0 (the number of pages behind k_pages / v_pages) lets bfloat16 take the TMA kernel; status: the step's
 // status word (may be null).
 int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages, int dtype,
                         const int* block_table, int table_width, int page_size, const int* positions,
                         const int* token_seq, const int* seq_slot, void* out, long ldo, float* part_acc,
                         float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
-                        float scale, int split_len, int n_splits, int* status, void* stream);
+                        float scale, int split_len, int n_splits, int* status, int* counters, void* stream);
 
 int fx_argmax(const float* logits, long ld, int n_rows, int vocab, int* out, void* stream);
 int fx_repetition_penalty(float* work, long ld, int n_rows, int vocab, const int* history, const int* hist_offsets,

@@ -313,7 +313,7 @@ template <typename T>
 int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages, const int* block_table,
         int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot, void* out,
         long ldo, float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
-        float scale, int split_len, int n_splits, int* status, cudaStream_t s)
+        float scale, int split_len, int n_splits, int* status, int* counters, cudaStream_t s)
 {
     constexpr int N = Vec<T>::N;
     if (head_dim % N || head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -322,10 +322,14 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n
         // bfloat16: the tensor-core kernels write the same partial results; the merge below is shared.  The one
         // that streams whole pages by TMA first (head sizes in steps of 64, pages of a multiple of 64 positions).
         int rc_mma = FX_ERR_SIZE;
-        if (n_pages > 0)
+        if (n_pages > 0) {
+            if (n_splits > 32) counters = nullptr;
             rc_mma = fx_decode_split_tma(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size,
                                          positions, token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads,
-                                         n_kv_heads, head_dim, window, scale, split_len, n_splits, status, (void*)s);
+                                         n_kv_heads, head_dim, window, scale, split_len, n_splits, status, out, ldo,
+                                         counters, (void*)s);
+            if (rc_mma == FX_OK && (counters || n_splits == 1)) return FX_OK;   // merged by the kernel's last blocks
+        }
         if (rc_mma < 0)
             rc_mma = fx_decode_split_mma(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions,
                                          token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads, n_kv_heads,
@@ -370,7 +374,7 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
                                    const int* positions, const int* token_seq, const int* seq_slot, void* out, long ldo,
                                    float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
                                    int head_dim, int window, float scale, int split_len, int n_splits, int* status,
-                                   void* stream)
+                                   int* counters, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (split_len < 0 || n_splits <= 0) return FX_ERR_SIZE;
@@ -378,11 +382,11 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
                           seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, status, s);
+                          split_len, n_splits, status, counters, s);
     if (dtype == FX_BF16)
         return run<bf16>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
                          seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, status, s);
+                         split_len, n_splits, status, counters, s);
     return FX_ERR_DTYPE;
 }
 
@@ -435,10 +439,10 @@ extern "C" int fx_decode_attention_noalloc(const void* q, long ldq, const void* 
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                           out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, nullptr, s);
+                          split_len, n_splits, nullptr, nullptr, s);
     if (dtype == FX_BF16)
         return run<bf16>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                          out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, nullptr, s);
+                         split_len, n_splits, nullptr, nullptr, s);
     return FX_ERR_DTYPE;
 }

@@ -49,6 +49,10 @@ struct DecArgs {
     float scale_log2e, scale;
     int split_len, n_splits, stages;
     int* status;
+    // With `counters` (one zeroed int per (token, block of heads), left zeroed again) the block that finishes a token's
+    // last key range merges all of them into `out`; without, the caller runs the merge kernel.  A single key range a
+    // token is written to `out` at once if that is given.
+    bf16* out; long ldo; int* counters;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -77,7 +81,8 @@ __device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, %0;
 __device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
 template <int DMAX>
-__global__ void __launch_bounds__(NTHREADS) decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+// (two blocks an SM up to head size 128: the compiler may use the registers that leaves, which the loop's speed needs)
+__global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                               const __grid_constant__ CUtensorMap map_v, DecArgs a)
 {
     const int head_dim = a.head_dim, n_heads = a.n_heads, n_kv_heads = a.n_kv_heads;
@@ -95,7 +100,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_tma_kernel(const __grid_const
     if (k_begin >= k_end) return;   // nothing of this range is visible: `merge` skips it by the same rule
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ int abort_flag_s;
+    __shared__ int abort_flag_s, last_block_s, complete_s;
+    __shared__ uint32_t ranges_with_keys_s;
     __shared__ int page_ok_s[MAX_STAGES];
     __shared__ float m_s[4][16], l_s[4][16];
     __shared__ __align__(8) uint64_t bars_s[2 * MAX_STAGES];
@@ -255,6 +261,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_tma_kernel(const __grid_const
         consumers_sync();                            // every warp has left the ring (all its tiles have arrived)
         float* acc_s = reinterpret_cast<float*>(smem_raw + (ring - smem_u32(smem_raw)));   // [4][16][head_dim]
         if (t4 == 0) { m_s[warp][g] = m0; m_s[warp][g + 8] = m1; l_s[warp][g] = l0; l_s[warp][g + 8] = l1; }
+        if (threadIdx.x == 0) complete_s = !abort_flag_s;   // one reading for all: the barriers below are taken by all or none
 #pragma unroll
         for (int i = 0; i < ON; ++i) {
             const int col = i * 8 + 2 * t4;
@@ -265,7 +272,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_tma_kernel(const __grid_const
             }
         }
         consumers_sync();
-        if (!*abort_flag) {
+        if (complete_s) {
             for (int idx = threadIdx.x; idx < nq * head_dim; idx += NCONSUMERS) {
                 const int h = idx / head_dim, e = idx - h * head_dim;
                 float mm = -INFINITY;
@@ -280,10 +287,55 @@ __global__ void __launch_bounds__(NTHREADS) decode_tma_kernel(const __grid_const
                         acc += acc_s[((long)w * 16 + h) * head_dim + e] * wgt;
                     }
                 }
+                if (a.n_splits == 1 && a.out) {
+                    // the only key range of its token: this is the result
+                    a.out[(long)tkn * a.ldo + (long)(h0 + h) * head_dim + e] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+                    continue;
+                }
                 const long slot = ((long)tkn * n_heads + (h0 + h)) * a.n_splits + split;
                 a.part_acc[slot * head_dim + e] = acc;
                 // merge_kernel works with natural-log maxima of the scaled scores
                 if (e == 0) { a.part_ml[slot * 2] = mm == -INFINITY ? -INFINITY : mm * a.scale; a.part_ml[slot * 2 + 1] = ll; }
+            }
+            if (a.counters && a.n_splits > 1) {
+                // ---- the block that finishes a token's last key range merges them, in range order ----
+                __threadfence();                       // this block's partial result is visible before it is counted
+                consumers_sync();
+                if (threadIdx.x == 0) {
+                    uint32_t with_keys = 0;            // ranges without visible keys never ran (n_splits <= 32 here)
+                    for (int s2 = 0; s2 < a.n_splits; ++s2) {
+                        int b, e;
+                        fx_split_range(pos, lo, s2, a.n_splits, a.split_len, b, e);
+                        if (b < e) with_keys |= 1u << s2;
+                    }
+                    ranges_with_keys_s = with_keys;
+                    int* counter = a.counters + (long)tkn * gridDim.x + blockIdx.x;
+                    const int before = atomicAdd(counter, 1);
+                    last_block_s = before == __popc(with_keys) - 1;
+                    if (last_block_s) *counter = 0;    // every other block of this token has counted: ready for the next launch
+                }
+                consumers_sync();
+                if (last_block_s) {
+                    __threadfence();
+                    const uint32_t with_keys = ranges_with_keys_s;
+                    for (int idx = threadIdx.x; idx < nq * head_dim; idx += NCONSUMERS) {
+                        const int h = idx / head_dim, e = idx - h * head_dim;
+                        const long base = ((long)tkn * n_heads + (h0 + h)) * a.n_splits;
+                        float mm = -INFINITY;
+                        for (int s2 = 0; s2 < a.n_splits; ++s2)
+                            if (with_keys >> s2 & 1) mm = fmaxf(mm, __ldcg(a.part_ml + (base + s2) * 2));
+                        float ll = 0.f, acc = 0.f;
+                        for (int s2 = 0; s2 < a.n_splits; ++s2) {
+                            if (!(with_keys >> s2 & 1)) continue;
+                            const float ms = __ldcg(a.part_ml + (base + s2) * 2);
+                            if (ms == -INFINITY) continue;
+                            const float wgt = __expf(ms - mm);
+                            ll += __ldcg(a.part_ml + (base + s2) * 2 + 1) * wgt;
+                            acc += __ldcg(a.part_acc + (base + s2) * head_dim + e) * wgt;
+                        }
+                        a.out[(long)tkn * a.ldo + (long)(h0 + h) * head_dim + e] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+                    }
+                }
             }
         }
     }
@@ -332,14 +384,17 @@ static int tma_ring(int head_dim, size_t* smem)
     return stages;
 }
 
-// Partials only, as fx_decode_split_mma; the caller runs the merge.  Returns FX_ERR_SIZE for shapes it does not take.
+// As fx_decode_split_mma (partials; the caller runs the merge), or with `counters` the whole attention: the last block of
+// a token merges its key ranges into `out`.  Returns FX_ERR_SIZE for shapes it does not take.
 extern "C" int fx_decode_split_tma(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages,
                                    const int* block_table, int table_width, int page_size, const int* positions,
                                    const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml,
                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                                   int split_len, int n_splits, int* status, void* stream)
+                                   int split_len, int n_splits, int* status, void* out, long ldo, int* counters,
+                                   void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
+    if (counters && (n_splits > 32 || !out || ldo % 2)) return FX_ERR_SIZE;
     size_t smem = 0;
     const int stages = tma_ring(head_dim, &smem);
     if (stages == 0 || n_pages <= 0 || page_size < TK || page_size % TK || n_kv_heads <= 0 || n_heads % n_kv_heads)
@@ -365,6 +420,8 @@ extern "C" int fx_decode_split_tma(const void* q, long ldq, const void* k_pages,
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f; a.scale = scale;
     a.split_len = split_len; a.n_splits = n_splits; a.stages = stages; a.status = status;
+    a.out = (bf16*)out; a.ldo = ldo; a.counters = counters;
+    if (n_splits > 1 && !counters) a.out = nullptr;   // partial results only
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim <= 64) return launch<64>(mk, mv, a, grid, smem, s);
     if (head_dim <= 128) return launch<128>(mk, mv, a, grid, smem, s);

@@ -53,7 +53,7 @@ _SIGNATURES = {
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "fx_decode_attention": [_P, _L, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                            _I, _P, _P],
+                            _I, _P, _P, _P],
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
     "fx_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "fx_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
@@ -321,7 +321,9 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
 
 
 DECODE_BLOCK_SLOTS = 148 * 3      # blocks of the decode attention kernel that run at the same time (cp.async kernel)
-DECODE_BLOCK_OVERHEAD = 256       # start-up and merge of a block, in keys' worth of time
+DECODE_BLOCK_OVERHEAD = 128       # start and end of a block, in keys' worth of a block's time
+DECODE_MERGE_COST = 256           # the merge of the key ranges, in the same unit
+DECODE_BLOCKS_TO_SATURATE = 160   # blocks streaming at the same time that draw the machine's whole bandwidth
 DECODE_MAX_SPLITS = 16
 
 
@@ -337,17 +339,23 @@ def decode_tma_blocks_per_sm(dtype, head_dim: int, page_size: int) -> int:
     return min(2, (227 * 1024) // (smem + 1024))
 
 
-def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int, blocks_per_sm: int = 3):
+def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int, blocks_per_sm: int = 3,
+                      single_is_final: bool = False):
     """(split_len, n_splits) for :func:`decode_attention`.  split_len 0: every token's visible keys are cut
     into n_splits runs of equal length, so that all blocks have work whatever the context length is.
-    n_splits is a function of the step's size and the context limit only (a CUDA graph keeps its grid): the
-    number of runs that minimises (waves of blocks) x (keys of a run + a block's fixed cost); a few blocks
-    beyond a whole wave cost a wave of their own, and many short runs pay the fixed cost too often."""
+    n_splits is a function of the step's size and the context limit only (a CUDA graph keeps its grid).  The cost
+    of n runs, in the time one block takes for a key: the keys stream at the rate of the whole machine
+    (DECODE_BLOCKS_TO_SATURATE blocks' worth) or, with few or unevenly many blocks, at the rate of the blocks of a
+    wave one after the other; every wave pays a block's start and end; more than one run pays the merge
+    (``single_is_final``: a kernel that writes a single run's result itself, so only n > 1 pays it).  Measured
+    on a B200 with 16 kv heads of 128: 64 requests 178 us with one run and 189 us with two, 8 requests 35 and 29."""
     blocks = max(1, n_tokens * n_kv_blocks)
+    slots = 148 * blocks_per_sm
     best, best_cost = 1, None
     for n in range(1, min(DECODE_MAX_SPLITS, max(1, -(-max_positions // 64))) + 1):
-        waves = -(-blocks * n // (148 * blocks_per_sm))
-        cost = waves * (max_positions / n + DECODE_BLOCK_OVERHEAD)
+        waves = -(-blocks * n // slots)
+        stream = max(blocks * max_positions / DECODE_BLOCKS_TO_SATURATE, waves * max_positions / n)
+        cost = stream + waves * DECODE_BLOCK_OVERHEAD + (DECODE_MERGE_COST if n > 1 or not single_is_final else 0)
         if best_cost is None or cost < best_cost * 0.98:   # more runs only for a clear gain
             best, best_cost = n, cost
     return 0, best
@@ -355,12 +363,25 @@ def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int, block
 
 def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,
                      n_kv_heads, head_dim, window, scale, split_len, n_splits, part_acc, part_ml, status=None,
-                     stream=None):
+                     counters=None, stream=None):
+    """``counters``: zeroed int32 scratch that the call leaves zeroed, at least tokens x ceil(group / 16) x kv heads;
+    with it the kernel that streams pages by TMA merges the key ranges itself (one kernel instead of two)."""
+    global _launches
     T = q.shape[0]
+    per_sm = decode_tma_blocks_per_sm(q.dtype, head_dim, page_size)
+    blocks = T * n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
+    # Merging in the kernel pays while all blocks run at the same time: the count and the fence lengthen the end of
+    # every block, which costs nothing only where no other block waits for its place.
+    if counters is not None and not (per_sm > 0 and 1 < n_splits <= 32 and counters.numel() >= blocks
+                                     and blocks * n_splits <= 148 * per_sm):
+        counters = None
+    if per_sm > 0 and (counters is not None or n_splits == 1):
+        _launches -= 1      # no merge kernel
     call("fx_decode_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], code(q),
          _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(out), _rows(out), _ptr(part_acc), _ptr(part_ml), T, n_heads, n_kv_heads, head_dim, int(window or 0),
-         float(scale), split_len, n_splits, _ptr(status), stream if stream is not None else stream_ptr())
+         float(scale), split_len, n_splits, _ptr(status), _ptr(counters),
+         stream if stream is not None else stream_ptr())
     return out
 
 

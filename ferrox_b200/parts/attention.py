@@ -21,6 +21,7 @@ from ..weights.loader import TensorDecl
 from .base import Mixer, build_part, register_part
 
 
+RANGE_COUNTERS = 16384            # (token, block of heads) pairs of a decode step whose key ranges one kernel merges
 DECODE_ATTENTION_MAX_NEW = 8  # entries that bring at most this many tokens use the split-key kernel
 
 
@@ -75,6 +76,9 @@ class GqaAttention(Mixer):
         self.w_o = src.get(p + "o_proj.weight")
         if self.position is not None:
             self.position.load(src, rt)
+        # zeroed scratch of the decode attention kernel that merges its own key ranges (it leaves it zeroed)
+        self._range_counters = (torch.zeros(RANGE_COUNTERS, dtype=torch.int32, device=rt.device)
+                                if rt.device.type == "cuda" else None)
 
     def forward_add(self, x, h, batch, cache):
         s = self.spec
@@ -98,13 +102,13 @@ class GqaAttention(Mixer):
             if per_sm:
                 kv_blocks = s.n_kv_heads * -(-group // 16)
             split_len, n_splits = ops.decode_split_plan(T, kv_blocks, cache.block_table.shape[1] * cache.page_size,
-                                                        per_sm or 3)
+                                                        per_sm or 3, single_is_final=per_sm > 0)
             part_acc = self.rt.empty(T, s.n_heads, n_splits, s.head_dim, dtype=torch.float32)
             part_ml = self.rt.empty(T, s.n_heads, n_splits, 2, dtype=torch.float32)
             ops.decode_attention(
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, split_len, n_splits,
-                part_acc, part_ml, status=batch.status, stream=batch.stream,
+                part_acc, part_ml, status=batch.status, counters=self._range_counters, stream=batch.stream,
             )
         elif batch.q_tiles_wide is not None and ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
             # prompt portions: tiles of 256 queries, tcgen05

@@ -11,10 +11,15 @@ def test_decode_split_plan_depends_on_sizes_only_and_stays_in_bounds():
                 assert split_len == 0 and 1 <= n <= ops.DECODE_MAX_SPLITS
                 assert n <= max(1, -(-ctx // 64))          # no run shorter than one tile of keys
                 assert (split_len, n) == ops.decode_split_plan(tokens, kv_blocks, ctx)
-    # one wave of blocks beats a wave and a bit: 8 tokens x 16 kv heads -> 3 runs (384 blocks), not 4 (512 > 444)
-    assert ops.decode_split_plan(8, 16, 4096) == (0, 3)
-    # a single request: many runs, but bounded
-    assert ops.decode_split_plan(1, 16, 4096)[1] == ops.DECODE_MAX_SPLITS
+    # 8 tokens x 16 kv heads: two runs fill one wave (256 of 444 blocks); a third adds no bandwidth
+    assert ops.decode_split_plan(8, 16, 4096) == (0, 2)
+    # the kernel that holds two blocks an SM and writes a single run's result itself
+    assert ops.decode_split_plan(8, 16, 4096, 2, single_is_final=True) == (0, 2)
+    assert ops.decode_split_plan(16, 16, 4096, 2, single_is_final=True) == (0, 1)
+    assert ops.decode_split_plan(64, 16, 4096, 2, single_is_final=True) == (0, 1)
+    # a single request: many runs, but no more than fill the machine
+    assert 8 <= ops.decode_split_plan(1, 16, 4096)[1] <= ops.DECODE_MAX_SPLITS
+    assert 8 <= ops.decode_split_plan(1, 16, 4096, 2, single_is_final=True)[1] <= ops.DECODE_MAX_SPLITS
     # many requests already fill the machine
     assert ops.decode_split_plan(200, 16, 4096)[1] <= 2
 

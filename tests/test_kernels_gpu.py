@@ -297,6 +297,16 @@ def test_attention_over_pages(dtype, case, kernel):
             o.decode_attention(q, kp, vp, table, ps, positions, token_seq, seq_slot, out, nh, nkv, d, window, scale,
                                split_len, n_splits, pa, pm)
             _check_attention(out, q, ks, vs, toks, nh, d, window, scale, dtype)
+            # the key ranges merged by the kernel's last blocks instead of the merge kernel: the same bits, twice
+            # in a row with the same counters, which it leaves zeroed
+            counters = torch.zeros(T * nkv * -(-(nh // nkv) // 16), dtype=torch.int32, device=DEV)
+            for _ in range(2):
+                fused = torch.zeros_like(out)
+                o.decode_attention(q, kp, vp, table, ps, positions, token_seq, seq_slot, fused, nh, nkv, d, window,
+                                   scale, split_len, n_splits, torch.empty_like(pa), torch.empty_like(pm),
+                                   counters=counters)
+                assert torch.equal(fused, out)
+                assert int(counters.abs().sum()) == 0
         return
     _check_attention(out, q, ks, vs, toks, nh, d, window, scale, dtype)
 
