@@ -59,6 +59,8 @@ int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int w_rows, co
                 void* stream);
 int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo, int dtype, int n_rows, int width,
                    void* stream);
+int fx_route(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
+             int* scratch, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
 int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
                    int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
 int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin, void* stream);

@@ -11,31 +11,35 @@ namespace {
 // and the weights are the kept p, divided by their sum when `renorm` is set
 // (reference: crates/ferrox-moe/src/lib.rs:333-355; lowest-index tie-break as in
 // its GPU kernel, crates/ferrox-metal/src/gpu.rs:686-699).
+// In shared memory a probability is kept as its bit pattern plus one (probabilities are >= 0, so the patterns
+// order like the values) and 0 once taken: the warp's maximum and the lowest index that holds it are two integer
+// warp reductions instead of two chains of shuffles.  `counts` (optional): counts[e] += 1 for each kept expert.
 __device__ __forceinline__ void route_token(const float* __restrict__ lg, float* p, int lane, int t, int n_experts,
-                                            int top_k, int renorm, int* __restrict__ ids, float* __restrict__ weights)
+                                            int top_k, int renorm, int* __restrict__ ids, float* __restrict__ weights,
+                                            int* __restrict__ counts = nullptr)
 {
+    uint32_t* pb = reinterpret_cast<uint32_t*>(p);
     float mx = -INFINITY;
     for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
     mx = warp_max(mx);
     float sum = 0.f;
-    for (int e = lane; e < n_experts; e += 32) { const float v = expf(lg[e] - mx); p[e] = v; sum += v; }
+    for (int e = lane; e < n_experts; e += 32) { const float v = expf(lg[e] - mx); pb[e] = __float_as_uint(v) + 1u; sum += v; }
     sum = warp_sum(sum);
     __syncwarp();
     float kept = 0.f;
     for (int k = 0; k < top_k; ++k) {
-        float best = -1.f; int best_e = 0x7fffffff;
+        uint32_t best = 0u; int best_e = 0x7fffffff;
         for (int e = lane; e < n_experts; e += 32) {
-            const float v = p[e];
+            const uint32_t v = pb[e];
             if (v > best) { best = v; best_e = e; }  // ascending e: the first maximum stays
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        const uint32_t top = __reduce_max_sync(0xffffffffu, best);
+        const int win = __reduce_min_sync(0xffffffffu, best == top ? best_e : 0x7fffffff);
+        const float w = __uint_as_float(top - 1u) / sum;
+        if (lane == 0) {
+            ids[(long)t * top_k + k] = win; weights[(long)t * top_k + k] = w; pb[win] = 0u;
+            if (counts) atomicAdd(&counts[win], 1);
         }
-        const float w = best / sum;
-        if (lane == 0) { ids[(long)t * top_k + k] = best_e; weights[(long)t * top_k + k] = w; p[best_e] = -2.f; }
         kept += w;
         __syncwarp();
     }
@@ -46,20 +50,21 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
 }
 
 __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, int n_tokens, int n_experts, int top_k,
-                                   int renorm, int* __restrict__ ids, float* __restrict__ weights)
+                                   int renorm, int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts)
 {
     extern __shared__ float smem[];  // [warps][n_experts]
+    fx_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= n_tokens) return;
     route_token(logits + (long)t * ld, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
-                weights);
+                weights, counts);
 }
 
 // Routing and bookkeeping of a small step in ONE block: top-k per token (a warp
 // each), then counts, offsets, the list of experts that got rows, and the placement
 // of every (token, rank) pair, all in shared memory.
-constexpr int SMALL_WARPS = 16;
+constexpr int SMALL_WARPS = 32;
 __global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
     const float* __restrict__ logits, long ld, int n_tokens, int n_experts, int top_k, int renorm,
     int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ src_token, int* __restrict__ inv_perm,
@@ -140,6 +145,46 @@ __global__ void place_kernel(const int* __restrict__ ids, int n, int n_experts, 
     }
 }
 
+// scan_kernel and place_kernel in one: every block sums the counts before its experts itself (one warp, a run of
+// experts per lane), block 0 also writes the offsets (and the list of experts with rows); cursors start at zero.
+constexpr int SCAN_MAX_EXPERTS = 4096;
+__global__ void scan_place_kernel(const int* __restrict__ ids, int n, int n_experts, int top_k,
+                                  const int* __restrict__ counts, int* __restrict__ cursors, int* __restrict__ offsets,
+                                  int* __restrict__ src_token, int* __restrict__ inv_perm, int* __restrict__ active, int n_slots)
+{
+    __shared__ int offs[SCAN_MAX_EXPERTS + 1];
+    fx_pdl_wait();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x, per = (n_experts + 31) / 32;
+        const int e0 = min(lane * per, n_experts), e1 = min(e0 + per, n_experts);
+        int mine = 0;
+        for (int e = e0; e < e1; ++e) mine += counts[e];
+        int before = mine;                         // inclusive scan over the lanes
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, before, o); if (lane >= o) before += v; }
+        int run = before - mine;
+        for (int e = e0; e < e1; ++e) { offs[e] = run; run += counts[e]; }
+        if (lane == 31) offs[n_experts] = before;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0) {
+        for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) offsets[e] = offs[e];
+        if (active && threadIdx.x == 0) {
+            int n_active = 0;
+            for (int e = 0; e < n_experts; ++e)
+                if (offs[e + 1] > offs[e] && n_active < n_slots) active[n_active++] = e;
+            for (int i = n_active; i < n_slots; ++i) active[i] = -1;
+        }
+    }
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int e = ids[i];
+        if (e < 0 || e >= n_experts) { inv_perm[i] = 0; continue; }
+        const int r = offs[e] + atomicAdd(&cursors[e], 1);
+        src_token[r] = i / top_k;
+        inv_perm[i] = r;
+    }
+}
+
 }  // namespace
 
 extern "C" int fx_router_topk(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
@@ -151,7 +196,31 @@ extern "C" int fx_router_topk(const float* logits, long ld, int n_tokens, int n_
     const size_t smem = (size_t)warps * n_experts * sizeof(float);
     if (smem > 48 * 1024) return FX_ERR_SIZE;
     router_topk_kernel<<<(unsigned)fx_cdiv(n_tokens, warps), warps * 32, smem, (cudaStream_t)stream>>>(
-        logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights);
+        logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, nullptr);
+    return fx_launch_status();
+}
+
+// fx_router_topk and fx_moe_align of a step of any size in two kernels (and a memset): the top-k kernel counts the
+// rows of every expert as it chooses them, the placing kernel sums the counts itself.  scratch: 2 * n_experts ints.
+extern "C" int fx_route(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
+                        float* weights, int* scratch, int* offsets, int* src_token, int* inv_perm, int* active,
+                        int n_slots, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (top_k <= 0 || top_k > n_experts || n_experts > SCAN_MAX_EXPERTS) return FX_ERR_SIZE;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * n_experts * sizeof(float);
+    if (smem > 48 * 1024) return FX_ERR_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(int) * 2 * n_experts, s);
+    if (e != cudaSuccess) return (int)e;
+    fx_launch_pdl(router_topk_kernel, (unsigned)fx_cdiv(n_tokens, warps), warps * 32, smem, s,
+                  logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, scratch);
+    const int n = n_tokens * top_k;
+    int blocks = (int)fx_cdiv(n, 256);
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    fx_launch_pdl(scan_place_kernel, blocks, 256, 0, s, ids, n, n_experts, top_k, scratch, scratch + n_experts, offsets,
+                  src_token, inv_perm, active, n_slots);
     return fx_launch_status();
 }
 

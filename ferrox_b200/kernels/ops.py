@@ -44,6 +44,7 @@ _SIGNATURES = {
     "fx_gemm_tc2": [_P, _L, _P, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
     "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
+    "fx_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
@@ -62,7 +63,7 @@ _SIGNATURES = {
 _fn = {}
 
 # kernels launched by one call of an entry point (fx_moe_align: count, scan, place)
-_KERNELS = {"fx_moe_align": 3, "fx_decode_attention": 2}   # (a split-K product adds a second kernel; not counted)
+_KERNELS = {"fx_moe_align": 3, "fx_route": 2, "fx_decode_attention": 2}   # (a split-K product adds a second kernel; not counted)
 _launches = 0
 
 
@@ -216,6 +217,20 @@ def route_small(logits, top_k, renorm, ids, weights, offsets, src_token, inv_per
     T, E = logits.shape[0], (n_experts or logits.shape[1])
     call("fx_route_small", _ptr(logits), _rows(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights), _ptr(offsets),
          _ptr(src_token), _ptr(inv_perm), _ptr(active), active.numel() if active is not None else 0,
+         stream if stream is not None else stream_ptr())
+
+
+ROUTE_SMALL_MAX_TOKENS = 48    # measured with 60 experts: the one-block kernel 4 to 8 us up to here, the two kernels 8 us
+ROUTE_SMALL_MAX_EXPERTS = 256  # its shared memory: 32 warps x experts x 4 bytes
+
+
+def route(logits, top_k, renorm, ids, weights, scratch, offsets, src_token, inv_perm, active=None, n_experts=None,
+          stream=None):
+    """router_topk and moe_align of a step of any size: the top-k kernel counts each expert's rows as it chooses,
+    the placing kernel sums the counts itself.  ``scratch``: 2 * n_experts int32."""
+    T, E = logits.shape[0], (n_experts or logits.shape[1])
+    call("fx_route", _ptr(logits), _rows(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights), _ptr(scratch),
+         _ptr(offsets), _ptr(src_token), _ptr(inv_perm), _ptr(active), active.numel() if active is not None else 0,
          stream if stream is not None else stream_ptr())
 
 

@@ -135,12 +135,12 @@ class SoftmaxTopkMoe(FeedForward):
         src_token = rt.empty(T * K, dtype=i32)
         inv_perm = rt.empty(T * K, dtype=i32)
         active = rt.empty(min(E, T * K), dtype=i32) if small else None
-        if T <= 256 and E <= 512:
+        if T <= ops.ROUTE_SMALL_MAX_TOKENS and E <= ops.ROUTE_SMALL_MAX_EXPERTS:
             ops.route_small(logits, K, s.norm_topk_prob, ids, weights, offsets, src_token, inv_perm, active,
                             n_experts=E, stream=st)
         else:
-            ops.router_topk(logits, K, s.norm_topk_prob, ids, weights, n_experts=E, stream=st)
-            ops.moe_align(ids, E, self._scratch, offsets, src_token, inv_perm, active, stream=st)
+            ops.route(logits, K, s.norm_topk_prob, ids, weights, self._scratch, offsets, src_token, inv_perm, active,
+                      n_experts=E, stream=st)
 
         act = rt.empty(T * K, I)
         y = rt.empty(T * K, H)

@@ -424,6 +424,29 @@ def test_route_small_equals_the_two_step_routing(T, E, K):
     assert act == [e for e in range(E) if counts[e] > 0]
 
 
+@pytest.mark.parametrize("T,E,K", [(1, 4, 2), (70, 60, 4), (2048, 61, 5), (700, 1000, 8), (300, 8, 3)])
+def test_route_in_two_kernels_equals_the_separate_steps(T, E, K):
+    o = ops()
+    logits = rnd(T, E + 1, scale=2.0, seed=T)      # one more column than experts, as with the shared expert's gate
+    i32 = dict(dtype=torch.int32, device=DEV)
+    ids_a, w_a = torch.empty(T, K, **i32), torch.empty(T, K, device=DEV)
+    o.router_topk(logits, K, True, ids_a, w_a, n_experts=E)
+    ids_b, w_b = torch.empty(T, K, **i32), torch.empty(T, K, device=DEV)
+    offsets, src, inv = torch.empty(E + 1, **i32), torch.empty(T * K, **i32), torch.empty(T * K, **i32)
+    active = torch.empty(min(E, T * K), **i32)
+    scratch = torch.full((2 * E,), 7, **i32)       # the call clears it itself
+    for _ in range(2):
+        o.route(logits, K, True, ids_b, w_b, scratch, offsets, src, inv, active, n_experts=E)
+        assert torch.equal(ids_a, ids_b) and torch.equal(w_a, w_b)
+        counts = torch.bincount(ids_b.flatten().long(), minlength=E)
+        assert offsets.tolist() == [0] + counts.cumsum(0).tolist()
+        inv_l, src_l, off_l, flat = inv.tolist(), src.tolist(), offsets.tolist(), ids_b.flatten().tolist()
+        assert sorted(inv_l) == list(range(T * K))
+        assert all(off_l[flat[i]] <= r < off_l[flat[i] + 1] and src_l[r] == i // K for i, r in enumerate(inv_l))
+        act = [e for e in active.tolist() if e >= 0]
+        assert act == [e for e in range(E) if counts[e] > 0][: active.numel()]
+
+
 def test_rope_table_matches_inline_angles():
     o = ops()
     nh, nkv, d, ps = 2, 1, 32, 8
