@@ -153,12 +153,13 @@ def swiglu_mlp(x, gate, up, down):
     return (silu(x @ gate.T) * (x @ up.T)) @ down.T
 
 
-def route(logits, k, renorm):
+def route(logits, k, renorm, chosen=None):
     """Softmax over all experts, the k largest in descending order (lowest index
     first among equals), weights = those probabilities, divided by their sum when
-    renorm (crates/ferrox-moe/src/lib.rs:333-355)."""
+    renorm (crates/ferrox-moe/src/lib.rs:333-355).  ``chosen``: this set of experts
+    instead of the k largest (what a router with slightly rounded logits may decide)."""
     p = torch.softmax(logits, dim=-1)
-    order = sorted(range(p.numel()), key=lambda e: (-float(p[e]), e))[:k]
+    order = sorted(range(p.numel()) if chosen is None else chosen, key=lambda e: (-float(p[e]), e))[:k]
     wts = p[order]
     if renorm:
         wts = wts / wts.sum()
@@ -178,7 +179,7 @@ def router_margins(x, w, cfg, l):
     return ((top[:, k - 1] - top[:, k]) / lg.abs().max(dim=-1).values).to(torch.float32)
 
 
-def moe_block(x, w, cfg, l):
+def moe_block(x, w, cfg, l, chosen=None):
     """Router, routed experts summed in rank order, shared expert scaled by
     sigmoid(w_sg . x) (crates/ferrox-moe/src/lib.rs:735-752;
     crates/ferrox-models/src/decoder.rs:2660-2681)."""
@@ -187,7 +188,7 @@ def moe_block(x, w, cfg, l):
     k, renorm = cfg["num_experts_per_tok"], cfg.get("norm_topk_prob", False)
     router_logits = x @ w[p + "gate.weight"].T
     for t in range(x.shape[0]):
-        experts, wts = route(router_logits[t], k, renorm)
+        experts, wts = route(router_logits[t], k, renorm, chosen)
         y = torch.zeros_like(x[t])
         for e, wt in zip(experts, wts):
             y = y + wt * swiglu_mlp(
@@ -211,9 +212,35 @@ def dense_block(x, w, l):
 
 
 # --------------------------------------------------------------------------- whole model
-def forward(cfg, w, tokens, return_hidden=False, return_margins=False):
+def close_choices(logits, k, rel):
+    """The sets of k experts that differ from the k largest in one expert, where the one
+    left and the one taken both lie within rel * max|logit| of the border between taken
+    and left out: the choices a router may make whose logits are off by that much."""
+    order = sorted(range(logits.numel()), key=lambda e: (-float(logits[e]), e))
+    if len(order) <= k:
+        return []
+    band = rel * float(logits.abs().max())
+    lo, hi = float(logits[order[k]]), float(logits[order[k - 1]])
+    out = [e for e in order[:k] if float(logits[e]) <= lo + band]
+    into = [e for e in order[k:] if float(logits[e]) >= hi - band]
+    return [[e for e in order[:k] if e != a] + [b] for a in out for b in into]
+
+
+def one_layer_position(cfg, w, h_t, n_t, chosen):
+    """Logits of one position of a model of ONE layer from its residual stream after attention
+    (h_t), the normed input of the feed-forward (n_t) and the experts its router is to take."""
+    assert cfg["num_hidden_layers"] == 1
+    h = h_t[None] + moe_block(n_t[None], w, cfg, 0, chosen)
+    hn = rms_norm(h, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-6))
+    head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
+    return (hn @ head.T)[0]
+
+
+def forward(cfg, w, tokens, return_hidden=False, return_margins=False, return_ffn_inputs=False):
     """Logits [T, vocab] for one whole sequence starting at position 0
-    (crates/ferrox-models/src/decoder.rs:3014-3677 and :2952-2973)."""
+    (crates/ferrox-models/src/decoder.rs:3014-3677 and :2952-2973).  ``return_ffn_inputs``:
+    also, for the last layer, the residual stream after attention and the normed input of
+    the feed-forward."""
     dtype = w["model.embed_tokens.weight"].dtype
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(tokens.numel())
@@ -226,11 +253,14 @@ def forward(cfg, w, tokens, return_hidden=False, return_margins=False):
         n = rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
         if layer_is_moe(cfg, l) and return_margins:
             margins = torch.minimum(margins, router_margins(n, w, cfg, l))
+        ffn_inputs = (h, n)
         h = h + (moe_block(n, w, cfg, l) if layer_is_moe(cfg, l) else dense_block(n, w, l))
     hn = rms_norm(h, w["model.norm.weight"], eps)
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     logits = hn @ head.T
     assert logits.dtype == dtype
+    if return_ffn_inputs:
+        return logits, margins, ffn_inputs
     if return_margins:
         return logits, margins
     return (logits, h) if return_hidden else logits

@@ -19,12 +19,30 @@ class Expected:
     """Plain logits per request plus, per position, the router's smallest relative
     margin over the layers (see plain.router_margins)."""
 
-    def __init__(self, folder: str, prompts: Dict[str, List[int]]):
-        cfg, w = plain.load_model(folder, torch.float32)
-        self.logits, self.margins = {}, {}
+    def __init__(self, folder: str, prompts: Dict[str, List[int]], one_layer: bool = False):
+        """``one_layer``: keep what `close_to_a_choice` needs (a model of one layer only)."""
+        self.cfg, self.w = plain.load_model(folder, torch.float32)
+        self.logits, self.margins, self.ffn_inputs = {}, {}, {}
         for rid, toks in prompts.items():
-            lg, mg = plain.forward(cfg, w, toks, return_margins=True)
+            if one_layer:
+                lg, mg, self.ffn_inputs[rid] = plain.forward(self.cfg, self.w, toks, return_ffn_inputs=True)
+            else:
+                lg, mg = plain.forward(self.cfg, self.w, toks, return_margins=True)
             self.logits[rid], self.margins[rid] = lg, mg
+
+    def close_to_a_choice(self, rid: str, t: int, got: torch.Tensor, rel: float = 0.05) -> float:
+        """In a model of one layer the logits of a position hang on its own router's choice only.  The smallest
+        distance (relative to the largest plain logit of the request) between ``got`` and the plain logits of
+        position t under any choice of experts that differs from the plain one in one expert near the border
+        (plain.close_choices): what an engine with rounded router logits may rightly have computed."""
+        h, n = self.ffn_inputs[rid]
+        router = n[t] @ self.w["model.layers.0.mlp.gate.weight"].T
+        scale = float(self.logits[rid].abs().max())
+        best = float("inf")
+        for chosen in plain.close_choices(router, self.cfg["num_experts_per_tok"], rel):
+            lg = plain.one_layer_position(self.cfg, self.w, h[t], n[t], chosen)
+            best = min(best, float((got - lg).abs().max()) / scale)
+        return best
 
     def __getitem__(self, rid):
         return self.logits[rid]
@@ -89,6 +107,21 @@ def run_tail_decode(eng, prompts, tail=32):
         for i in range(head, len(toks)):
             c.step({rid: toks[i:i + 1]})
         eng.close_request(c.slots.pop(rid))
+    return {rid: c.stacked(rid) for rid in prompts}
+
+
+def run_decode_together(eng, prompts, tail=8):
+    """Most of each request in a step of its own, then the last ``tail`` tokens of all requests one by one in
+    common steps: a decode batch of requests of different lengths."""
+    c = Collector(eng)
+    rest = {}
+    for rid, toks in prompts.items():
+        head = max(1, len(toks) - tail)
+        c.step({rid: toks[:head]})
+        rest[rid] = list(toks[head:])
+    while any(rest.values()):
+        portions = {rid: [r.pop(0)] for rid, r in rest.items() if r}
+        c.step(portions, end=[rid for rid in portions if not rest[rid]])
     return {rid: c.stacked(rid) for rid in prompts}
 
 

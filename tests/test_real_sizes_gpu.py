@@ -39,16 +39,23 @@ def model(request, tmp_path_factory):
     folder = write_random_model(str(tmp_path_factory.mktemp("real") / request.param), cfg, seed=5, std=0.02,
                                 norm_init="around_one")
     rng = random.Random(1)
-    prompts = {"p": [rng.randrange(cfg["vocab_size"]) for _ in range(150)],
-               "q": [rng.randrange(cfg["vocab_size"]) for _ in range(70)]}
-    return folder, prompts, ru.Expected(folder, prompts)
+    prompts = {rid: [rng.randrange(cfg["vocab_size"]) for _ in range(n)]
+               for rid, n in (("p", 150), ("q", 70), ("r", 200), ("s", 9))}
+    return folder, prompts, ru.Expected(folder, prompts, one_layer=True)
 
 
 def check(got, want, tol, bf16):
+    """Every position within the tolerance of the plain logits.  In bfloat16 rounded router logits may tip a close
+    choice between experts: such a position must then be within the tolerance of the plain logits under that other
+    choice (one layer: a position's logits hang on its own router only), and such positions must be few.  No
+    position is left out."""
     for rid in want:
         diff = (got[rid] - want[rid]).abs().max(dim=1).values / want[rid].abs().max()
-        if bf16:
-            diff = torch.where(want.margins[rid] < 2.0 ** -7, torch.zeros_like(diff), diff)
+        tipped = 0
+        for t in (diff >= tol).nonzero().flatten().tolist() if bf16 else []:
+            diff[t] = want.close_to_a_choice(rid, t, got[rid][t])
+            tipped += 1
+        assert tipped <= max(2, len(diff) // 20), (rid, tipped)
         assert float(diff.max()) < tol, (rid, int(diff.argmax()), float(diff.max()))
 
 
@@ -57,7 +64,7 @@ def test_real_layer_sizes_under_three_cuts(model, dtype, tol):
     from ferrox_b200 import Engine
 
     folder, prompts, want = model
-    eng = Engine.from_folder(folder, dtype=dtype, page_size=64, n_pages=8, max_slots=3)
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=64, n_pages=10, max_slots=4)
     first = ru.run_whole(eng, prompts)
     check(first, want, tol, dtype == "bfloat16")
     for _ in range(3):   # the same steps again give the same bits (fixed order of sums, no race between kernels)
@@ -65,6 +72,8 @@ def test_real_layer_sizes_under_three_cuts(model, dtype, tol):
         assert all(torch.equal(first[r], again[r]) for r in prompts)
     check(ru.run_tail_decode(eng, prompts, tail=24), want, tol, dtype == "bfloat16")
     check(ru.run_mixed(eng, prompts, seed=2, max_live=2, max_portion=40), want, tol, dtype == "bfloat16")
+    # requests of 150, 70, 200 and 9 tokens decoding together (replayed graphs; key ranges of unequal length, some empty)
+    check(ru.run_decode_together(eng, prompts, tail=8), want, tol, dtype == "bfloat16")
     assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())
 
 
