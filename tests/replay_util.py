@@ -117,8 +117,8 @@ def run_decode_together(eng, prompts, tail=8):
     rest = {}
     for rid, toks in prompts.items():
         head = max(1, len(toks) - tail)
-        c.step({rid: toks[:head]})
         rest[rid] = list(toks[head:])
+        c.step({rid: toks[:head]}, end=[] if rest[rid] else [rid])
     while any(rest.values()):
         portions = {rid: [r.pop(0)] for rid, r in rest.items() if r}
         c.step(portions, end=[rid for rid in portions if not rest[rid]])
