@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape a2.7b|a14b]
 
 Default workload: the layer sizes of the Qwen1.5-MoE-A2.7B shape (24 layers, hidden
 2048, 16 heads of 128, 60 experts top-4 of width 1408, shared expert 5632, vocab
@@ -34,7 +34,12 @@ A27B = dict(
     norm_topk_prob=False, qkv_bias=True, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
     use_sliding_window=False, tie_word_embeddings=False, max_position_embeddings=4096,
 )
-FULL_LAYERS = 24
+# The larger shape, on request (--shape a14b): Qwen2-57B-A14B, 114 GB of bfloat16 weights.
+A14B = dict(
+    A27B, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, num_experts=64,
+    num_experts_per_tok=8, moe_intermediate_size=2560, shared_expert_intermediate_size=20480, intermediate_size=20480,
+)
+SHAPES = {"a2.7b": ("Qwen1.5-MoE-A2.7B shape", A27B), "a14b": ("Qwen2-57B-A14B shape", A14B)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -152,7 +157,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes (named in config)")
+    ap.add_argument("--shape", default="a2.7b", choices=sorted(SHAPES), help="layer sizes (default: the headline shape)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers of the same sizes (named in config); 0 = all")
     ap.add_argument("--points", default="1,64", help="further decode batch sizes for 'points' ('' = none)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=64)
@@ -171,7 +177,10 @@ def main() -> int:
     from ferrox_b200.kernels import ops
 
     torch.manual_seed(0)
-    cfg = dict(A27B, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
+    args.layers = args.layers or full_layers
+    cfg = dict(shape, num_hidden_layers=args.layers)
     point_batches = [int(b) for b in args.points.split(",") if b.strip()]
     max_batch = max([args.batch] + point_batches)
     total_new = args.warmup + args.steps + 2
@@ -287,14 +296,17 @@ def main() -> int:
                "steps_issued_ahead": stats["ahead_steps"]}
 
     line = {
-        "metric": "decode tokens/s at batch %d (Qwen1.5-MoE-A2.7B shape, context %d)" % (args.batch, CONTEXT),
+        "metric": "decode tokens/s at batch %d (%s, context %d)" % (args.batch, shape_name, CONTEXT),
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random N(0,0.02) weights drawn on the device, uniform random token ids",
         "config": {
-            "model": "Qwen1.5-MoE-A2.7B shape", "layers": args.layers, "layers_full": FULL_LAYERS, "hidden": 2048,
-            "heads": 16, "kv_heads": 16, "head_dim": 128, "experts": 60, "top_k": 4, "moe_intermediate": 1408,
-            "shared_intermediate": 5632, "vocab": 151936, "global_batch": args.batch, "seq_len": CONTEXT,
+            "model": shape_name, "layers": args.layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "experts": cfg["num_experts"], "top_k": cfg["num_experts_per_tok"],
+            "moe_intermediate": cfg["moe_intermediate_size"],
+            "shared_intermediate": cfg["shared_expert_intermediate_size"], "vocab": cfg["vocab_size"],
+            "global_batch": args.batch, "seq_len": CONTEXT,
             "prompt_tokens": PREFILL_TOKENS, "context_at_timing": ctx_mid, "page_size": ps, "parallelism": "single GPU",
             "l2": "weights and cache exceed L2, no flush", "load_s": round(load_s, 1),
         },
