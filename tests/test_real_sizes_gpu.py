@@ -77,6 +77,26 @@ def test_real_layer_sizes_under_three_cuts(model, dtype, tol):
     assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())
 
 
+def test_two_layers_one_windowed_served_in_mixed_batches_fp32(tmp_path):
+    """The widths of Qwen1.5-MoE-A2.7B in true 32-bit, two layers of which the second has a sliding window (two groups
+    of pages with different needs), prompts of random lengths served as portions beside decoded tokens with pages
+    used again: every logit against the plain implementation."""
+    from ferrox_b200 import Engine, write_random_model
+
+    cfg = dict(A27B_LAYER, num_hidden_layers=2, use_sliding_window=True, sliding_window=96, max_window_layers=1,
+               vocab_size=1500)
+    folder = write_random_model(str(tmp_path / "two"), cfg, seed=9, std=0.02, norm_init="around_one")
+    rng = random.Random(4)
+    lens = [64, 1, 300] + [rng.randint(2, 300) for _ in range(4)]
+    prompts = {f"r{i}": [rng.randrange(cfg["vocab_size"]) for _ in range(n)] for i, n in enumerate(lens)}
+    want = ru.Expected(folder, prompts)
+    eng = Engine.from_folder(folder, dtype="float32", page_size=64, n_pages=3 * 5, max_slots=3)
+    check(ru.run_mixed(eng, prompts, seed=6, max_live=3, max_portion=50), want, 3e-5, False)
+    check(ru.run_decode_together(eng, dict(list(prompts.items())[2:5]), tail=20),
+          {rid: want[rid] for rid in list(prompts)[2:5]}, 3e-5, False)
+    assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())
+
+
 def test_long_prompt_cut_three_ways_agrees_with_itself():
     """6,000 tokens at the real layer sizes, too long for the plain implementation: the logits at the last positions
     must not depend on whether the prompt came whole (pairs of SMs, 256-query attention tiles, 128-row expert tiles),
