@@ -335,7 +335,6 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
     return out
 
 
-DECODE_BLOCK_SLOTS = 148 * 3      # blocks of the decode attention kernel that run at the same time (cp.async kernel)
 DECODE_BLOCK_OVERHEAD = 128       # start and end of a block, in keys' worth of a block's time
 DECODE_MERGE_COST = 256           # the merge of the key ranges, in the same unit
 DECODE_BLOCKS_TO_SATURATE = 160   # blocks streaming at the same time that draw the machine's whole bandwidth
