@@ -86,6 +86,9 @@ int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void
                         float scale, int split_len, int n_splits, int* status, int* counters, void* stream);
 
 int fx_argmax(const float* logits, long ld, int n_rows, int vocab, int* out, void* stream);
+int fx_sample_or(const float* scores, long lds, float* work, long ld, int n_rows, int vocab, const float* temperature,
+                 const int* top_k, const float* top_p, const float* draw, const int* use_sample, const int* instead,
+                 int* out, void* stream);
 int fx_repetition_penalty(float* work, long ld, int n_rows, int vocab, const int* history, const int* hist_offsets,
                           const float* penalty, void* stream);
 int fx_sample(float* work, long ld, int n_rows, int vocab, const float* temperature, const int* top_k,

@@ -96,23 +96,34 @@ __device__ __forceinline__ void mass_at_least(const float* p, int vocab, unsigne
 }
 
 // work: scores in, probabilities out (in place).  temperature > 0.
+// With `scores` the scores are read from there and `work` is written only.  With `use_sample` and `instead` a row
+// whose flag is 0, or whose candidates were all filtered away, gets instead[r] (the arg max of its untouched scores):
+// the whole choice of a step in one launch, for steps replayed from a CUDA graph.
 __global__ void __launch_bounds__(NT) sample_kernel(float* __restrict__ work, long ld, int vocab,
                                                     const float* __restrict__ temperature,
                                                     const int* __restrict__ top_k, const float* __restrict__ top_p,
-                                                    const float* __restrict__ draw, int* __restrict__ out)
+                                                    const float* __restrict__ draw, int* __restrict__ out,
+                                                    const float* __restrict__ scores, long lds,
+                                                    const int* __restrict__ use_sample, const int* __restrict__ instead)
 {
     __shared__ float scratch[33];
     __shared__ float chunk_sum[NT];
     __shared__ int chosen;
+    fx_pdl_wait();
     const int r = blockIdx.x;
+    if (use_sample && !use_sample[r]) {
+        if (threadIdx.x == 0) out[r] = instead[r];
+        return;
+    }
     float* p = work + (long)r * ld;
+    const float* src = scores ? scores + (long)r * lds : p;
     const float inv_t = 1.0f / temperature[r];
 
     float mx = -INFINITY;
-    for (int i = threadIdx.x; i < vocab; i += NT) mx = fmaxf(mx, p[i] * inv_t);
+    for (int i = threadIdx.x; i < vocab; i += NT) mx = fmaxf(mx, src[i] * inv_t);
     mx = block_max(mx, scratch);
     float sum = 0.f;
-    for (int i = threadIdx.x; i < vocab; i += NT) { const float e = expf(p[i] * inv_t - mx); p[i] = e; sum += e; }
+    for (int i = threadIdx.x; i < vocab; i += NT) { const float e = expf(src[i] * inv_t - mx); p[i] = e; sum += e; }
     sum = block_sum(sum, scratch);
     for (int i = threadIdx.x; i < vocab; i += NT) p[i] = sum > 0.f ? p[i] / sum : 1.0f / (float)vocab;
     __syncthreads();
@@ -184,7 +195,7 @@ __global__ void __launch_bounds__(NT) sample_kernel(float* __restrict__ work, lo
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) out[r] = chosen;
+    if (threadIdx.x == 0) out[r] = (instead && chosen < 0) ? instead[r] : chosen;
 }
 
 }  // namespace
@@ -209,6 +220,21 @@ extern "C" int fx_sample(float* work, long ld, int n_rows, int vocab, const floa
                          const float* top_p, const float* draw, int* out, void* stream)
 {
     if (n_rows <= 0) return FX_OK;
-    sample_kernel<<<n_rows, NT, 0, (cudaStream_t)stream>>>(work, ld, vocab, temperature, top_k, top_p, draw, out);
+    sample_kernel<<<n_rows, NT, 0, (cudaStream_t)stream>>>(work, ld, vocab, temperature, top_k, top_p, draw, out,
+                                                           nullptr, 0, nullptr, nullptr);
+    return fx_launch_status();
+}
+
+// The choice of a whole step: row r gets a sample of scores[r] (temperature, top-k, top-p, draw as in fx_sample) if
+// use_sample[r], else instead[r]; also instead[r] when every candidate of the row was filtered away.  `scores` is
+// left untouched, `work` ([n_rows, vocab] floats) is scratch.
+extern "C" int fx_sample_or(const float* scores, long lds, float* work, long ld, int n_rows, int vocab,
+                            const float* temperature, const int* top_k, const float* top_p, const float* draw,
+                            const int* use_sample, const int* instead, int* out, void* stream)
+{
+    if (n_rows <= 0) return FX_OK;
+    if (!scores || !use_sample || !instead) return FX_ERR_SIZE;
+    fx_launch_pdl(sample_kernel, n_rows, NT, 0, (cudaStream_t)stream, work, ld, vocab, temperature, top_k, top_p, draw, out,
+                  scores, lds, use_sample, instead);
     return fx_launch_status();
 }

@@ -109,14 +109,15 @@ class Engine:
         """Run the entries' tokens as one batch; [wanted, vocab] float32 logits."""
         return _step(self.model, self.cache, entries, check=check, graphs=self.graphs)
 
-    def decode_ahead(self, slots, tokens):
-        """Greedy decoding of these requests issued one step ahead of the host (see
-        :class:`~ferrox_b200.engine.step.DecodeAhead`), or None while no graph of this batch size exists."""
+    def decode_ahead(self, slots, tokens, sampling=None):
+        """Decoding of these requests issued one step ahead of the host (see
+        :class:`~ferrox_b200.engine.step.DecodeAhead`), or None while no graph of this batch size exists.  Greedy, or
+        with ``sampling`` (per request its SamplingParams and generator) sampled inside the graph."""
         from .step import DecodeAhead
 
         if not DecodeAhead.ready(self.graphs, len(slots)):
             return None
-        return DecodeAhead(self.model, self.cache, self.graphs, slots, tokens)
+        return DecodeAhead(self.model, self.cache, self.graphs, slots, tokens, sampling)
 
     # ---- generation -------------------------------------------------------------
     def generate(self, prompts, max_new_tokens=128, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0,

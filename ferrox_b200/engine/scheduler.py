@@ -286,8 +286,8 @@ class Scheduler:
 
     # ---- decoding issued ahead of the host ----------------------------------------------
     def _decode_ahead(self) -> bool:
-        """While nothing waits, every running request is decoding greedily and a CUDA graph of this batch size
-        exists, steps are issued one ahead: the host reads a step's tokens while the next step runs.  Only
+        """While nothing waits, every running request is decoding (greedily, or sampling without a repetition
+        penalty) and a CUDA graph of this batch size exists, steps are issued one ahead: the host reads a step's tokens while the next step runs.  Only
         lengths decide how many steps may be issued (no request reaches its limit inside the run); an end-of-
         sequence token shows one step late, the step issued meanwhile for that request is thrown away.  Pages
         that run out end the run before the step that lacks them: the ordinary step then decides.
@@ -297,13 +297,18 @@ class Scheduler:
             return False
         reqs = sorted(self.running, key=lambda q: q.admitted_at)
         for r in reqs:
-            if r.pending != 1 or not r.generated or not (r.params.greedy and r.params.repetition_penalty == 1.0):
+            if r.pending != 1 or not r.generated or r.params.repetition_penalty != 1.0:
                 return False
         ctx = self.cache.max_positions
         n_safe = min(min(r.max_new - len(r.generated), ctx - len(r.prompt) - len(r.generated)) for r in reqs)
         if n_safe < 2:
             return False
-        run = issue([r.slot for r in reqs], [r.generated[-1] for r in reqs])
+        if all(r.params.greedy for r in reqs):
+            run = issue([r.slot for r in reqs], [r.generated[-1] for r in reqs])
+        else:
+            # (a generator's draws go with the steps as they are issued: a step issued for a request that then turns
+            # out to have ended costs that request a draw it no longer needs)
+            run = issue([r.slot for r in reqs], [r.generated[-1] for r in reqs], [(r.params, r.rng) for r in reqs])
         if run is None:
             return False
         from .step import OutOfPages

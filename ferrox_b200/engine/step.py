@@ -105,6 +105,7 @@ class GraphedDecode:
         self.max_batch = max_batch
         self.seen = set()
         self.graphs = {}
+        self.sampled = {}   # graphs that end with the choice of the next tokens by sampling, for steps issued ahead
         self.kernels_per_replay = {}
 
     def eligible(self, entries) -> bool:
@@ -132,12 +133,14 @@ class GraphedDecode:
         ops.count_launches(self.kernels_per_replay[B])
         return g["logits"]
 
-    def _capture(self, B, entries, status):
+    def _capture(self, B, entries, status, sampled: bool = False):
+        """``sampled``: the graph ends with temperature / top-k / top-p sampling instead of the arg max alone; its
+        static buffer holds five more runs of B values (top_k, sample or not, temperature, top_p, draw)."""
         import numpy as np
 
         dev = self.model.rt.device
-        n = 5 * B
-        host = torch.empty(n, dtype=torch.int32).pin_memory()
+        n = 10 * B if sampled else 5 * B
+        host = torch.zeros(n, dtype=torch.int32).pin_memory()
         arr = host.numpy()
         arr[2 * B:3 * B] = np.arange(B)  # token_seq: token b belongs to entry b
         arr[4 * B:5 * B] = np.arange(B)  # want_rows: every row
@@ -146,20 +149,31 @@ class GraphedDecode:
         buf = torch.empty(n, dtype=torch.int32, device=dev)
         buf.copy_(host)
         chosen = torch.zeros(B, dtype=torch.int32, device=dev)   # arg max of each row of the logits, for steps issued ahead
+        if sampled:
+            best = torch.zeros(B, dtype=torch.int32, device=dev)
+            work = torch.empty(B, self.model.spec.vocab_size, dtype=torch.float32, device=dev)
+            fl = buf.view(torch.float32)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(graph):
             batch = StepBatch(
                 n_tokens=B, n_seqs=B, n_want=B, token_ids=buf[:B], positions=buf[B:2 * B], token_seq=buf[2 * B:3 * B],
-                seq_slot=buf[3 * B:4 * B], want_rows=buf[4 * B:], status=status, stream=ops.stream_ptr(),
-                entries=list(entries), max_len=self.cache.max_positions, max_new=1, h2d_bytes=4 * n,
+                seq_slot=buf[3 * B:4 * B], want_rows=buf[4 * B:5 * B], status=status, stream=ops.stream_ptr(),
+                entries=list(entries), max_len=self.cache.max_positions, max_new=1, h2d_bytes=20 * B,
             )
             with ops.stream_scope(batch.stream):
                 logits = self.model.forward(batch, lambda entry: self.cache.layer_cache(entry.cache, entry.writes_cache))
-                ops.argmax(logits, chosen)
-        self.kernels_per_replay[B] = ops.launch_count() - before
-        self.graphs[B] = {
+                if sampled:
+                    ops.argmax(logits, best)
+                    ops.sample_or(logits, work, fl[7 * B:8 * B], buf[5 * B:6 * B], fl[8 * B:9 * B], fl[9 * B:10 * B],
+                                  buf[6 * B:7 * B], best, chosen)
+                else:
+                    ops.argmax(logits, chosen)
+        self.kernels_per_replay[(B, sampled)] = ops.launch_count() - before
+        if not sampled:
+            self.kernels_per_replay[B] = self.kernels_per_replay[(B, False)]
+        (self.sampled if sampled else self.graphs)[B] = {
             "graph": graph, "host": host, "dev": buf, "logits": logits, "event": torch.cuda.Event(), "chosen": chosen,
             # steps issued ahead: two pinned buffers each way, used in turn
             "ahead_in": [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(2)],
@@ -167,20 +181,45 @@ class GraphedDecode:
             "ahead_out": [torch.empty(B, dtype=torch.int32).pin_memory() for _ in range(2)],
             "ahead_out_done": [torch.cuda.Event() for _ in range(2)],
         }
-        for h in self.graphs[B]["ahead_in"]:
+        for h in (self.sampled if sampled else self.graphs)[B]["ahead_in"]:
             h.copy_(host)
 
+    def capture_sampled(self, B, slots, status) -> None:
+        """The sampling graph of batch size B, captured when decoding ahead first asks for it (the plain graph of
+        this size exists by then, so every kernel of the model has run before)."""
+        if B in self.sampled:
+            return
+        entries = []
+        for s in slots:
+            e = StepEntry(s, [0], want=[0])
+            e.start = self.cache.seq_len[s]
+            entries.append(e)
+        dev = self.model.rt.device
+        # the sampling kernel once outside a capture
+        z = torch.zeros(1, 4, device=dev)
+        one_i, one_f = torch.ones(1, dtype=torch.int32, device=dev), torch.ones(1, device=dev)
+        ops.sample_or(z, z.clone(), one_f, one_i, one_f, one_f * 0.5, one_i, one_i, one_i.clone())
+        self._capture(B, entries, status, sampled=True)
+
     # ---- steps issued ahead of the host ------------------------------------------------
-    def replay_ahead(self, B, starts, slots, tokens, turn: int) -> None:
+    def replay_ahead(self, B, starts, slots, tokens, turn: int, sampling=None) -> None:
         """Replay the graph of size B without waiting for anything.  ``tokens`` None: the step's tokens are the
-        ones the previous replay of this size chose (arg max), which never left the device.  The chosen tokens
-        of this replay travel to pinned memory behind it; :meth:`chosen_tokens` waits for them."""
-        g = self.graphs[B]
+        ones the previous replay of this size chose, which never left the device.  The chosen tokens of this
+        replay travel to pinned memory behind it; :meth:`chosen_tokens` waits for them.  ``sampling``: the
+        step's (top_k, sample or not, temperature, top_p, draw), each a list of B; the sampling graph then."""
+        g = self.graphs[B] if sampling is None else self.sampled[B]
         g["ahead_in_done"][turn].synchronize()
         host = g["ahead_in"][turn]
         arr = host.numpy()
         arr[B:2 * B] = starts
         arr[3 * B:4 * B] = slots
+        if sampling is not None:
+            import numpy as np
+
+            top_k, use, temp, top_p, draw = sampling
+            arr[5 * B:6 * B] = top_k
+            arr[6 * B:7 * B] = use
+            arr[7 * B:10 * B].view(np.float32)[:] = list(temp) + list(top_p) + list(draw)
         if tokens is not None:
             arr[:B] = tokens
             g["dev"].copy_(host, non_blocking=True)
@@ -189,27 +228,38 @@ class GraphedDecode:
             g["dev"][:B].copy_(g["chosen"], non_blocking=True)
         g["ahead_in_done"][turn].record()
         g["graph"].replay()
-        ops.count_launches(self.kernels_per_replay[B])
+        ops.count_launches(self.kernels_per_replay[(B, sampling is not None)])
         g["ahead_out"][turn].copy_(g["chosen"], non_blocking=True)
         g["ahead_out_done"][turn].record()
 
-    def chosen_tokens(self, B, turn: int):
-        g = self.graphs[B]
+    def chosen_tokens(self, B, turn: int, sampled: bool = False):
+        g = self.sampled[B] if sampled else self.graphs[B]
         g["ahead_out_done"][turn].synchronize()
         return g["ahead_out"][turn].tolist()
 
 
 class DecodeAhead:
-    """Greedy decode steps of a fixed set of requests, issued one step ahead of the host: step k+1 is on the
-    stream before the host has read what step k chose.  The chosen token of a request is fed to its next step
-    on the device; the host reads it one step later, from pinned memory.  A step maps its pages and advances
-    the requests' lengths when it is issued (both depend on counts only, not on the tokens)."""
+    """Decode steps of a fixed set of requests, issued one step ahead of the host: step k+1 is on the stream
+    before the host has read what step k chose.  The chosen token of a request is fed to its next step on the
+    device; the host reads it one step later, from pinned memory.  A step maps its pages and advances the
+    requests' lengths when it is issued (both depend on counts only, not on the tokens).
 
-    def __init__(self, model, cache, graphs, slots, tokens):
+    Greedy by default.  ``sampling``: per request its (SamplingParams, generator); the choice is then made inside
+    the graph by the sampling kernel (no repetition penalty: that needs the tokens on the host).  A request's
+    uniform draws come from its own generator, one per step in which it samples, as without the graph: they do
+    not depend on the tokens, so the host can send them with the step."""
+
+    def __init__(self, model, cache, graphs, slots, tokens, sampling=None):
         self.model, self.cache, self.graphs = model, cache, graphs
         self.slots, self.first_tokens = list(slots), list(tokens)
         self.B = len(self.slots)
         self.issued = self.collected = 0
+        self.sampling = None
+        if sampling is not None and any(not p.greedy for p, _ in sampling):
+            if any(p.repetition_penalty != 1.0 for p, _ in sampling):
+                raise ValueError("steps issued ahead cannot apply a repetition penalty")
+            self.sampling = list(sampling)
+            graphs.capture_sampled(self.B, self.slots, _status(model.rt.device))
 
     @staticmethod
     def ready(graphs, n: int) -> bool:
@@ -232,15 +282,22 @@ class DecodeAhead:
             assert ok
         cache.sync_tables()
         first = self.issued == 0
-        self.graphs.replay_ahead(self.B, starts, self.slots, self.first_tokens if first else None, self.issued & 1)
-        last_h2d_bytes = (20 if first else 16) * self.B
+        step_sampling = None
+        if self.sampling is not None:
+            ps = [p for p, _ in self.sampling]
+            step_sampling = ([p.top_k for p in ps], [0 if p.greedy else 1 for p in ps],
+                             [1.0 if p.greedy else p.temperature for p in ps], [p.top_p for p in ps],
+                             [0.0 if p.greedy else g.next_f32() for p, g in self.sampling])
+        self.graphs.replay_ahead(self.B, starts, self.slots, self.first_tokens if first else None, self.issued & 1,
+                                 step_sampling)
+        last_h2d_bytes = ((20 if first else 16) + (20 if step_sampling else 0)) * self.B
         for s, st in zip(self.slots, starts):
             cache.commit(s, st + 1)
         self.issued += 1
 
     def collect(self):
         """The tokens chosen by the oldest step not read yet (waits for it)."""
-        toks = self.graphs.chosen_tokens(self.B, self.collected & 1)
+        toks = self.graphs.chosen_tokens(self.B, self.collected & 1, self.sampling is not None)
         self.collected += 1
         return toks
 

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
     "fx_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "fx_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
+    "fx_sample_or": [_P, _L, _P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
 }
 
 _fn = {}
@@ -559,6 +560,16 @@ def repetition_penalty(work, history, hist_offsets, penalty, stream=None):
     n, V = work.shape
     call("fx_repetition_penalty", _ptr(work), _rows(work), n, V, _ptr(history), _ptr(hist_offsets), _ptr(penalty),
          stream if stream is not None else stream_ptr())
+
+
+def sample_or(scores, work, temperature, top_k, top_p, draw, use_sample, instead, out, stream=None):
+    """Row r of ``out``: a sample of ``scores[r]`` as :func:`sample` draws it if ``use_sample[r]``, else ``instead[r]``
+    (also when every candidate was filtered away).  ``scores`` stay untouched; ``work`` is scratch of the same shape."""
+    n, V = scores.shape
+    call("fx_sample_or", _ptr(scores), _rows(scores), _ptr(work), _rows(work), n, V, _ptr(temperature), _ptr(top_k),
+         _ptr(top_p), _ptr(draw), _ptr(use_sample), _ptr(instead), _ptr(out),
+         stream if stream is not None else stream_ptr())
+    return out
 
 
 def sample(work, temperature, top_k, top_p, draw, out, stream=None):

@@ -79,6 +79,34 @@ def test_decoding_issued_ahead_gives_the_same_tokens(folders):
     assert [len(o) for o in outs] == [24, 24, 24] and stats["ahead_steps"] >= 10
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sampled_decoding_issued_ahead_gives_the_same_tokens(folders, dtype):
+    """Temperature, top-k and top-p sampling chosen inside the replayed graph, one step ahead of the host: the same
+    tokens as the engine without graphs draws with the same seeds (the same kernels give the same logits bit for
+    bit; each request's uniform draws come from its own generator in both)."""
+    prompts = [[5, 9, 200, 31], [7, 8], list(range(40, 60))]
+    for kw in (dict(temperature=0.9), dict(temperature=1.3, top_k=7), dict(temperature=0.8, top_p=0.6),
+               dict(temperature=1.0, top_k=12, top_p=0.9)):
+        plain_eng = engine(folders["B"], dtype, cuda_graphs=False)
+        want, st0 = plain_eng.generate(prompts, max_new_tokens=30, seed=11, return_stats=True, **kw)
+        assert st0["ahead_steps"] == 0
+        eng = engine(folders["B"], dtype)
+        got, st = eng.generate(prompts, max_new_tokens=30, seed=11, return_stats=True, **kw)
+        assert got == want and st["ahead_steps"] >= 10, kw
+        again = eng.generate(prompts, max_new_tokens=30, seed=11, **kw)        # the sampling graph a second time
+        other = eng.generate(prompts, max_new_tokens=30, seed=12, **kw)
+        assert again == want and other != want
+        eng.cache.check_invariants()
+    # an end-of-sequence token that shows one step late; a repetition penalty keeps the ordinary path
+    eng = engine(folders["B"], dtype)
+    free = eng.generate(prompts, max_new_tokens=30, seed=3, temperature=1.1, top_k=20)
+    eos = free[2][12]
+    want = [f[:f.index(eos)] if eos in f else f for f in free]
+    assert eng.generate(prompts, max_new_tokens=30, seed=3, temperature=1.1, top_k=20, eos_token_id=eos) == want
+    outs, st = eng.generate(prompts, max_new_tokens=12, seed=3, temperature=1.1, repetition_penalty=1.2, return_stats=True)
+    assert st["ahead_steps"] == 0 and [len(o) for o in outs] == [12, 12, 12]
+
+
 def test_long_decoding_stays_on_the_plain_implementation(folders):
     """One token at a time up to the context's end (pages and, for B, the window roll over many times)."""
     for name in ("A", "B"):

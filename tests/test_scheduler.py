@@ -226,10 +226,11 @@ class FakeAheadEngine(FakeEngine):
             self.sizes_seen[len(entries)] = self.sizes_seen.get(len(entries), 0) + 1
         return super().step(entries)
 
-    def decode_ahead(self, slots, tokens):
+    def decode_ahead(self, slots, tokens, sampling=None):
         if self.sizes_seen.get(len(slots), 0) < self.ready_after:   # "no graph of this size yet"
             return None
         self.ahead_runs += 1
+        self.sampling_seen = sampling
         return FakeAheadRun(self, slots, tokens)
 
 
@@ -278,10 +279,26 @@ def test_pages_run_out_inside_a_run_issued_ahead():
     eng.cache.check_invariants()
 
 
-def test_sampled_requests_are_never_issued_ahead():
+def test_requests_with_a_repetition_penalty_are_never_issued_ahead():
     eng = FakeAheadEngine(n_pages=32, page_size=4, max_slots=2, ready_after=0)
     s = make_greedy(eng)
-    s.add_request([1, 2, 3], 8, SamplingParams(temperature=0.7, seed=1))
+    s.add_request([1, 2, 3], 8, SamplingParams(temperature=0.7, seed=1, repetition_penalty=1.3))
     s.add_request([4, 5], 8)
     s.run()
     assert eng.ahead_runs == 0
+
+
+def test_sampled_requests_are_issued_ahead_with_their_own_generators():
+    """Sampling without a repetition penalty needs nothing from the host but a uniform draw a step, which does not
+    depend on the tokens: such requests decode ahead too, and the run gets each request's parameters and generator."""
+    eng = FakeAheadEngine(n_pages=32, page_size=4, max_slots=2, ready_after=0)
+    s = make_greedy(eng)
+    a = s.add_request([1, 2, 3], 8, SamplingParams(temperature=0.7, top_k=5, seed=1))
+    b = s.add_request([4, 5], 8)
+    s.run()
+    assert eng.ahead_runs >= 1
+    (pa, ga), (pb, gb) = eng.sampling_seen
+    assert pa.temperature == 0.7 and pa.top_k == 5 and pb.greedy
+    assert ga is not gb and ga.state != gb.state      # one generator per request, seeded by the request
+    assert len(s.result(a)) == 8 and len(s.result(b)) == 8
+    eng.cache.check_invariants()
