@@ -109,6 +109,11 @@ __global__ void __launch_bounds__(NT) sample_kernel(float* __restrict__ work, lo
     __shared__ float scratch[33];
     __shared__ float chunk_sum[NT];
     __shared__ int chosen;
+    __shared__ int digit_count[256], digit_found, digit_above;
+    __shared__ int walk_chunk, walk_last;
+    __shared__ float walk_run, walk_target, group_sum[32];
+    constexpr int LIST = 8;                      // probabilities a thread keeps after a top-k
+    __shared__ float kept_list[NT][LIST];
     fx_pdl_wait();
     const int r = blockIdx.x;
     if (use_sample && !use_sample[r]) {
@@ -132,27 +137,72 @@ __global__ void __launch_bounds__(NT) sample_kernel(float* __restrict__ work, lo
     unsigned keep_bits = 0u;
     const int k = top_k[r];
     if (k > 0 && k < vocab) {
-        // largest pattern b with count(p >= b) >= k, by bisection over the 31 value bits
-        unsigned lo = 0u, hi = 0x7f800000u;  // invariant: count(lo) >= k, count(hi) < k (no p is +inf)
-        while (hi - lo > 1u) {
-            const unsigned mid = lo + ((hi - lo) >> 1);
-            float mass, cnt;
-            mass_at_least(p, vocab, mid, scratch, &mass, &cnt);
-            if (cnt >= (float)k) lo = mid; else hi = mid;
+        // The pattern of the k-th largest probability = the largest pattern b with count(p >= b) >= k, found digit
+        // by digit from the top (8, 8, 8 and 7 bits): a histogram of the digit over the probabilities that share the
+        // digits found so far, then the digit in which the k-th largest lies.  Integer counts: the same answer in
+        // every run.  Fewer than k probabilities above zero: nothing is dropped.
+        unsigned prefix = 0u, prefix_mask = 0u;
+        int remaining = k;
+        for (int level = 0; level < 4 && remaining > 0; ++level) {
+            const int shift = level == 0 ? 23 : (level == 1 ? 15 : (level == 2 ? 7 : 0));
+            const unsigned digit_mask = level == 3 ? 0x7fu : 0xffu;
+            for (int i = threadIdx.x; i < 256; i += NT) digit_count[i] = 0;
+            __syncthreads();
+            for (int i = threadIdx.x; i < vocab; i += NT) {
+                const unsigned b = __float_as_uint(p[i]);
+                if (b != 0u && (b & prefix_mask) == prefix) atomicAdd(&digit_count[(b >> shift) & digit_mask], 1);
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int above = 0, d = (int)digit_mask;
+                for (; d >= 0; --d) { if (above + digit_count[d] >= remaining) break; above += digit_count[d]; }
+                digit_found = d;           // -1: fewer than `remaining` candidates in all
+                digit_above = above;
+            }
+            __syncthreads();
+            if (digit_found < 0) { prefix = 0u; remaining = 0; break; }
+            prefix |= (unsigned)digit_found << shift;
+            prefix_mask |= digit_mask << shift;
+            remaining -= digit_above;
         }
-        keep_bits = lo;
+        keep_bits = prefix;
     }
     const float tp = top_p[r];
     if (tp < 1.0f) {
         // largest pattern b >= keep_bits with mass(p >= b) >= top_p; if even the whole
         // kept mass stays below top_p nothing more is dropped.
+        // After a top-k the few probabilities still kept are copied to shared memory, every thread its own (those it
+        // meets in the loops above and below, in the same order), and the bisection sums those: the same sums as over
+        // the whole row, bit for bit, without reading the row 31 times.
+        int mine = 0;
+        bool listed = false;
+        if (keep_bits != 0u) {
+            int overflow = 0;
+            for (int i = threadIdx.x; i < vocab; i += NT) {
+                const float v = p[i];
+                if (__float_as_uint(v) >= keep_bits && v > 0.f) {
+                    if (mine < LIST) kept_list[threadIdx.x][mine++] = v; else overflow = 1;
+                }
+            }
+            listed = !__syncthreads_or(overflow);
+        }
+        auto mass_of = [&](unsigned bits, float* mass, float* cnt) {
+            if (!listed) { mass_at_least(p, vocab, bits, scratch, mass, cnt); return; }
+            float s2 = 0.f, c2 = 0.f;
+            for (int j = 0; j < mine; ++j) {
+                const float v = kept_list[threadIdx.x][j];
+                if (__float_as_uint(v) >= bits) { s2 += v; c2 += 1.f; }
+            }
+            *mass = block_sum(s2, scratch);
+            *cnt = block_sum(c2, scratch);
+        };
         float mass, cnt;
-        mass_at_least(p, vocab, keep_bits, scratch, &mass, &cnt);
+        mass_of(keep_bits, &mass, &cnt);
         if (mass >= tp) {
             unsigned lo = keep_bits, hi = 0x7f800000u;
             while (hi - lo > 1u) {
                 const unsigned mid = lo + ((hi - lo) >> 1);
-                mass_at_least(p, vocab, mid, scratch, &mass, &cnt);
+                mass_of(mid, &mass, &cnt);
                 if (mass >= tp) lo = mid; else hi = mid;
             }
             keep_bits = lo;
@@ -167,31 +217,57 @@ __global__ void __launch_bounds__(NT) sample_kernel(float* __restrict__ work, lo
     chunk_sum[threadIdx.x] = local;
     if (threadIdx.x == 0) chosen = -1;
     __syncthreads();
+    // sums of 32 chunks each (32 threads side by side), then one thread: the group, then the chunk inside it
+    static_assert(NT == 32 * 32, "two levels of 32");
+    if (threadIdx.x < 32) {
+        float g = 0.f;
+        for (int i = 0; i < 32; ++i) g += chunk_sum[threadIdx.x * 32 + i];
+        group_sum[threadIdx.x] = g;
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         float total = 0.f;
-        for (int i = 0; i < NT; ++i) total += chunk_sum[i];
+        for (int i = 0; i < 32; ++i) total += group_sum[i];
         if (total <= 0.f) {
             chosen = -2;  // degenerate filters: the caller falls back to argmax of the logits
         } else {
             const float target = draw[r] * total;
-            float run = 0.f; int c = NT - 1;
-            for (int i = 0; i < NT; ++i) { if (target < run + chunk_sum[i]) { c = i; break; } run += chunk_sum[i]; }
-            // walk the chunk; if rounding leaves the draw above the last sum, the last kept token stands
-            int pick = -1, last = -1;
-            for (int cc = c; cc < NT && pick < 0; ++cc) {
-                const int b0 = cc * per, b1 = min(vocab, b0 + per);
+            float run = 0.f; int g = 31;
+            for (int i = 0; i < 32; ++i) { if (target < run + group_sum[i]) { g = i; break; } run += group_sum[i]; }
+            int c = g * 32 + 31;
+            for (int i = g * 32; i < g * 32 + 32; ++i) { if (target < run + chunk_sum[i]) { c = i; break; } run += chunk_sum[i]; }
+            walk_chunk = c; walk_run = run; walk_target = target; walk_last = -1;
+        }
+    }
+    __syncthreads();
+    if (chosen != -2) {
+        // Walk the chunk in index order; if rounding leaves the draw above the last sum, the last kept token stands.
+        // All threads bring the chunk to shared memory (one thread reading it element by element from global
+        // memory takes ten times as long as the rest of the kernel), one thread walks it.
+        float* stage = &kept_list[0][0];
+        for (int cc = walk_chunk; cc < NT; ++cc) {
+            const int b0 = cc * per, b1 = min(vocab, b0 + per);
+            const bool staged = per <= NT * LIST;
+            if (staged) for (int i = b0 + threadIdx.x; i < b1; i += NT) stage[i - b0] = p[i];
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float run = walk_run;
+                int last = walk_last;
                 for (int i = b0; i < b1; ++i) {
-                    const float v = p[i];
+                    const float v = staged ? stage[i - b0] : p[i];
                     if (!(__float_as_uint(v) >= keep_bits && v > 0.f)) continue;
                     last = i; run += v;
-                    if (target < run) { pick = i; break; }
+                    if (walk_target < run) { chosen = i; break; }
                 }
+                walk_run = run; walk_last = last;
             }
-            if (pick < 0) {
-                if (last < 0) for (int i = vocab - 1; i >= 0; --i) { const float v = p[i]; if (__float_as_uint(v) >= keep_bits && v > 0.f) { last = i; break; } }
-                pick = last < 0 ? 0 : last;
-            }
-            chosen = pick;
+            __syncthreads();
+            if (chosen >= 0) break;
+        }
+        if (threadIdx.x == 0 && chosen < 0) {
+            int last = walk_last;
+            if (last < 0) for (int i = vocab - 1; i >= 0; --i) { const float v = p[i]; if (__float_as_uint(v) >= keep_bits && v > 0.f) { last = i; break; } }
+            chosen = last < 0 ? 0 : last;
         }
     }
     __syncthreads();
