@@ -21,7 +21,6 @@ from ..weights.loader import TensorDecl
 from .base import FeedForward, register_part
 from .mlp import pack_gate_up
 
-# Up to this many tokens the shared expert runs on a second stream beside the routed experts.
 # From this many tokens on the routed experts go through the tcgen05 kernel with swapped roles (measured).
 SWAP_MIN_TOKENS = 8
 
@@ -41,7 +40,6 @@ def expert_tile_tokens(T: int, K: int, E: int):
     return None
 
 
-OVERLAP_SHARED_MAX_TOKENS = 64   # measured: 3 to 10 % of a decode step at 8 to 64 tokens
 
 
 class SoftmaxTopkMoe(FeedForward):
@@ -116,10 +114,12 @@ class SoftmaxTopkMoe(FeedForward):
         small = tiles is None and T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
         big = T > ops.SKINNY_MAX_TOKENS and tc
         n_route = self.w_route.shape[0]      # E router logits, then the shared expert's gate logit if it has one
-        # Few tokens: the shared expert's two products run on a second stream beside the routing and the routed
-        # experts (short kernels that leave most of the machine idle); both meet again at the combination.
+        # The shared expert's two products run on a second stream beside the routing and the routed experts; both
+        # meet again at the combination.  In a decode step the routed experts' kernels leave most of the machine
+        # idle; in a prompt the router's short kernels hide under the shared expert's products.  Measured on a
+        # B200: 3 to 10 % of a decode step of 8 to 64 tokens, 14 % of a prompt portion of 256 tokens, 4 % at 2,048.
         shared = None
-        overlap = self.w_shared_gu is not None and T <= OVERLAP_SHARED_MAX_TOKENS
+        overlap = self.w_shared_gu is not None
         if overlap:
             main = torch.cuda.current_stream()
             self._fork.record(main)
