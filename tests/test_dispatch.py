@@ -45,3 +45,19 @@ def test_expert_tile_tokens_by_rows_per_expert():
     assert expert_tile_tokens(200, 4, 60) == (64, 64)
     assert expert_tile_tokens(2048, 4, 60) is None
     assert expert_tile_tokens(16, 8, 10) == (64, 64)       # few experts: more rows each
+
+
+def test_decode_attention_by_tma_where_pages_and_heads_fit_its_boxes():
+    import torch
+
+    bf, f32 = torch.bfloat16, torch.float32
+    # head sizes in steps of 64 on pages of a multiple of 64 positions, bfloat16 only
+    assert ops.decode_tma_blocks_per_sm(bf, 128, 64) == 2 and ops.decode_tma_blocks_per_sm(bf, 64, 128) == 2
+    assert ops.decode_tma_blocks_per_sm(bf, 256, 64) == 1 and ops.decode_tma_blocks_per_sm(bf, 192, 64) == 1
+    for dtype, d, ps in ((f32, 128, 64), (bf, 96, 64), (bf, 128, 16), (bf, 128, 96), (bf, 320, 64), (bf, 0, 64)):
+        assert ops.decode_tma_blocks_per_sm(dtype, d, ps) == 0
+
+
+def test_routing_in_one_block_only_for_small_steps():
+    assert ops.ROUTE_SMALL_MAX_TOKENS <= 64      # the one-block kernel takes a token per warp and round
+    assert 32 * ops.ROUTE_SMALL_MAX_EXPERTS * 4 + (2 * ops.ROUTE_SMALL_MAX_EXPERTS + 1) * 4 <= 48 * 1024   # its shared memory
