@@ -57,6 +57,9 @@ int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw, long w_gro
 int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int w_rows, const void* bias, int bias_dtype, void* C,
                 int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated, int gate_up_offset, int* status,
                 void* stream);
+int fx_moe_combine_norm(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w, int top_k,
+                        const void* shared, const float* shared_gate_logit, long gate_ld, int n_tokens, int hidden,
+                        const void* norm_w, int norm_w_dtype, float eps, void* x_out, void* stream);
 int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo, int dtype, int n_rows, int width,
                    void* stream);
 int fx_route(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,

@@ -379,6 +379,68 @@ __global__ void moe_combine_vec_kernel(float* __restrict__ h, const T* __restric
     }
 }
 
+// The same combine with the RMSNorm that follows it (the next layer's first norm): one block takes a whole row,
+// keeps the new residual values in registers, sums their squares and writes the normed row beside the residual
+// stream.  Saves the norm's launch and its reading of the row.  A thread holds up to CH vectors of the row.
+template <typename T, int CH>
+__global__ void moe_combine_norm_kernel(float* __restrict__ h, const T* __restrict__ y, const int* __restrict__ inv_perm,
+                                        const float* __restrict__ topk_w, int top_k,
+                                        const T* __restrict__ shared, const float* __restrict__ shared_gate_logit,
+                                        long gate_ld, int hidden, const void* __restrict__ norm_w, int norm_w_dtype,
+                                        float eps, T* __restrict__ x_out)
+{
+    constexpr int V = Pack<T>::N;
+    __shared__ float scratch[33];
+    fx_pdl_wait();
+    const int t = blockIdx.x;
+    float g = 1.f;
+    if (shared && shared_gate_logit) g = 1.0f / (1.0f + expf(-shared_gate_logit[(long)t * gate_ld]));
+    float hv[CH][V];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * V;
+        if (i >= hidden) continue;
+        float acc[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = 0.f;
+        for (int k = 0; k < top_k; ++k) {
+            const long r = inv_perm[(long)t * top_k + k];
+            const float w = topk_w[(long)t * top_k + k];
+            float v[V];
+            Pack<T>::load(y + r * hidden + i, v);
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] = fmaf(w, v[e], acc[e]);
+        }
+        if (shared) {
+            float v[V];
+            Pack<T>::load(shared + (long)t * hidden + i, v);
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] = fmaf(g, v[e], acc[e]);
+        }
+        float* hp = h + (long)t * hidden + i;
+#pragma unroll
+        for (int e = 0; e < V; e += 4) {
+            float4 o = *reinterpret_cast<float4*>(hp + e);
+            o.x += acc[e]; o.y += acc[e + 1]; o.z += acc[e + 2]; o.w += acc[e + 3];
+            *reinterpret_cast<float4*>(hp + e) = o;
+            hv[c][e] = o.x; hv[c][e + 1] = o.y; hv[c][e + 2] = o.z; hv[c][e + 3] = o.w;
+            ss = fmaf(o.x, o.x, ss); ss = fmaf(o.y, o.y, ss); ss = fmaf(o.z, o.z, ss); ss = fmaf(o.w, o.w, ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * V;
+        if (i >= hidden) continue;
+        float o[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) o[e] = hv[c][e] * scale * load_any(norm_w, norm_w_dtype, i + e);
+        Pack<T>::store(x_out + (long)t * hidden + i, o);
+    }
+}
+
 inline int threads_for(int n) { int t = 32; while (t < n && t < 1024) t <<= 1; return t; }
 
 }  // namespace
@@ -506,6 +568,32 @@ extern "C" int fx_moe_combine(float* h, const void* y, int dtype, const int* inv
         fx_launch_pdl(moe_combine_kernel<bf16>, grid, nt, 0, s, h, (const bf16*)y, inv_perm, topk_w, top_k,
                                                      (const bf16*)shared, shared_gate_logit, gate_ld, hidden);
     else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+// fx_moe_combine and, on the new residual rows, the RMSNorm with weight `norm_w` into x_out (element type of y).
+// Refuses (FX_ERR_SIZE / FX_ERR_ALIGN) rows it cannot keep in registers; the caller then runs the two kernels.
+extern "C" int fx_moe_combine_norm(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w,
+                                   int top_k, const void* shared, const float* shared_gate_logit, long gate_ld,
+                                   int n_tokens, int hidden, const void* norm_w, int norm_w_dtype, float eps,
+                                   void* x_out, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (dtype != FX_F32 && dtype != FX_BF16) return FX_ERR_DTYPE;
+    const int vw = dtype == FX_F32 ? 4 : 8;
+    if (hidden % vw) return FX_ERR_SIZE;
+    if ((uintptr_t)y % 16 || (uintptr_t)h % 16 || (uintptr_t)shared % 16 || (uintptr_t)x_out % 16) return FX_ERR_ALIGN;
+    const int vecs = hidden / vw;
+    const int nt = threads_for(vecs > 256 ? 256 : vecs);
+    const int ch = (int)fx_cdiv(vecs, nt);
+    if (ch > 4) return FX_ERR_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+#define FX_GO(T, CH)                                                                                                \
+    fx_launch_pdl(moe_combine_norm_kernel<T, CH>, n_tokens, nt, 0, s, h, (const T*)y, inv_perm, topk_w, top_k,       \
+                  (const T*)shared, shared_gate_logit, gate_ld, hidden, norm_w, norm_w_dtype, eps, (T*)x_out)
+    if (dtype == FX_F32) { if (ch <= 1) FX_GO(float, 1); else if (ch == 2) FX_GO(float, 2); else FX_GO(float, 4); }
+    else { if (ch <= 1) FX_GO(bf16, 1); else if (ch == 2) FX_GO(bf16, 2); else FX_GO(bf16, 4); }
+#undef FX_GO
     return fx_launch_status();
 }
 

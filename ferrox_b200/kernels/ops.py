@@ -46,6 +46,7 @@ _SIGNATURES = {
     "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P],
+    "fx_moe_combine_norm": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P, _I, _F, _P, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P],
@@ -540,8 +541,23 @@ def gated_linear(x, w_gu, out, *, status=None, stream=None):
     return silu_mul(gu, out, stream=stream)
 
 
-def moe_combine(h, y, inv_perm, topk_w, shared=None, shared_gate_logit=None, stream=None):
+def combine_norm_ok(h, y) -> bool:
+    """Whether :func:`moe_combine` can also write the normed rows (a thread keeps its part of a row in registers)."""
+    vw = 4 if y.dtype == torch.float32 else 8
+    H = h.shape[1]
+    return y.dtype in _CODES and H % vw == 0 and H // vw <= 4 * 256
+
+
+def moe_combine(h, y, inv_perm, topk_w, shared=None, shared_gate_logit=None, stream=None, norm=None):
+    """h[t] += sum_k topk_w[t, k] * y[inv_perm[t, k]] (+ sigmoid(gate logit) * shared[t]).  ``norm`` = (weight, eps,
+    out): also out[t] = rmsnorm(h[t]) * weight on the new rows, in the same kernel (see :func:`combine_norm_ok`)."""
     T, H = h.shape
+    if norm is not None:
+        w, eps, out = norm
+        call("fx_moe_combine_norm", _ptr(h), _ptr(y), code(y), _ptr(inv_perm), _ptr(topk_w), topk_w.shape[1],
+             _ptr(shared), _ptr(shared_gate_logit), shared_gate_logit.stride(0) if shared_gate_logit is not None else 0,
+             T, H, _ptr(w), code(w), float(eps), _ptr(out), stream if stream is not None else stream_ptr())
+        return out
     call("fx_moe_combine", _ptr(h), _ptr(y), code(y), _ptr(inv_perm), _ptr(topk_w), topk_w.shape[1], _ptr(shared),
          _ptr(shared_gate_logit), shared_gate_logit.stride(0) if shared_gate_logit is not None else 0, T, H, stream if stream is not None else stream_ptr())
 

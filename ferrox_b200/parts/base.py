@@ -57,6 +57,11 @@ class Norm(Part):
     def forward(self, h: torch.Tensor, rows=None) -> torch.Tensor:  # pragma: no cover - interface
         raise NotImplementedError
 
+    def as_rms(self):
+        """(weight, eps) if this norm is x / sqrt(mean(x^2) + eps) * weight over whole rows, which a kernel that
+        has just produced the rows can apply itself; None otherwise."""
+        return None
+
 
 class Mixer(Part):
     def cache_spec(self):
@@ -67,12 +72,21 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    # A feed-forward whose last kernel can also apply the norm that follows it sets ``fuses_norm`` and takes
+    # ``forward_add(x, h, batch, then_norm=norm)``: it returns that norm's output on the new ``h``, or None if it
+    # left the norm to the caller.  Parts without the flag are never given the argument.
+    fuses_norm = False
+
     def forward_add(self, x, h, batch) -> None:  # pragma: no cover - interface
         raise NotImplementedError
 
 
 class Block(Part):
     mixer: Mixer
+    # A block that can take its first norm's output from the block before it (``forward(..., x=...)``) and hand the
+    # next block's to it (``then_norm=`` that block's first norm; returns its output or None) sets ``passes_norm``
+    # and names its first norm ``norm1``.  Blocks without the flag are called with (h, batch, cache) only.
+    passes_norm = False
 
     def forward(self, h, batch, cache) -> None:  # pragma: no cover - interface
         raise NotImplementedError

@@ -33,9 +33,17 @@ class PreNormBlock(Block):
     def graph_safe(self):
         return all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.ffn))
 
-    def forward(self, h, batch, cache):
-        self.mixer.forward_add(self.norm1.forward(h), h, batch, cache)
-        self.ffn.forward_add(self.norm2.forward(h), h, batch)
+    passes_norm = True
+
+    def forward(self, h, batch, cache, x=None, then_norm=None):
+        """``x``: norm1(h) if the block before has computed it.  ``then_norm``: the first norm of the block that runs
+        next; its output on the new h is returned if the feed-forward's last kernel applied it, else None."""
+        self.mixer.forward_add(x if x is not None else self.norm1.forward(h), h, batch, cache)
+        x2 = self.norm2.forward(h)
+        if then_norm is not None and self.ffn.fuses_norm:
+            return self.ffn.forward_add(x2, h, batch, then_norm=then_norm)
+        self.ffn.forward_add(x2, h, batch)
+        return None
 
 
 register_part("pre_norm", PreNormBlock, replace=True)

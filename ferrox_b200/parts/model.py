@@ -88,8 +88,16 @@ class DecoderModel(Part):
         s, rt = self.spec, self.rt
         h = rt.empty(batch.n_tokens, s.hidden, dtype=torch.float32)
         ops.embed(self.embedding, batch.token_ids, h, status=batch.status, stream=batch.stream)
-        for entry in s.schedule:
-            self.layers[entry.layer].forward(h, batch, caches(entry))
+        x = None    # the next block's first norm of h, when the block before it has computed it
+        for i, entry in enumerate(s.schedule):
+            block = self.layers[entry.layer]
+            if not block.passes_norm:
+                block.forward(h, batch, caches(entry))
+                x = None
+                continue
+            nxt = self.layers[s.schedule[i + 1].layer] if i + 1 < len(s.schedule) else None
+            then = nxt.norm1 if nxt is not None and nxt.passes_norm else None
+            x = block.forward(h, batch, caches(entry), x=x, then_norm=then)
         if batch.n_want == 0:
             return rt.empty(0, s.vocab_size, dtype=torch.float32)
         x = self.final_norm.forward(h, rows=batch.want_rows)

@@ -44,6 +44,7 @@ def expert_tile_tokens(T: int, K: int, E: int):
 
 class SoftmaxTopkMoe(FeedForward):
     graph_safe = True
+    fuses_norm = True
     def tensor_decls(self):
         s, p = self.spec, self.spec.prefix
         d = [TensorDecl(p + "gate.weight", (s.n_experts, s.hidden))]
@@ -105,7 +106,7 @@ class SoftmaxTopkMoe(FeedForward):
         ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
         return shared
 
-    def forward_add(self, x, h, batch):
+    def forward_add(self, x, h, batch, then_norm=None):
         s, rt, st = self.spec, self.rt, batch.stream
         T, E, K, I, H = x.shape[0], s.n_experts, s.top_k, s.expert_intermediate, s.hidden
         i32 = torch.int32
@@ -179,7 +180,13 @@ class SoftmaxTopkMoe(FeedForward):
                 shared = self._shared_expert(x, batch, st)
             if self.w_shared_gate is not None:
                 gate_logit = logits[:, E:]      # [T, 1] view with the logits' row stride
+        # the combination applies the norm that follows it where that is an RMSNorm over rows it can hold
+        rms = then_norm.as_rms() if then_norm is not None else None
+        if rms is not None and ops.combine_norm_ok(h, y):
+            out = rt.empty(T, H)
+            return ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st, norm=(rms[0], rms[1], out))
         ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st)
+        return None
 
 
 register_part("softmax_topk_moe", SoftmaxTopkMoe, replace=True)

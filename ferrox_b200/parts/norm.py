@@ -22,4 +22,8 @@ class RmsNorm(Norm):
         return ops.rmsnorm(h, self.weight, self.spec.eps, out, rows=rows)
 
 
+    def as_rms(self):
+        return self.weight, self.spec.eps
+
+
 register_part("rms_norm", RmsNorm, replace=True)

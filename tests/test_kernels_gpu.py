@@ -213,6 +213,34 @@ def test_moe_combine_in_rank_order():
     assert rel(h, want) < 1e-6
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H", [40, 2048, 3584, 8192, 1000])
+@pytest.mark.parametrize("with_shared", [True, False])
+def test_moe_combine_with_the_norm_that_follows(dtype, H, with_shared):
+    """The combine that also applies the next RMSNorm: the same residual rows, bit for bit, as the combine alone, and
+    the normed rows of the norm kernel on them (sums of squares in another order: a rounding apart)."""
+    o, dt = ops(), DT[dtype]
+    T, K = 5, 4
+    y, shared = rnd(T * K, H, dtype=dt), (rnd(T, H, dtype=dt) if with_shared else None)
+    inv = torch.randperm(T * K, generator=torch.Generator().manual_seed(0)).to(torch.int32).to(DEV)
+    w = torch.rand(T, K, generator=torch.Generator().manual_seed(1)).to(DEV)
+    logits = rnd(T, 7)
+    gate = logits[:, 6:] if with_shared else None      # a strided column, as the router's product leaves it
+    nw = (1 + 0.1 * rnd(H, seed=5)).to(dt)
+    h0 = rnd(T, H, seed=2)
+    h_a, h_b = h0.clone(), h0.clone()
+    o.moe_combine(h_a, y, inv, w, shared, gate)
+    x_a = o.rmsnorm(h_a, nw, 1e-5, torch.empty(T, H, dtype=dt, device=DEV))
+    assert o.combine_norm_ok(h_b, y) == (H % (4 if dtype == "float32" else 8) == 0 and H // (4 if dtype == "float32" else 8) <= 1024)
+    if not o.combine_norm_ok(h_b, y):
+        return
+    x_b = o.moe_combine(h_b, y, inv, w, shared, gate, norm=(nw, 1e-5, torch.empty(T, H, dtype=dt, device=DEV)))
+    assert torch.equal(h_a, h_b)
+    assert rel(x_b.float(), x_a.float()) < (1e-6 if dtype == "float32" else 8e-3)
+    want = h_a / torch.sqrt((h_a * h_a).mean(dim=1, keepdim=True) + 1e-5) * nw.float()
+    assert rel(x_b.float(), want) < (1e-6 if dtype == "float32" else 8e-3)
+
+
 # ------------------------------------------------------------------ rotary + cache write + attention
 def build_cache(dtype, seqs, nkv, d, page_size, n_pages, seed=0):
     """Random K/V for requests of the given lengths, scattered into shuffled pages."""
