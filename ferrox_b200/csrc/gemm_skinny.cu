@@ -257,7 +257,9 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
     // few long ones; measured)
     const int slots = group_offsets ? n_slots : 1;
     // wide matrices: 32 features per block, so that half as many blocks pay the start-up latency
-    const bool two_tiles = !gated && fx_cdiv(N, 32) * slots >= 2 * 148;
+    // (also where 16-feature tiles would be a little more than one round of resident blocks: one round of fat
+    // blocks beats a round and a bit of thin ones)
+    const bool two_tiles = !gated && (fx_cdiv(N, 32) * slots >= 2 * 148 || fx_cdiv(N, 16) * slots > 2 * 148);
     // Two resident blocks per SM walk the tiles (expert slot major, then feature tile); a block fetches its
     // next tile's weights while it finishes the current one.
     long tiles = fx_cdiv(N, two_tiles ? 32 : 16) * (long)slots;
