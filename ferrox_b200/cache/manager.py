@@ -1,10 +1,12 @@
 """The cache manager: pages of keys and values with a block table per request,
 groups of layers with different needs, and slots for per-request state of fixed size.
 
-* A **page** holds ``page_size`` consecutive positions of one request for one layer:
-  K and V tensors of shape [n_pages, n_kv_heads, page_size, head_dim] per cache
-  index.  A page *id* is valid in every layer of its **group**: the layers of a
-  group share one id space, one free list and one block table per request.
+* A **page** holds ``page_size`` consecutive positions of one request for one layer.
+  What a position stores is the mixer's own affair: it names its tensors and the
+  shape of one position's entry (``cache.specs.PagedSpec``; keys and values, each
+  [n_pages, n_kv_heads, page_size, head_dim], are the built-in case).  A page *id*
+  is valid in every layer of its **group**: the layers of a group share one id
+  space, one free list and one block table per request, whatever they store.
 * **Groups** are formed by what the layers need: all earlier keys (window None) or
   the last W positions.  A windowed group gives pages back as soon as every
   position in them has fallen out of the window of the request's next query; the
@@ -46,13 +48,20 @@ class CacheError(RuntimeError):
 class LayerCache:
     """What a mixer sees of the cache while one schedule entry runs."""
 
-    k: Optional[torch.Tensor]
-    v: Optional[torch.Tensor]
+    pages: Dict[str, torch.Tensor]  # the mixer's paged tensors by the names of its PagedSpec
     block_table: Optional[torch.Tensor]  # device int32 [max_slots, table_width]; -1 = no page
     page_size: int
     state: Optional[torch.Tensor]  # [max_slots, *shape]
     writes: bool = True
     window: Optional[int] = None
+
+    @property
+    def k(self) -> Optional[torch.Tensor]:
+        return self.pages.get("k")
+
+    @property
+    def v(self) -> Optional[torch.Tensor]:
+        return self.pages.get("v")
 
 
 _CHECKS = {
@@ -120,27 +129,28 @@ class CacheManager:
         self.table_width = (self.max_positions + self.page_size - 1) // self.page_size
         self.groups: Dict[object, _Group] = {}
         self._group_of: List[Optional[_Group]] = []
-        self._k: List[Optional[torch.Tensor]] = []
-        self._v: List[Optional[torch.Tensor]] = []
+        self._pages: List[Dict[str, torch.Tensor]] = []
         self._state: List[Optional[torch.Tensor]] = []
         for idx, cs in enumerate(cache_specs):
             g = None
-            k = v = st = None
-            if cs is not None and cs.kv is not None:
-                key = cs.kv.window
+            st = None
+            pages: Dict[str, torch.Tensor] = {}
+            if cs is not None and cs.paged is not None:
+                key = cs.paged.window
                 if key not in self.groups:
                     n = n_pages[key] if isinstance(n_pages, dict) else int(n_pages)
                     self.groups[key] = _Group(self, len(self.groups), key, n, self.max_slots, self.table_width, self.device)
                 g = self.groups[key]
                 g.caches.append(idx)
-                shape = (g.pool.n_pages, cs.kv.n_kv_heads, self.page_size, cs.kv.head_dim)
-                k = torch.zeros(shape, dtype=dtype, device=self.device)
-                v = torch.zeros(shape, dtype=dtype, device=self.device)
+                for ts in cs.paged.tensors:
+                    if ts.name in pages:
+                        raise CacheError(f"cache {idx}: two paged tensors are named {ts.name!r}")
+                    pages[ts.name] = torch.zeros((g.pool.n_pages, *ts.page_shape(self.page_size)),
+                                                 dtype=ts.dtype or dtype, device=self.device)
             if cs is not None and cs.state is not None:
                 st = torch.zeros((self.max_slots, *cs.state.shape), dtype=cs.state.dtype, device=self.device)
             self._group_of.append(g)
-            self._k.append(k)
-            self._v.append(v)
+            self._pages.append(pages)
             self._state.append(st)
         order = sorted(self.groups.values(), key=lambda g: g.index)
         windows = (ctypes.c_int * max(1, len(order)))(*[-1 if g.window is None else int(g.window) for g in order])
@@ -244,8 +254,7 @@ class CacheManager:
     def layer_cache(self, cache_index: int, writes: bool = True) -> LayerCache:
         g = self._group_of[cache_index]
         return LayerCache(
-            k=self._k[cache_index],
-            v=self._v[cache_index],
+            pages=self._pages[cache_index],
             block_table=g.table_dev if g is not None else None,
             page_size=self.page_size,
             state=self._state[cache_index],
@@ -254,7 +263,7 @@ class CacheManager:
         )
 
     def kv_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self._k + self._v if t is not None)
+        return sum(t.numel() * t.element_size() for pages in self._pages for t in pages.values())
 
     # ---- invariants (tests) -----------------------------------------------------
     def check_invariants(self) -> None:

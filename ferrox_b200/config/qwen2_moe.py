@@ -43,7 +43,23 @@ _SCHEMA = (
     Key("hidden_act", str, default="silu"),
     Key("eos_token_id", int, default=None, nullable=True),
     Key("bos_token_id", int, default=None, nullable=True),
+    # keys of this family's config.json that change the arithmetic and are implemented in one setting only
+    Key("rope_scaling", object, default=None, nullable=True,
+        check=lambda v: "scaled rotary positions are not implemented (only null)"),
+    Key("partial_rotary_factor", float, default=1.0,
+        check=lambda v: None if v == 1.0 else "a rotary width below head_dim is not implemented (only 1.0)"),
+    Key("attention_bias", bool, default=None, nullable=True),   # another spelling of qkv_bias; must agree with it
+    Key("attention_dropout", float, default=0.0, check=non_negative),  # training only
+    Key("mlp_bias", bool, default=False, check=lambda v: "a bias in the feed-forward is not implemented" if v else None),
 )
+
+# Keys a checkpoint's config.json carries that do not concern inference.
+_BOOKKEEPING = (
+    "architectures", "model_type", "torch_dtype", "dtype", "transformers_version", "_name_or_path", "use_cache",
+    "initializer_range", "output_router_logits", "router_aux_loss_coef", "pad_token_id", "auto_map", "id2label",
+    "label2id", "return_dict", "output_attentions", "output_hidden_states", "is_decoder", "use_bfloat16",
+    "tokenizer_class", "task_specific_params", "problem_type", "chunk_size_feed_forward", "tie_encoder_decoder",
+    )
 
 
 @dataclass(frozen=True)
@@ -92,8 +108,12 @@ class Qwen2MoeConfig:
     # ---- JSON ---------------------------------------------------------------
     @classmethod
     def from_json(cls, obj: dict) -> "Qwen2MoeConfig":
-        v = read_keys(obj, _SCHEMA)
+        v = read_keys(obj, _SCHEMA, ignore=_BOOKKEEPING)
         problems = []
+        if v["attention_bias"] is not None and v["attention_bias"] != v["qkv_bias"]:
+            problems.append(f"attention_bias={v['attention_bias']} contradicts qkv_bias={v['qkv_bias']}")
+        for k in ("rope_scaling", "partial_rotary_factor", "attention_bias", "attention_dropout", "mlp_bias"):
+            v.pop(k)
         if v["head_dim"] % 2:
             problems.append("head_dim must be even (rotary pairs)")
         if v["num_attention_heads"] % v["num_key_value_heads"]:

@@ -32,7 +32,7 @@ class Key:
     """One row of a configuration schema."""
 
     name: str
-    kind: type  # int, float, bool, str, list
+    kind: type  # int, float, bool, str, list; object = any JSON value
     default: Any = REQUIRED  # REQUIRED, a value, or a callable(values_so_far) -> value
     check: Optional[Callable[[Any], Optional[str]]] = None  # returns an error text or None
     nullable: bool = False
@@ -75,15 +75,25 @@ def _coerce(key: Key, raw: Any) -> Any:
         if not isinstance(raw, (list, tuple)):
             raise TypeError(f"expected a list, found {raw!r}")
         return list(raw)
+    if key.kind is object:
+        return raw
     raise TypeError(f"schema error: unsupported kind {key.kind}")
 
 
-def read_keys(obj: dict, schema: Sequence[Key], where: str = "config.json") -> dict:
-    """Validate ``obj`` against ``schema``; returns {name: value}. Keys of ``obj``
-    that the schema does not list are ignored (checkpoints carry many keys that
-    do not concern inference)."""
+def read_keys(obj: dict, schema: Sequence[Key], where: str = "config.json", ignore=None) -> dict:
+    """Validate ``obj`` against ``schema``; returns {name: value}.  ``ignore``: the keys of ``obj`` beside the
+    schema's that do not concern inference (book-keeping of the checkpoint: its dtype, the library version that
+    wrote it, training settings).  With it, a key that neither the schema nor ``ignore`` lists is an error: the
+    engine refuses a configuration that asks for something it does not implement rather than compute something
+    else (the reference refuses metadata it cannot honour, crates/ferrox-models/src/capability.rs:616-637,
+    loader.rs:141-158).  ``ignore=None`` ignores every unlisted key."""
     values: dict = {}
     problems: list[str] = []
+    if ignore is not None:
+        known = {k.name for k in schema} | set(ignore)
+        for name in obj:
+            if name not in known:
+                problems.append(f"{name}: not a key this engine implements (refused rather than ignored)")
     for key in schema:
         if key.name in obj and not (obj[key.name] is None and not key.nullable and key.default is not REQUIRED):
             try:

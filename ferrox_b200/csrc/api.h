@@ -11,6 +11,9 @@ int fx_gemm(const void* A, int a_dtype, long lda, const int* a_rows, const void*
             const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K,
             const int* group_offsets, int n_groups, long w_group_stride, void* stream);
 
+// Streaming multiprocessors of the current device (asked once).
+int fx_sm_count();
+
 // Programmatic dependent launch of the short kernels on (1, default) or off (0); returns the old setting.
 int fx_set_pdl(int on);
 
@@ -21,7 +24,7 @@ int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, floa
 int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev, int rows, int n,
                 void* stream);
 int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const int* token_seq, const int* seq_slot,
-                     const float* inv_freq, const float* cos_sin, int rotary_dim, void* k_pages, void* v_pages, const int* block_table,
+                     const float* inv_freq, const float* cos_sin, int rotary_dim, int pairing, void* k_pages, void* v_pages, const int* block_table,
                      int table_width, int page_size, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                      int write_cache, int* status, void* stream);
 int fx_moe_combine(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w, int top_k,
@@ -74,19 +77,30 @@ int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, lo
 int fx_decode_split_mma(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table,
                         int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot,
                         float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                        int window, float scale, int split_len, int n_splits, void* stream);
+                        int window, float scale, int split_len, int n_splits, int fresh_positions, void* stream);
 int fx_decode_split_tma(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages,
                         const int* block_table, int table_width, int page_size, const int* positions,
                         const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml, int n_tokens,
                         int n_heads, int n_kv_heads, int head_dim, int window, float scale, int split_len,
-                        int n_splits, int* status, void* out, long ldo, int* counters, void* stream);
+                        int n_splits, int* status, void* out, long ldo, int* counters, int fresh_positions,
+                        void* stream);
 // n_pages > 0 (the number of pages behind k_pages / v_pages) lets bfloat16 take the TMA kernel; status: the step's
 // status word (may be null).
+// fresh_positions: 0 makes no assumption about the kernel launched before this one on the stream: nothing is read until
+// it has finished.  N > 0 is the caller's promise that that kernel wrote, of everything this call reads, only the
+// queries and the keys and values of at most the last N positions of each request (positions, token_seq, seq_slot and
+// the block table are older); the bfloat16 kernels then fetch tiles of older keys while that kernel still runs.  A
+// promise that does not hold gives stale keys without any error.
 int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages, int dtype,
                         const int* block_table, int table_width, int page_size, const int* positions,
                         const int* token_seq, const int* seq_slot, void* out, long ldo, float* part_acc,
                         float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
-                        float scale, int split_len, int n_splits, int* status, int* counters, void* stream);
+                        float scale, int split_len, int n_splits, int* status, int* counters, int fresh_positions,
+                        void* stream);
+
+// out[i] = mean + stdev * z_i, z the standard normal stream of `key` (random_init.cu; the host restates the rule
+// bit for bit).  dtype: FX_F32 or FX_BF16.
+int fx_random_normal(void* out, int dtype, long n, unsigned long long key, double mean, double stdev, void* stream);
 
 int fx_argmax(const float* logits, long ld, int n_rows, int vocab, int* out, void* stream);
 int fx_sample_or(const float* scores, long lds, float* work, long ld, int n_rows, int vocab, const float* temperature,

@@ -313,7 +313,7 @@ template <typename T>
 int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages, const int* block_table,
         int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot, void* out,
         long ldo, float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
-        float scale, int split_len, int n_splits, int* status, int* counters, cudaStream_t s)
+        float scale, int split_len, int n_splits, int* status, int* counters, int fresh, cudaStream_t s)
 {
     constexpr int N = Vec<T>::N;
     if (head_dim % N || head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -327,13 +327,13 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n
             rc_mma = fx_decode_split_tma(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size,
                                          positions, token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads,
                                          n_kv_heads, head_dim, window, scale, split_len, n_splits, status, out, ldo,
-                                         counters, (void*)s);
+                                         counters, fresh, (void*)s);
             if (rc_mma == FX_OK && (counters || n_splits == 1)) return FX_OK;   // merged by the kernel's last blocks
         }
         if (rc_mma < 0)
             rc_mma = fx_decode_split_mma(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions,
                                          token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads, n_kv_heads,
-                                         head_dim, window, scale, split_len, n_splits, (void*)s);
+                                         head_dim, window, scale, split_len, n_splits, fresh, (void*)s);
         if (rc_mma == FX_OK) {
             fx_launch_pdl(merge_kernel<T>, dim3(n_tokens, n_heads), 64, 0, s, part_acc, part_ml, positions, (T*)out, ldo,
                           n_heads, head_dim, n_splits, split_len, window);
@@ -374,7 +374,7 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
                                    const int* positions, const int* token_seq, const int* seq_slot, void* out, long ldo,
                                    float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
                                    int head_dim, int window, float scale, int split_len, int n_splits, int* status,
-                                   int* counters, void* stream)
+                                   int* counters, int fresh_positions, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (split_len < 0 || n_splits <= 0) return FX_ERR_SIZE;
@@ -382,11 +382,11 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
                           seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, status, counters, s);
+                          split_len, n_splits, status, counters, fresh_positions, s);
     if (dtype == FX_BF16)
         return run<bf16>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
                          seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, status, counters, s);
+                         split_len, n_splits, status, counters, fresh_positions, s);
     return FX_ERR_DTYPE;
 }
 
@@ -434,15 +434,17 @@ extern "C" int fx_decode_attention_noalloc(const void* q, long ldq, const void* 
     float* part_acc = g_noalloc_ptr[dev];
     float* part_ml = part_acc + slots * head_dim;   // offset is a multiple of head_dim floats; only 4-byte access
     cudaStream_t s = (cudaStream_t)stream;
-    // Every slot that the merge reads is written by the split kernel of the same call
-    // (empty splits write max = -inf, sum = 0), so nothing has to be cleared first.
+    // Every slot that the merge reads is written by the split kernel of the same call (a split
+    // without visible keys writes nothing and the merge skips it by the same rule), so nothing
+    // has to be cleared first.  No promise is made about the kernel before this call: the
+    // attention kernels read nothing before it has finished.
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                           out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, nullptr, nullptr, s);
+                          split_len, n_splits, nullptr, nullptr, 0, s);
     if (dtype == FX_BF16)
         return run<bf16>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                          out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, nullptr, nullptr, s);
+                         split_len, n_splits, nullptr, nullptr, 0, s);
     return FX_ERR_DTYPE;
 }

@@ -28,7 +28,6 @@
 namespace {
 
 constexpr int NTHREADS = 128, TK = 64, STAGES = 2, MAXQ = 16;
-constexpr int NEWEST_POSITIONS = 64;   // a launch may follow the write of at most this many new positions of a request
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -58,8 +57,11 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     const int* __restrict__ block_table, int table_width, int page_size,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
     float* __restrict__ part_acc, float* __restrict__ part_ml,
-    int n_heads, int n_kv_heads, int head_dim, int window, float scale_log2e, float scale, int split_len, int n_splits)
+    int n_heads, int n_kv_heads, int head_dim, int window, float scale_log2e, float scale, int split_len, int n_splits,
+    int fresh)
 {
+    // fresh <= 0: nothing is known about the kernel before this one, so nothing is read before it has finished.
+    if (fresh <= 0) fx_pdl_wait();
     const int group_size = n_heads / n_kv_heads;
     const int chunks = (group_size + MAXQ - 1) / MAXQ;
     const int kvh = blockIdx.x / chunks;
@@ -127,10 +129,11 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             if (ch == 0) fl[r] = ok ? 1 : 0;
         }
     };
-    // The kernel before this one on the stream wrote the queries and the keys and values of the step's own positions
-    // (at most NEWEST_POSITIONS of a request, its last ones); everything read so far, and every older key, is older.
-    // A block whose first tile ends before those positions asks for it before it waits for that kernel.
-    const bool early = k_begin + TK <= pos + 1 - NEWEST_POSITIONS;
+    // fresh > 0 is the caller's promise: the kernel before this one on the stream wrote the queries and the keys and
+    // values of at most the last `fresh` positions of each request, and nothing else that this kernel reads
+    // (positions, slots and block table are older).  A block whose first tile ends before those positions then asks
+    // for it before it waits for that kernel.
+    const bool early = fresh > 0 && k_begin + TK <= pos + 1 - fresh;
     if (early) load_tile(0, 0);
     fx_pdl_wait();
     load_q();
@@ -267,7 +270,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
 template <int DMAX>
 int launch(dim3 grid, size_t smem, cudaStream_t s, const bf16* q, long ldq, const bf16* k, const bf16* v, const int* bt,
            int tw, int ps, const int* pos, const int* tseq, const int* sslot, float* pa, float* pm, int nh, int nkv, int d,
-           int window, float scale, int split_len, int n_splits)
+           int window, float scale, int split_len, int n_splits, int fresh)
 {
     auto kern = decode_mma_kernel<DMAX>;
     if (smem > 48 * 1024) {
@@ -275,7 +278,7 @@ int launch(dim3 grid, size_t smem, cudaStream_t s, const bf16* q, long ldq, cons
         if (e != cudaSuccess) return (int)e;
     }
     fx_launch_pdl(kern, grid, NTHREADS, smem, s, q, ldq, k, v, bt, tw, ps, pos, tseq, sslot, pa, pm, nh, nkv, d, window,
-                  scale * 1.4426950408889634f, scale, split_len, n_splits);
+                  scale * 1.4426950408889634f, scale, split_len, n_splits, fresh);
     return fx_launch_status();
 }
 
@@ -287,7 +290,7 @@ extern "C" int fx_decode_split_mma(const void* q, long ldq, const void* k_pages,
                                    const int* block_table, int table_width, int page_size, const int* positions,
                                    const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml,
                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                                   int split_len, int n_splits, void* stream)
+                                   int split_len, int n_splits, int fresh_positions, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (head_dim % 16 || head_dim <= 0 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -304,10 +307,10 @@ extern "C" int fx_decode_split_mma(const void* q, long ldq, const void* k_pages,
     const bf16* Q = (const bf16*)q; const bf16* K = (const bf16*)k_pages; const bf16* V = (const bf16*)v_pages;
     if (head_dim <= 64)
         return launch<64>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, positions, token_seq, seq_slot,
-                          part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits);
+                          part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions);
     if (head_dim <= 128)
         return launch<128>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, positions, token_seq, seq_slot,
-                           part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits);
+                           part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions);
     return launch<256>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, positions, token_seq, seq_slot,
-                       part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits);
+                       part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions);
 }

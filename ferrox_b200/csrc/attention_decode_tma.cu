@@ -37,7 +37,6 @@ namespace {
 using namespace fxtc;
 
 constexpr int NCONSUMERS = 128, NTHREADS = 160, TK = 64, MAXQ = 16, MAX_STAGES = 8;
-constexpr int NEWEST_POSITIONS = 64;   // a launch may follow the write of at most this many new positions of a request
 constexpr int PIECE = TK * 128;        // bytes of a [64 keys][64 dims] piece
 
 struct DecArgs {
@@ -48,6 +47,10 @@ struct DecArgs {
     int n_heads, n_kv_heads, head_dim, window;
     float scale_log2e, scale;
     int split_len, n_splits, stages;
+    // fresh > 0 is the caller's promise: the kernel before this one on the stream wrote the queries and the keys and
+    // values of at most the last `fresh` positions of each request and nothing else that this kernel reads; tiles of
+    // older keys are then asked for before that kernel has finished.  fresh <= 0: nothing is read before it has.
+    int fresh;
     int* status;
     // With `counters` (one zeroed int per (token, block of heads), left zeroed again) the block that finishes a token's
     // last key range merges all of them into `out`; without, the caller runs the merge kernel.  A single key range a
@@ -85,6 +88,7 @@ template <int DMAX>
 __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                               const __grid_constant__ CUtensorMap map_v, DecArgs a)
 {
+    if (a.fresh <= 0) fx_pdl_wait();
     const int head_dim = a.head_dim, n_heads = a.n_heads, n_kv_heads = a.n_kv_heads;
     const int group_size = n_heads / n_kv_heads;
     const int chunks = (group_size + MAXQ - 1) / MAXQ;
@@ -141,8 +145,8 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
                 const int page = page_next;
                 if (j + 1 < n_tiles) page_next = table[(key0 + TK) / a.page_size];
                 // The kernel before this one wrote the keys and values of the step's own positions (the last
-                // NEWEST_POSITIONS of a request at most); a tile that ends before them may be asked for at once.
-                if (!waited && key0 + TK > pos + 1 - NEWEST_POSITIONS) { fx_pdl_wait(); waited = true; }
+                // a.fresh of a request at most); a tile that ends before them may be asked for at once.
+                if (!waited && key0 + TK > pos + 1 - a.fresh) { fx_pdl_wait(); waited = true; }
                 if (j >= stages && !mbar_wait(empty(s), ((j / stages) - 1) & 1, abort_flag)) break;
                 page_ok_s[s] = page >= 0;
                 if (page >= 0) {
@@ -391,7 +395,7 @@ extern "C" int fx_decode_split_tma(const void* q, long ldq, const void* k_pages,
                                    const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml,
                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                    int split_len, int n_splits, int* status, void* out, long ldo, int* counters,
-                                   void* stream)
+                                   int fresh_positions, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (counters && (n_splits > 32 || !out || ldo % 2)) return FX_ERR_SIZE;
@@ -420,6 +424,7 @@ extern "C" int fx_decode_split_tma(const void* q, long ldq, const void* k_pages,
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f; a.scale = scale;
     a.split_len = split_len; a.n_splits = n_splits; a.stages = stages; a.status = status;
+    a.fresh = fresh_positions;
     a.out = (bf16*)out; a.ldo = ldo; a.counters = counters;
     if (n_splits > 1 && !counters) a.out = nullptr;   // partial results only
     cudaStream_t s = (cudaStream_t)stream;

@@ -116,3 +116,6 @@ static inline int fx_launch_status() {
 }
 
 static inline long fx_cdiv(long a, long b) { return (a + b - 1) / b; }
+
+// Streaming multiprocessors of the current device, asked once (elementwise.cu); grids are sized by it.
+extern "C" int fx_sm_count();

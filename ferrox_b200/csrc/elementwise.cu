@@ -13,6 +13,18 @@ extern "C" int fx_set_pdl(int on)
     return was;
 }
 
+extern "C" int fx_sm_count()
+{
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) n = v;
+        else return 148;   // no answer (no device yet): the B200's count, not remembered
+    }
+    return n;
+}
+
 namespace {
 
 // ---------------------------------------------------------------------------
@@ -73,13 +85,16 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, long ld_in, T* __restr
 }
 
 // ---------------------------------------------------------------------------
-// Rotary encoding (split-half pairing) of q and k, and the write of k and v into
-// their cache pages, in one pass over the fused q|k|v rows.
-//   angle = pos * inv_freq[i];  (x_i, x_{i+r/2}) <- (x_i cos - x_{i+r/2} sin, x_i sin + x_{i+r/2} cos)
-// (reference: crates/ferrox-core/src/attention.rs:20-32; applied per head at the
-// token's absolute position, decoder.rs:2106-2111, 3489-3507; K/V append
-// decoder.rs:2123-2125, paged cache.rs:382-404).  Elements beyond `rotary_dim`
-// pass through.  `inv_freq == nullptr` means no rotation (position encoding none).
+// Rotary encoding of q and k, and the write of k and v into their cache pages, in
+// one pass over the fused q|k|v rows.
+//   angle = pos * inv_freq[i];  (a, b) <- (a cos - b sin, a sin + b cos)
+// where pair i is (x_i, x_{i+r/2}) for pairing 0 (split halves; reference:
+// crates/ferrox-core/src/attention.rs:20-32) and (x_2i, x_2i+1) for pairing 1
+// (adjacent elements; attention.rs:340-352); the table inv_freq carries whatever
+// per-band frequencies the position part wants (attention.rs:319-337 divides them
+// by factors).  Applied per head at the token's absolute position
+// (decoder.rs:2106-2111, 3489-3507); K/V append decoder.rs:2123-2125, paged
+// cache.rs:382-404.  Elements beyond `rotary_dim` pass through.  `inv_freq == nullptr` means no rotation (position encoding none).
 // `cos_sin` (optional, [tokens, rotary_dim/2, 2]) holds cos and sin of exactly these
 // angles, made once per step by rope_table_kernel for all layers that share them.
 // Page layout: [page][kv_head][token_in_page][head_dim].
@@ -87,7 +102,7 @@ template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __restrict__ positions,
                                      const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                                      const float* __restrict__ inv_freq, const float* __restrict__ cos_sin,
-                                     int rotary_dim, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                     int rotary_dim, int pairing, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      const int* __restrict__ block_table, int table_width, int page_size,
                                      int n_heads, int n_kv_heads, int head_dim, int write_cache,
                                      int* __restrict__ status)
@@ -117,9 +132,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __
                 sincosf((float)pos * inv_freq[i], &s, &c);
             }
             T* x = row + (long)h * head_dim;
-            const float a = to_f32(x[i]), b = to_f32(x[i + half]);
-            x[i] = from_f32<T>(a * c - b * s);
-            x[i + half] = from_f32<T>(a * s + b * c);
+            const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+            const float a = to_f32(x[ia]), b = to_f32(x[ib]);
+            x[ia] = from_f32<T>(a * c - b * s);
+            x[ib] = from_f32<T>(a * s + b * c);
         }
     }
     if (page_base < 0) return;
@@ -483,7 +499,7 @@ extern "C" int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, i
     if (rows <= 0 || n <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     long blocks = fx_cdiv((long)rows * n, 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > fx_sm_count() * 16L) blocks = fx_sm_count() * 16L;
     if (dtype == FX_F32) silu_mul_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)gu, ld_in, (float*)out, ld_out, n_rows_dev, rows, n);
     else if (dtype == FX_BF16) silu_mul_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((const bf16*)gu, ld_in, (bf16*)out, ld_out, n_rows_dev, rows, n);
     else return FX_ERR_DTYPE;
@@ -492,18 +508,18 @@ extern "C" int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, i
 
 extern "C" int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const int* token_seq,
                                 const int* seq_slot, const float* inv_freq, const float* cos_sin, int rotary_dim,
-                                void* k_pages,
+                                int pairing, void* k_pages,
                                 void* v_pages, const int* block_table, int table_width, int page_size, int n_tokens,
                                 int n_heads, int n_kv_heads, int head_dim, int write_cache, int* status, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
-    if (rotary_dim % 2 || rotary_dim > head_dim || page_size <= 0) return FX_ERR_SIZE;
+    if (rotary_dim % 2 || rotary_dim > head_dim || page_size <= 0 || pairing < 0 || pairing > 1) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const int work = (n_heads + n_kv_heads) * (head_dim / 2);
     const int nt = threads_for(work > 256 ? 256 : work);
     const int vw = dtype == FX_F32 ? 4 : 8;
     const int es = dtype == FX_F32 ? 4 : 2;
-    const bool vec = (rotary_dim == head_dim || inv_freq == nullptr) && (head_dim / 2) % vw == 0 && (ld * es) % 16 == 0 &&
+    const bool vec = ((rotary_dim == head_dim && pairing == 0) || inv_freq == nullptr) && (head_dim / 2) % vw == 0 && (ld * es) % 16 == 0 &&
                      (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0;
     if (vec && (dtype == FX_F32 || dtype == FX_BF16)) {
         const int items = ((n_heads + n_kv_heads) * (head_dim / 2) + n_kv_heads * head_dim) / vw;
@@ -520,11 +536,11 @@ extern "C" int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positi
     }
     if (dtype == FX_F32)
         fx_launch_pdl(rope_kv_write_kernel<float>, n_tokens, nt, 0, s, (float*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
-            cos_sin, rotary_dim, (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
+            cos_sin, rotary_dim, pairing, (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
             head_dim, write_cache, status);
     else if (dtype == FX_BF16)
         fx_launch_pdl(rope_kv_write_kernel<bf16>, n_tokens, nt, 0, s, (bf16*)qkv, ld, positions, token_seq, seq_slot, inv_freq,
-            cos_sin, rotary_dim, (bf16*)k_pages, (bf16*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
+            cos_sin, rotary_dim, pairing, (bf16*)k_pages, (bf16*)v_pages, block_table, table_width, page_size, n_heads, n_kv_heads,
             head_dim, write_cache, status);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
@@ -535,7 +551,7 @@ extern "C" int fx_rope_table(const int* positions, const float* inv_freq, int n_
 {
     if (n_tokens <= 0 || half <= 0) return FX_OK;
     long blocks = fx_cdiv((long)n_tokens * half, 128);
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > fx_sm_count() * 8L) blocks = fx_sm_count() * 8L;
     fx_launch_pdl(rope_table_kernel, (unsigned)blocks, 128, 0, (cudaStream_t)stream, positions, inv_freq, n_tokens, half, cos_sin);
     return fx_launch_status();
 }
@@ -618,7 +634,7 @@ extern "C" int fx_residual_add(float* h, const void* y, int dtype, long n, void*
     if (n <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     long blocks = fx_cdiv(n, 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > fx_sm_count() * 16L) blocks = fx_sm_count() * 16L;
     if (dtype == FX_F32) residual_add_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(h, (const float*)y, n);
     else if (dtype == FX_BF16) residual_add_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>(h, (const bf16*)y, n);
     else return FX_ERR_DTYPE;

@@ -259,11 +259,12 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
     // wide matrices: 32 features per block, so that half as many blocks pay the start-up latency
     // (also where 16-feature tiles would be a little more than one round of resident blocks: one round of fat
     // blocks beats a round and a bit of thin ones)
-    const bool two_tiles = !gated && (fx_cdiv(N, 32) * slots >= 2 * 148 || fx_cdiv(N, 16) * slots > 2 * 148);
+    const long resident = 2L * fx_sm_count();   // two blocks an SM
+    const bool two_tiles = !gated && (fx_cdiv(N, 32) * slots >= resident || fx_cdiv(N, 16) * slots > resident);
     // Two resident blocks per SM walk the tiles (expert slot major, then feature tile); a block fetches its
     // next tile's weights while it finishes the current one.
     long tiles = fx_cdiv(N, two_tiles ? 32 : 16) * (long)slots;
-    dim3 grid((unsigned)(tiles < 2 * 148 ? tiles : 2 * 148), 1);
+    dim3 grid((unsigned)(tiles < resident ? tiles : resident), 1);
     const int hint = group_offsets ? tokens_hint : n_tokens;
     cudaStream_t s = (cudaStream_t)stream;
     if (gated) return launch_nt<1>(a, hint, grid, s);

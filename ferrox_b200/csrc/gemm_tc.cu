@@ -336,17 +336,6 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t d1, uint64
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int sm_count()
-{
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
-    }
-    return n;
-}
-
 template <int BN, bool GATED>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, long max_tiles, cudaStream_t s)
 {
@@ -357,7 +346,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, long m
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const unsigned grid = (unsigned)(max_tiles < sm_count() ? max_tiles : sm_count());
+    const unsigned grid = (unsigned)(max_tiles < fx_sm_count() ? max_tiles : fx_sm_count());
     fx_launch_pdl(kern, grid, NTHREADS, Cfg<BN>::SMEM, s, ma, mb, a);
     return fx_launch_status();
 }

@@ -323,8 +323,7 @@ extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    int sms = 148, dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = fx_sm_count();
     const int out_n = gated ? BNH : 2 * BNH;
     const long tiles = fx_cdiv(M, 2 * BM) * fx_cdiv(N, out_n);
     long pairs = tiles < sms / 2 ? tiles : sms / 2;

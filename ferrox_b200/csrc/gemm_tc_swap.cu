@@ -337,17 +337,6 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t d1, uint64
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int sm_count()
-{
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
-    }
-    return n;
-}
-
 template <int TNB, bool GATED>
 int launch(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, const SwArgs& a, cudaStream_t s)
 {
@@ -366,12 +355,12 @@ int launch(const void* X, long ldx, const void* W, long ldw, long w_group_stride
     }
     const long t_tiles = a.group_offsets ? fx_cdiv(a.M, TNB) + a.n_groups : fx_cdiv(a.M, TNB);   // an upper bound when grouped
     const long max_tiles = t_tiles * fx_cdiv(a.N, BF) * (a.k_splits > 1 ? a.k_splits : 1);
-    const long slots = (long)sm_count() * Cfg<TNB, GATED>::CTAS_PER_SM;
+    const long slots = (long)fx_sm_count() * Cfg<TNB, GATED>::CTAS_PER_SM;
     const unsigned grid = (unsigned)(max_tiles < slots ? max_tiles : slots);
     fx_launch_pdl(kern, grid, NTHREADS, Cfg<TNB, GATED>::SMEM, s, mw, mx, a);
     if (a.k_splits > 1) {
         long blocks = fx_cdiv((long)a.M * a.N, 256);
-        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks > fx_sm_count() * 8L) blocks = fx_sm_count() * 8L;
         fx_launch_pdl(splitk_reduce_kernel, (unsigned)blocks, 256, 0, s, (const float*)a.partials, a.k_splits, a.M, a.N, a.C,
                       a.ldc, a.c_dtype, a.accumulate, a.bias, a.bias_dtype);
     }

@@ -218,7 +218,7 @@ extern "C" int fx_route(const float* logits, long ld, int n_tokens, int n_expert
                   logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, scratch);
     const int n = n_tokens * top_k;
     int blocks = (int)fx_cdiv(n, 256);
-    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks > fx_sm_count() * 4L) blocks = fx_sm_count() * 4L;
     fx_launch_pdl(scan_place_kernel, blocks, 256, 0, s, ids, n, n_experts, top_k, scratch, scratch + n_experts, offsets,
                   src_token, inv_perm, active, n_slots);
     return fx_launch_status();
@@ -251,7 +251,7 @@ extern "C" int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_exper
     cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(int) * 2 * n_experts, s);
     if (e != cudaSuccess) return (int)e;
     int blocks = (int)fx_cdiv(n, 256);
-    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks > fx_sm_count() * 4L) blocks = fx_sm_count() * 4L;
     count_kernel<<<blocks, 256, 0, s>>>(ids, n, n_experts, scratch);
     scan_kernel<<<1, 32, 0, s>>>(scratch, n_experts, offsets, scratch + n_experts, active, n_slots);
     place_kernel<<<blocks, 256, 0, s>>>(ids, n, n_experts, top_k, offsets, scratch + n_experts, src_token, inv_perm);

@@ -19,6 +19,9 @@
 //  * The first call on a device looks up the array's device address (that device
 //    must be current).  Make this first call outside any stream capture.
 //  * The call itself calls no cudaMalloc, cudaFree or allocating library routine.
+//  * The call assumes nothing about the kernels launched before it on the stream:
+//    its kernels read nothing (queries, positions, block table, keys, values) until
+//    those have finished, however many positions they wrote.
 //  * All calls share the one array, and it keeps the previous call's contents.
 //    Nothing needs clearing between calls (every value read is written first by the
 //    same call), but two calls whose kernels overlap on the GPU (different streams,

@@ -21,10 +21,6 @@ import numpy as np
 import torch
 
 
-QUERY_TILE = 64  # query tokens per tile of the mma.sync prompt attention kernel
-WIDE_QUERY_TILE = 256  # query tokens per tile of the tcgen05 prompt attention kernel (two sub-tiles of 128)
-
-
 @dataclass
 class StepEntry:
     slot: int
@@ -49,23 +45,19 @@ class StepBatch:
     max_len: int = 0  # longest request length after this step
     max_new: int = 0  # most tokens any entry brings
     h2d_bytes: int = 0  # size of the step's host-to-device copy
-    q_tiles: torch.Tensor = None  # [n_tiles, 4] int32: (first flat token, rows <= 64, entry, first position)
-    q_tiles_wide: torch.Tensor = None  # the same for tiles of <= 256 rows
-    shared: dict = field(default_factory=dict)  # per-step values that several layers share (e.g. rotary tables)
+    # per-step values that a part makes once and the layers like it share (rotary tables, the work lists of a
+    # mixer's kernels), under keys of the part's own choosing
+    shared: dict = field(default_factory=dict)
 
 
 def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: int) -> StepBatch:
     T = sum(len(e.tokens) for e in entries)
     B = len(entries)
     W = sum(len(e.want) for e in entries)
-    n_tiles = sum(-(-len(e.tokens) // QUERY_TILE) for e in entries)
-    n_wide = sum(-(-len(e.tokens) // WIDE_QUERY_TILE) for e in entries)
-    buf = np.empty(3 * T + B + W + 4 * n_tiles + 4 * n_wide, dtype=np.int32)
+    buf = np.empty(3 * T + B + W, dtype=np.int32)
     tok, pos, seq = buf[:T], buf[T:2 * T], buf[2 * T:3 * T]
     slots, want = buf[3 * T:3 * T + B], buf[3 * T + B:3 * T + B + W]
-    tiles = buf[3 * T + B + W:3 * T + B + W + 4 * n_tiles].reshape(n_tiles, 4)
-    wide = buf[3 * T + B + W + 4 * n_tiles:].reshape(n_wide, 4)
-    t = w = ti = wi = 0
+    t = w = 0
     max_len = max_new = 0
     for b, e in enumerate(entries):
         n = len(e.tokens)
@@ -78,12 +70,6 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
                 raise ValueError(f"want index {i} outside the entry's {n} tokens")
             want[w] = t + i
             w += 1
-        for i in range(0, n, QUERY_TILE):
-            tiles[ti] = (t + i, min(QUERY_TILE, n - i), b, e.start + i)
-            ti += 1
-        for i in range(0, n, WIDE_QUERY_TILE):
-            wide[wi] = (t + i, min(WIDE_QUERY_TILE, n - i), b, e.start + i)
-            wi += 1
         t += n
         max_len = max(max_len, e.start + n)
         max_new = max(max_new, n)
@@ -92,8 +78,6 @@ def flatten(entries: Sequence[StepEntry], device, status: torch.Tensor, stream: 
         n_tokens=T, n_seqs=B, n_want=W,
         token_ids=dev[:T], positions=dev[T:2 * T], token_seq=dev[2 * T:3 * T],
         seq_slot=dev[3 * T:3 * T + B], want_rows=dev[3 * T + B:3 * T + B + W],
-        q_tiles=dev[3 * T + B + W:3 * T + B + W + 4 * n_tiles].view(n_tiles, 4),
-        q_tiles_wide=dev[3 * T + B + W + 4 * n_tiles:].view(n_wide, 4),
         status=status, stream=stream, entries=list(entries), max_len=max_len, max_new=max_new,
         h2d_bytes=buf.nbytes,
     )

@@ -80,8 +80,9 @@ class Engine:
     @classmethod
     def from_random(cls, config, seed=0, dtype="bfloat16", device="cuda:0", std=0.02, norm_init="ones",
                     on_device=False, **cache_opts) -> "Engine":
-        """Random weights without a folder.  ``on_device=True`` draws them with the
-        device's generator (fast for large models; values differ from the CPU draw)."""
+        """Random weights without a folder, by the rule of ``weights.random_init`` (the same values as
+        ``write_random_model`` writes for this configuration and seed).  ``on_device=True`` draws them on the device
+        (fast for large models); the values are the same bit for bit."""
         _require_cuda(device)
         obj = load_json(config) if isinstance(config, str) else config
         config, spec = resolve(obj)

@@ -1,6 +1,7 @@
 """Trace replay: feed given token ids through a model step by step and write logits.
 
     trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    trace_run --random CONFIG.json --seed S --dtype ... --out DIR --max-tokens N
 
 Steps arrive on standard input, one JSON object a line:
 
@@ -30,7 +31,14 @@ import numpy as np
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    src = ap.add_mutually_exclusive_group(required=True)
+    src.add_argument("--model", help="folder with config.json and model.safetensors")
+    src.add_argument("--random", metavar="CONFIG", help="a config.json (or a folder holding one): random weights drawn "
+                     "on the device by the rule of the random-weights mode, the values a folder written by it holds")
+    ap.add_argument("--seed", type=int, default=0, help="seed of --random (default 0)")
+    ap.add_argument("--std", type=float, default=0.02, help="standard deviation of --random (default 0.02)")
+    ap.add_argument("--norm-init", default="ones", choices=["ones", "around_one", "normal"],
+                    help="norm weights of --random (default ones)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
@@ -46,8 +54,12 @@ def main(argv=None) -> int:
     os.makedirs(args.out, exist_ok=True)
     ps = args.page_size
     n_pages = max(1, (args.max_tokens + ps - 1) // ps)
-    eng = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, page_size=ps, n_pages=n_pages,
-                             max_slots=args.max_requests)
+    opts = dict(dtype=args.dtype, device=args.device, page_size=ps, n_pages=n_pages, max_slots=args.max_requests)
+    if args.model is not None:
+        eng = Engine.from_folder(args.model, **opts)
+    else:
+        eng = Engine.from_random(args.random, seed=args.seed, std=args.std, norm_init=args.norm_init, on_device=True,
+                                 **opts)
     slots = {}
     for line in sys.stdin:
         line = line.strip()

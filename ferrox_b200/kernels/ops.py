@@ -8,7 +8,7 @@ torch fallback, and a CPU tensor is an error.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_long, c_void_p
+from ctypes import c_double, c_float, c_int, c_long, c_ulonglong, c_void_p
 from typing import Optional
 
 import torch
@@ -37,7 +37,7 @@ _SIGNATURES = {
     "fx_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
     "fx_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_silu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _P],
-    "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_rope_table": [_P, _P, _I, _I, _P, _P],
     "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
     "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _P, _P, _P],
@@ -55,11 +55,12 @@ _SIGNATURES = {
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "fx_decode_attention": [_P, _L, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                            _I, _P, _P, _P],
+                            _I, _P, _P, _I, _P],
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
     "fx_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "fx_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "fx_sample_or": [_P, _L, _P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
+    "fx_random_normal": [_P, _I, _L, c_ulonglong, c_double, c_double, _P],
 }
 
 _fn = {}
@@ -107,6 +108,18 @@ def call(name: str, *args) -> None:
 
 
 _scoped_stream = None
+_sm_count = 0
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device, asked once; launch shapes and the choices between kernels are
+    functions of it.  Without a device (the choices are also tested on the CPU): the B200's 148."""
+    global _sm_count
+    if _sm_count == 0:
+        if not torch.cuda.is_available():
+            return 148
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sm_count
 
 
 def stream_ptr() -> int:
@@ -236,11 +249,19 @@ def route(logits, top_k, renorm, ids, weights, scratch, offsets, src_token, inv_
          stream if stream is not None else stream_ptr())
 
 
+PAIR_HALVES, PAIR_ADJACENT = 0, 1
+
+
 def rope_kv_write(qkv, positions, token_seq, seq_slot, inv_freq, rotary_dim, k_pages, v_pages, block_table, page_size,
-                  n_heads, n_kv_heads, head_dim, write_cache=True, status=None, stream=None, cos_sin=None):
+                  n_heads, n_kv_heads, head_dim, write_cache=True, status=None, stream=None, cos_sin=None,
+                  pairing=PAIR_HALVES):
+    """Rotates the q and k heads of the fused [q|k|v] rows in place at each token's position and stores k and v in
+    their cache pages.  ``inv_freq`` ([rotary_dim/2] float32, or None for no rotation) gives each pair's frequency,
+    ``pairing`` which elements form pair i: PAIR_HALVES (i, i + rotary_dim/2) or PAIR_ADJACENT (2i, 2i+1);
+    ``cos_sin`` ([T, rotary_dim/2, 2], optional) holds this step's cos and sin, made by :func:`rope_table`."""
     T = qkv.shape[0]
     call("fx_rope_kv_write", _ptr(qkv), code(qkv), _rows(qkv), _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
-         _ptr(inv_freq), _ptr(cos_sin), rotary_dim, _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
+         _ptr(inv_freq), _ptr(cos_sin), rotary_dim, int(pairing), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
          T, n_heads, n_kv_heads, head_dim, int(write_cache), _ptr(status), stream if stream is not None else stream_ptr())
 
 
@@ -270,6 +291,12 @@ def prefill_attention(q, k_pages, v_pages, block_table, page_size, tiles, seq_sl
 
 
 WIDE_PREFILL_TILE = 256
+
+
+def prefill_ok(q, out, k_pages, head_dim) -> bool:
+    """Whether the mma.sync prompt attention kernel takes these operands (bfloat16, head sizes in steps of 16)."""
+    return (q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and 0 < head_dim <= 256 and head_dim % 16 == 0
+            and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 16 == 0 and k_pages.data_ptr() % 16 == 0)
 
 
 def prefill_tc_ok(q, out, k_pages, page_size, head_dim) -> bool:
@@ -366,7 +393,7 @@ def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int, block
     (``single_is_final``: a kernel that writes a single run's result itself, so only n > 1 pays it).  Measured
     on a B200 with 16 kv heads of 128: 64 requests 178 us with one run and 189 us with two, 8 requests 35 and 29."""
     blocks = max(1, n_tokens * n_kv_blocks)
-    slots = 148 * blocks_per_sm
+    slots = sm_count() * blocks_per_sm
     best, best_cost = 1, None
     for n in range(1, min(DECODE_MAX_SPLITS, max(1, -(-max_positions // 64))) + 1):
         waves = -(-blocks * n // slots)
@@ -379,9 +406,12 @@ def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int, block
 
 def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,
                      n_kv_heads, head_dim, window, scale, split_len, n_splits, part_acc, part_ml, status=None,
-                     counters=None, stream=None):
+                     counters=None, stream=None, fresh_positions=0):
     """``counters``: zeroed int32 scratch that the call leaves zeroed, at least tokens x ceil(group / 16) x kv heads;
-    with it the kernel that streams pages by TMA merges the key ranges itself (one kernel instead of two)."""
+    with it the kernel that streams pages by TMA merges the key ranges itself (one kernel instead of two).
+    ``fresh_positions``: 0 assumes nothing about the kernel launched just before on the stream.  N > 0 promises that
+    that kernel wrote, of all this call reads, only the queries and the keys and values of at most the last N
+    positions of each request; older keys are then fetched while it still runs (a false promise reads stale keys)."""
     global _launches
     T = q.shape[0]
     per_sm = decode_tma_blocks_per_sm(q.dtype, head_dim, page_size)
@@ -389,14 +419,14 @@ def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, tok
     # Merging in the kernel pays while all blocks run at the same time: the count and the fence lengthen the end of
     # every block, which costs nothing only where no other block waits for its place.
     if counters is not None and not (per_sm > 0 and 1 < n_splits <= 32 and counters.numel() >= blocks
-                                     and blocks * n_splits <= 148 * per_sm):
+                                     and blocks * n_splits <= sm_count() * per_sm):
         counters = None
     if per_sm > 0 and (counters is not None or n_splits == 1):
         _launches -= 1      # no merge kernel
     call("fx_decode_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], code(q),
          _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(out), _rows(out), _ptr(part_acc), _ptr(part_ml), T, n_heads, n_kv_heads, head_dim, int(window or 0),
-         float(scale), split_len, n_splits, _ptr(status), _ptr(counters),
+         float(scale), split_len, n_splits, _ptr(status), _ptr(counters), int(fresh_positions),
          stream if stream is not None else stream_ptr())
     return out
 
@@ -485,9 +515,9 @@ def swap_better(T: int, N: int, K: int) -> bool:
 def pairs_better(M: int, N: int, gated: bool = False) -> bool:
     """Prompt-sized dense products: whether the kernel on pairs of SMs (256 x 256 tiles) beats the one with a CTA per
     128 x 256 tile.  Measured on a B200: from two rounds of tiles for the 74 pairs on (3 to 13 % faster, more with more
-    rows); with fewer tiles the pairs leave SMs idle."""
+    rows); with fewer tiles than SMs the pairs leave SMs idle."""
     tiles = -(-M // 256) * -(-N // (128 if gated else 256))
-    return M >= 1024 and tiles >= 148
+    return M >= 1024 and tiles >= sm_count()
 
 
 def swap_k_splits(T: int, N: int, K: int) -> int:
@@ -584,6 +614,16 @@ def sample_or(scores, work, temperature, top_k, top_p, draw, use_sample, instead
     n, V = scores.shape
     call("fx_sample_or", _ptr(scores), _rows(scores), _ptr(work), _rows(work), n, V, _ptr(temperature), _ptr(top_k),
          _ptr(top_p), _ptr(draw), _ptr(use_sample), _ptr(instead), _ptr(out),
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def random_normal(out, key: int, mean: float, std: float, stream=None):
+    """out[i] = mean + std * z_i, z the standard normal stream of the 64-bit ``key`` (the rule of
+    ``weights.random_init``, which states it for the CPU bit for bit).  ``out``: contiguous float32 or bfloat16."""
+    if not out.is_contiguous():
+        raise KernelError("random_normal fills contiguous tensors")
+    call("fx_random_normal", _ptr(out), code(out), out.numel(), key & ((1 << 64) - 1), float(mean), float(std),
          stream if stream is not None else stream_ptr())
     return out
 

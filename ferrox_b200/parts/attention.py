@@ -13,12 +13,14 @@ from __future__ import annotations
 
 import math
 
+import numpy as np
 import torch
 
 from ..cache.specs import CacheSpec, KvCacheSpec
 from ..kernels import ops
 from ..weights.loader import TensorDecl
 from .base import Mixer, build_part, register_part
+from .specs import NoPositionSpec
 
 
 RANGE_COUNTERS = 16384            # (token, block of heads) pairs of a decode step whose key ranges one kernel merges
@@ -29,22 +31,47 @@ def _common_dtype(tensors):
     return torch.float32 if any(t.dtype == torch.float32 for t in tensors) else tensors[0].dtype
 
 
+def query_tiles(batch, rows: int) -> torch.Tensor:
+    """The work list of a prompt-attention kernel that takes ``rows`` queries of one request at a time: int32
+    [n_tiles, 4] rows of (first flat token, rows in the tile, entry index, absolute position of the first row).
+    Made once a step for each tile size and shared by the layers (``batch.shared``)."""
+    key = ("attention query tiles", rows)
+    t = batch.shared.get(key)
+    if t is None:
+        out, flat = [], 0
+        for b, e in enumerate(batch.entries):
+            n = len(e.tokens)
+            for i in range(0, n, rows):
+                out.append((flat + i, min(rows, n - i), b, e.start + i))
+            flat += n
+        t = torch.from_numpy(np.asarray(out, dtype=np.int32).reshape(-1, 4)).to(batch.token_ids.device)
+        batch.shared[key] = t
+    return t
+
+
 class GqaAttention(Mixer):
-    graph_safe = True
+    @property
+    def graph_safe(self):
+        # this mixer only enqueues kernels; whether its position part does is that part's word
+        return self.position.graph_safe
+
     def __init__(self, spec):
         super().__init__(spec)
         s = spec
         if s.head_dim % 2 or s.head_dim > 256:
             raise ValueError(f"head_dim={s.head_dim}: must be even and at most 256")
+        if s.window is not None and s.window < 1:
+            raise ValueError(f"window={s.window}: a window holds at least the query's own position")
         if s.n_heads % s.n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
-        self.position = build_part(s.position) if s.position is not None else None
+        # the position encoding is a part of its own: it rotates q and k and stores k and v (no encoding: it only stores)
+        self.position = build_part(s.position if s.position is not None else NoPositionSpec())
         self.q_size = s.n_heads * s.head_dim
         self.kv_size = s.n_kv_heads * s.head_dim
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
 
     def cache_spec(self):
-        return CacheSpec(kv=KvCacheSpec(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window))
+        return CacheSpec(paged=KvCacheSpec(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window))
 
     def tensor_decls(self):
         s, p = self.spec, self.spec.prefix
@@ -74,8 +101,7 @@ class GqaAttention(Mixer):
             bdt = _common_dtype(bs)
             self.b_qkv = torch.cat([b.to(bdt) for b in bs]).contiguous()
         self.w_o = src.get(p + "o_proj.weight")
-        if self.position is not None:
-            self.position.load(src, rt)
+        self.position.load(src, rt)
         # zeroed scratch of the decode attention kernel that merges its own key ranges (it leaves it zeroed)
         self._range_counters = (torch.zeros(RANGE_COUNTERS, dtype=torch.int32, device=rt.device)
                                 if rt.device.type == "cuda" else None)
@@ -85,14 +111,7 @@ class GqaAttention(Mixer):
         T = x.shape[0]
         qkv = self.rt.empty(T, self.q_size + 2 * self.kv_size)
         ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, status=batch.status, stream=batch.stream)
-        inv_freq = self.position.inv_freq if self.position is not None else None
-        rotary = self.position.rotary_dim if self.position is not None else 0
-        cos_sin = self.position.table(batch) if self.position is not None else None
-        ops.rope_kv_write(
-            qkv, batch.positions, batch.token_seq, batch.seq_slot, inv_freq, rotary, cache.k, cache.v,
-            cache.block_table, cache.page_size, s.n_heads, s.n_kv_heads, s.head_dim,
-            write_cache=cache.writes, status=batch.status, stream=batch.stream, cos_sin=cos_sin,
-        )
+        self.position.rotate_and_store(qkv, batch, cache, s.n_heads, s.n_kv_heads, s.head_dim)
         attn = self.rt.empty(T, self.q_size)
         if batch.max_new <= DECODE_ATTENTION_MAX_NEW:
             # few query tokens: split each request's keys over many blocks
@@ -108,20 +127,26 @@ class GqaAttention(Mixer):
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, split_len, n_splits,
                 part_acc, part_ml, status=batch.status, counters=self._range_counters, stream=batch.stream,
+                # the kernel just before (the position part's) wrote these rows' q and the k, v of the step's own
+                # positions, at most max_new of a request
+                fresh_positions=batch.max_new,
             )
-        elif batch.q_tiles_wide is not None and ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
+        elif ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
             # prompt portions: tiles of 256 queries, tcgen05
             ops.prefill_attention_tc(
-                qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.q_tiles_wide, batch.seq_slot, attn,
+                qkv, cache.k, cache.v, cache.block_table, cache.page_size,
+                query_tiles(batch, ops.WIDE_PREFILL_TILE), batch.seq_slot, attn,
                 s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, status=batch.status, stream=batch.stream,
             )
-        elif qkv.dtype == torch.bfloat16 and batch.q_tiles is not None:
+        elif ops.prefill_ok(qkv, attn, cache.k, s.head_dim):
             # prompt portions, other head and page sizes: tiles of 64 queries, mma.sync
             ops.prefill_attention(
-                qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.q_tiles, batch.seq_slot, attn,
+                qkv, cache.k, cache.v, cache.block_table, cache.page_size, query_tiles(batch, ops.PREFILL_TILE),
+                batch.seq_slot, attn,
                 s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
             )
         else:
+            # 32-bit, and head sizes that are no multiple of 16: a warp per (token, head)
             ops.paged_attention(
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,

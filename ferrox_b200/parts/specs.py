@@ -36,13 +36,20 @@ class PositionSpec:
 
 
 @dataclass(frozen=True)
+class NoPositionSpec:
+    """Queries and keys are used as projected."""
+
+    kind: str = "no_position"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     hidden: int
     n_heads: int
     n_kv_heads: int
     head_dim: int
     qkv_bias: bool
-    position: Optional[PositionSpec]
+    position: Optional[object]  # the spec of a position-encoding part (None: no encoding)
     window: Optional[int]  # None = all earlier keys; W = the last W positions, the query's own included
     prefix: str  # tensors: <prefix>{q,k,v}_proj.{weight,bias}, <prefix>o_proj.weight
     softmax_scale: Optional[float] = None  # None = 1/sqrt(head_dim)

@@ -10,9 +10,9 @@ from ferrox_b200.cache.specs import CacheSpec, KvCacheSpec, StateSpec
 
 def manager(n_pages=8, page_size=4, window=6, max_slots=3, with_state=True):
     specs = [
-        CacheSpec(kv=KvCacheSpec(2, 8, None)),
-        CacheSpec(kv=KvCacheSpec(1, 16, window), state=StateSpec((5,)) if with_state else None),
-        CacheSpec(kv=KvCacheSpec(2, 8, None)),
+        CacheSpec(paged=KvCacheSpec(2, 8, None)),
+        CacheSpec(paged=KvCacheSpec(1, 16, window), state=StateSpec((5,)) if with_state else None),
+        CacheSpec(paged=KvCacheSpec(2, 8, None)),
         None,
     ]
     return CacheManager(specs, page_size=page_size, n_pages=n_pages, max_slots=max_slots, max_positions=64,

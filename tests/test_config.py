@@ -87,3 +87,42 @@ def test_round_trip_through_json():
     cfg, _ = resolve(TINY_B)
     again, _ = resolve(cfg.to_json())
     assert again == cfg
+
+
+@pytest.mark.parametrize("extra,named", [
+    ({"rope_scaling": {"type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32768}}, "rope_scaling"),
+    ({"partial_rotary_factor": 0.5}, "partial_rotary_factor"),
+    ({"attention_bias": False}, "attention_bias"),          # contradicts qkv_bias=true
+    ({"mlp_bias": True}, "mlp_bias"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"rope_parameters": {"rope_theta": 5e5}}, "rope_parameters"),   # a key this engine does not know at all
+    ({"attn_logit_softcapping": 30.0}, "attn_logit_softcapping"),
+])
+def test_a_configuration_that_asks_for_what_is_not_implemented_is_refused(extra, named):
+    """Keys that change the arithmetic and are not built, and keys the engine has never heard of, are refused by
+    name instead of being ignored (wrong logits otherwise)."""
+    with pytest.raises(ConfigError, match=named):
+        resolve(dict(TINY_A, **extra))
+
+
+def test_every_refusal_in_one_error_and_bookkeeping_keys_pass():
+    with pytest.raises(ConfigError) as e:
+        resolve(dict(TINY_A, rope_scaling={"type": "linear", "factor": 2.0}, partial_rotary_factor=0.25,
+                     sliding_window_pattern=4))
+    msg = str(e.value)
+    assert "rope_scaling" in msg and "partial_rotary_factor" in msg and "sliding_window_pattern" in msg
+    # what a published checkpoint's config.json carries beside the architecture's keys
+    cfg, _ = resolve(dict(TINY_A, model_type="qwen2_moe", torch_dtype="bfloat16", transformers_version="4.40.0",
+                          use_cache=True, initializer_range=0.02, attention_dropout=0.0, output_router_logits=False,
+                          router_aux_loss_coef=0.001, rope_scaling=None, partial_rotary_factor=1.0,
+                          attention_bias=True, bos_token_id=1, eos_token_id=2))
+    assert cfg.eos_token_id == 2 and cfg.qkv_bias
+
+
+def test_a_head_size_no_prompt_kernel_takes_in_bfloat16_still_builds():
+    """head_dim 40 (no multiple of 16) is a legal configuration: the mixer is built, and its prompt path is the
+    general kernel (checked on the GPU in the replay tests)."""
+    cfg, spec = resolve(dict(TINY_C, head_dim=40))
+    assert spec.layers[0].mixer.head_dim == 40
+    with pytest.raises(ConfigError, match="head_dim"):
+        resolve(dict(TINY_C, head_dim=41))

@@ -807,3 +807,126 @@ def test_gemm_skinny_transposed_store_and_linear_picks_it_for_narrow_outputs():
     wide = torch.full((T, N + 3), 7.0, device=DEV)   # a view with a row pitch of its own
     o.linear(x, w, wide[:, :N])
     assert rel(wide[:, :N], want) < 2e-5 and float(wide[:, N:].min()) == 7.0
+
+
+# ------------------------------------------------------------------ random weights
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape,mean,std", [((7,), 0.0, 0.02), ((33, 129), 1.0, 0.02), ((5, 64, 48), 0.0, 1.0),
+                                            ((1408, 2048), 0.0, 0.02)])
+def test_random_weights_are_the_same_bits_on_the_device_and_on_the_cpu(dtype, shape, mean, std):
+    """The device draw against the host's statement of the same rule, bit for bit (odd lengths end inside a pair;
+    the last shape is one expert matrix at the real width, its checksum compared as well)."""
+    from ferrox_b200.weights import random_init as ri
+
+    key = ri.tensor_key(11, f"t{shape}")
+    dev = ri.normal(key, shape, DT[dtype], mean, std, device=DEV).cpu()
+    cpu = ri.normal(key, shape, DT[dtype], mean, std, device="cpu")
+    assert dev.dtype == cpu.dtype == DT[dtype] and dev.shape == cpu.shape == shape
+    ibits = torch.int32 if dtype == "float32" else torch.int16
+    assert torch.equal(dev.view(ibits), cpu.view(ibits))
+    assert int(dev.view(ibits).to(torch.int64).sum()) == int(cpu.view(ibits).to(torch.int64).sum())
+
+
+def test_a_model_drawn_on_the_device_is_the_model_of_the_folder(tmp_path):
+    """Engine.from_random(on_device=True) and a folder written on the CPU for the same configuration and seed hold
+    the same weights: their logits are equal bit for bit."""
+    from ferrox_b200 import Engine, StepEntry, write_random_model
+    from tiny_configs import TINY_B
+
+    folder = write_random_model(str(tmp_path / "m"), TINY_B, seed=5, norm_init="around_one")
+    toks = [(i * 37 + 11) % TINY_B["vocab_size"] for i in range(41)]
+    outs = []
+    for make in (lambda: Engine.from_folder(folder, dtype="float32", page_size=16, n_pages=8, max_slots=2),
+                 lambda: Engine.from_random(TINY_B, seed=5, norm_init="around_one", dtype="float32", on_device=True,
+                                            page_size=16, n_pages=8, max_slots=2)):
+        eng = make()
+        slot = eng.open_request()
+        outs.append(eng.step([StepEntry(slot, toks, want=list(range(len(toks))))]).cpu())
+    assert torch.equal(outs[0], outs[1])
+
+
+# ------------------------------------------------------------------ the rotary kernel's other pairing rule
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,d,rot", [(4, 2, 16, 16), (3, 1, 48, 20), (2, 2, 128, 128)])
+def test_rope_adjacent_pairs_with_a_frequency_table(dtype, nh, nkv, d, rot):
+    """Pairs (2i, 2i+1) rotated by pos * inv_freq[i] for an arbitrary table (the reference's interleaved form with
+    per-band factors, crates/ferrox-core/src/attention.rs:340-352, 319-337); the rest of the head passes through;
+    the keys reach their pages as rotated."""
+    o, dt = ops(), DT[dtype]
+    ps, T = 8, 5
+    width = nh * d + 2 * nkv * d
+    qkv = rnd(T, width, dtype=dt)
+    before = qkv.clone()
+    positions = torch.tensor([0, 1, 2, 40, 41], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([0, 0, 0, 1, 1], dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor([1, 0], dtype=torch.int32, device=DEV)
+    table = torch.full((2, 8), -1, dtype=torch.int32)
+    table[1, 0], table[0, 5] = 2, 0
+    table = table.to(DEV)
+    kp = torch.zeros(3, nkv, ps, d, dtype=dt, device=DEV)
+    vp = torch.zeros_like(kp)
+    inv_freq = (torch.rand(rot // 2, generator=torch.Generator().manual_seed(rot)) + 0.01).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.rope_kv_write(qkv, positions, token_seq, seq_slot, inv_freq, rot, kp, vp, table, ps, nh, nkv, d, True, status,
+                    pairing=o.PAIR_ADJACENT)
+    assert int(status) == 0
+    x = before.float().cpu()
+    ang = positions.cpu().float()[:, None] * inv_freq.cpu()[None, :]
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    tol = 2e-6 if dtype == "float32" else 8e-3
+    for t in range(T):
+        for hh in range(nh + nkv):
+            head = x[t, hh * d:(hh + 1) * d]
+            want = head.clone()
+            a, b = head[0:rot:2], head[1:rot:2]
+            want[0:rot:2] = a * cos[t] - b * sin[t]
+            want[1:rot:2] = a * sin[t] + b * cos[t]
+            assert rel(qkv[t, hh * d:(hh + 1) * d].cpu(), want) < tol
+    for t, (pg, off) in {0: (2, 0), 2: (2, 2), 3: (0, 0), 4: (0, 1)}.items():
+        assert torch.equal(kp[pg, :, off, :].reshape(-1), qkv[t, nh * d:(nh + nkv) * d])
+        assert torch.equal(vp[pg, :, off, :].reshape(-1), before[t, (nh + nkv) * d:])
+
+
+# ------------------------------------------------------------------ decode attention right after a long write
+@pytest.mark.parametrize("page_size,d", [(64, 128), (16, 48)])
+def test_decode_attention_waits_for_a_write_of_many_positions(page_size, d):
+    """The public entry makes no assumption about the kernel before it: 100 positions of one request are written by
+    the rotary kernel and read by the decode attention launched right behind it (more than any early fetch could
+    skip), many times over, against the plain attention."""
+    o = ops()
+    nh, nkv, n_new, L0 = 4, 2, 100, 90
+    dt = torch.bfloat16
+    scale = 1 / math.sqrt(d)
+    n_pages = -(-(L0 + n_new) // page_size) + 1
+    table = torch.full((1, n_pages + 2), -1, dtype=torch.int32)
+    table[0, :n_pages] = torch.randperm(n_pages, generator=torch.Generator().manual_seed(3)).int()
+    table = table.to(DEV)
+    seq_slot = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for trial in range(5):
+        kp = torch.zeros(n_pages, nkv, page_size, d, dtype=dt, device=DEV)
+        vp = torch.zeros_like(kp)
+        # the old positions, then the new ones in the very launch before the attention
+        rows = rnd(L0 + n_new, (nh + 2 * nkv) * d, dtype=dt, seed=trial)
+        want_rows = rows.clone()
+        pos_all = torch.arange(L0 + n_new, dtype=torch.int32, device=DEV)
+        seq_all = torch.zeros(L0 + n_new, dtype=torch.int32, device=DEV)
+        o.rope_kv_write(rows[:L0], pos_all[:L0], seq_all[:L0], seq_slot, None, 0, kp, vp, table, page_size, nh, nkv, d,
+                        True, status)
+        torch.cuda.synchronize()
+        out = torch.zeros(n_new, nh * d, dtype=dt, device=DEV)
+        n_splits = 3
+        pa = torch.empty(n_new, nh, n_splits, d, device=DEV)
+        pm = torch.empty(n_new, nh, n_splits, 2, device=DEV)
+        o.rope_kv_write(rows[L0:], pos_all[L0:], seq_all[L0:], seq_slot, None, 0, kp, vp, table, page_size, nh, nkv, d,
+                        True, status)
+        o.decode_attention(rows[L0:], kp, vp, table, page_size, pos_all[L0:], seq_all[L0:], seq_slot, out, nh, nkv, d,
+                           0, scale, 0, n_splits, pa, pm)
+        torch.cuda.synchronize()
+        assert int(status) == 0
+        x = want_rows.float().cpu()
+        k = x[:, nh * d:(nh + nkv) * d].reshape(-1, nkv, d)
+        v = x[:, (nh + nkv) * d:].reshape(-1, nkv, d)
+        for i in (0, 1, 37, n_new - 1):
+            want = plain_attention(x[L0 + i, :nh * d].reshape(nh, d), k, v, L0 + i, 0, scale)
+            assert rel(out[i].float().cpu().reshape(nh, d), want) < 1e-2, (trial, i)

@@ -316,7 +316,9 @@ class UnrotatedSpec:
 
 def _register_more_toys():
     from ferrox_b200 import register_part
-    from ferrox_b200.parts.base import FeedForward, Part
+    from ferrox_b200.kernels import ops
+    from ferrox_b200.parts.base import FeedForward
+    from ferrox_b200.parts.position import PositionEncoding
     from ferrox_b200.weights.loader import TensorDecl
 
     class HashRouted(FeedForward):
@@ -336,14 +338,12 @@ def _register_more_toys():
             branch = (batch.positions.long() % self.spec.n_branches)
             h += torch.einsum("th,toh->to", x.float(), self.w[branch])
 
-    class Unrotated(Part):
-        def load(self, src, rt):
-            super().load(src, rt)
-            self.inv_freq = None      # tells the attention kernel not to rotate
-            self.rotary_dim = 0
-
-        def table(self, batch):
-            return None
+    class Unrotated(PositionEncoding):
+        def rotate_and_store(self, qkv, batch, cache, n_heads, n_kv_heads, head_dim):
+            # nothing to encode: keys and values go to their pages as projected
+            ops.rope_kv_write(qkv, batch.positions, batch.token_seq, batch.seq_slot, None, 0, cache.k, cache.v,
+                              cache.block_table, cache.page_size, n_heads, n_kv_heads, head_dim,
+                              write_cache=cache.writes, status=batch.status, stream=batch.stream)
 
     register_part("toy_hash_routed_ffn", HashRouted, replace=True)
     register_part("toy_unrotated_position", Unrotated, replace=True)
@@ -393,3 +393,243 @@ def test_toy_routed_feed_forward_and_unrotated_attention(tmp_path):
     a = eng.step([StepEntry(s, toks[:7], want=list(range(7)))]).cpu()
     b = eng.step([StepEntry(s, toks[7:], want=list(range(4)))]).cpu()
     assert rel(torch.cat([a, b]), want) < 3e-5
+
+
+# ------------------------------------------------------------------ a rotary encoding of another kind, defined here
+@dataclass(frozen=True)
+class AdjacentRopeSpec:
+    """Adjacent pairs (2i, 2i+1) with each band's frequency divided by a factor
+    (the reference: crates/ferrox-core/src/attention.rs:340-352 and :319-337)."""
+    rotary_dim: int
+    theta: float
+    factors: tuple
+    kind: str = "toy_rope_adjacent"
+
+
+def _register_adjacent_rope():
+    from ferrox_b200 import register_part
+    from ferrox_b200.kernels import ops
+    from ferrox_b200.parts.position import RotaryEncoding
+
+    class AdjacentRope(RotaryEncoding):
+        pairing = ops.PAIR_ADJACENT
+
+        def frequencies(self):
+            return super().frequencies() / torch.tensor(self.spec.factors, dtype=torch.float32)
+
+    register_part("toy_rope_adjacent", AdjacentRope, replace=True)
+
+
+def _rope_adjacent_plain(x, positions, theta, factors, rotary_dim):
+    """x: [T, heads, d]; attention.rs:340-352 with the per-band division of :319-337, over the first rotary_dim."""
+    out = x.clone()
+    half = rotary_dim // 2
+    for t, pos in enumerate(positions):
+        for i in range(half):
+            freq = 1.0 / theta ** ((2 * i) / rotary_dim)
+            angle = pos * freq / factors[i]
+            s, c = math.sin(angle), math.cos(angle)
+            a, b = x[t, :, 2 * i], x[t, :, 2 * i + 1]
+            out[t, :, 2 * i] = a * c - b * s
+            out[t, :, 2 * i + 1] = a * s + b * c
+    return out
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("rotary", [16, 12])
+def test_toy_rotary_encoding_with_adjacent_pairs_and_band_factors(tmp_path, dtype, rotary):
+    """Another position encoding is another part: adjacent pairs, per-band frequency factors and a rotary width below
+    the head size, registered here, built by the framework's attention from its spec, run in two cuts and a decode
+    step, against a plain statement of the reference's interleaved formula."""
+    import ferrox_b200
+    from ferrox_b200 import Engine, StepEntry, register_architecture
+    from ferrox_b200.parts.specs import AttentionSpec, BlockSpec, DenseMlpSpec, ModelSpec, NormSpec, ScheduleEntry
+
+    _register_adjacent_rope()
+    H, nh, nkv, d, theta = 48, 3, 1, 16, 500.0
+    factors = tuple(1.0 + 0.5 * i for i in range(rotary // 2))
+
+    def model_spec(c):
+        p = "model.layers.0."
+        attn = AttentionSpec(hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=d, qkv_bias=True,
+                             position=AdjacentRopeSpec(rotary, theta, factors), window=None, prefix=p + "self_attn.")
+        blk = BlockSpec(NormSpec(H, 1e-6, p + "input_layernorm."), attn, NormSpec(H, 1e-6, p + "post_attention_layernorm."),
+                        DenseMlpSpec(H, 64, p + "mlp."))
+        return ModelSpec(architecture="ToyAdjacentRopeForCausalLM", vocab_size=61, hidden=H, max_positions=64, layers=(blk,),
+                         schedule=(ScheduleEntry(0, 0),), final_norm=NormSpec(H, 1e-6, "model.norm."), head_name=None)
+
+    register_architecture("ToyAdjacentRopeForCausalLM", dict, model_spec, replace=True)
+    folder = ferrox_b200.write_random_model(str(tmp_path / "toy3"), dict(architectures=["ToyAdjacentRopeForCausalLM"]),
+                                            seed=6, std=0.3, norm_init="around_one")
+    w = {k: v.float() for k, v in plain.read_safetensors(folder + "/model.safetensors").items()}
+    toks = [(7 * i + 3) % 61 for i in range(29)]
+    T = len(toks)
+    x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+    n = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], 1e-6)
+
+    def proj(name, heads):
+        return (n @ w[f"model.layers.0.self_attn.{name}.weight"].T + w[f"model.layers.0.self_attn.{name}.bias"]).reshape(T, heads, d)
+
+    q = _rope_adjacent_plain(proj("q_proj", nh), range(T), theta, factors, rotary)
+    k = _rope_adjacent_plain(proj("k_proj", nkv), range(T), theta, factors, rotary)
+    x = x + plain.attention(q, k, proj("v_proj", nkv), None).reshape(T, nh * d) @ w["model.layers.0.self_attn.o_proj.weight"].T
+    n = plain.rms_norm(x, w["model.layers.0.post_attention_layernorm.weight"], 1e-6)
+    x = x + plain.dense_block(n, w, 0)
+    want = plain.rms_norm(x, w["model.norm.weight"], 1e-6) @ w["model.embed_tokens.weight"].T
+
+    dt, tol = DTYPES[dtype]
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=4, n_pages=8, max_slots=2)
+    assert eng.graphs is not None   # the part only enqueues kernels: decode steps are captured
+    s = eng.open_request()
+    outs = [eng.step([StepEntry(s, toks[:11], want=list(range(11)))]).cpu(),
+            eng.step([StepEntry(s, toks[11:26], want=list(range(15)))]).cpu()]
+    for t in range(26, T):   # decode steps: eager, captured, replayed
+        outs.append(eng.step([StepEntry(s, toks[t:t + 1], want=[0])]).cpu().clone())
+    assert rel(torch.cat(outs), want) < tol
+    # and the pairing matters: the split-half rule on the same weights gives other logits
+    assert rel(torch.cat(outs), _with_halves(w, toks, theta, factors, rotary, H, nh, nkv, d)) > 10 * tol
+
+
+def _with_halves(w, toks, theta, factors, rotary, H, nh, nkv, d):
+    T = len(toks)
+    x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+    n = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], 1e-6)
+
+    def proj(name, heads):
+        return (n @ w[f"model.layers.0.self_attn.{name}.weight"].T + w[f"model.layers.0.self_attn.{name}.bias"]).reshape(T, heads, d)
+
+    def rot(v):
+        out = v.clone()
+        out[..., :rotary] = plain.rope_neox(v[..., :rotary], torch.arange(T), theta)
+        return out
+
+    x = x + plain.attention(rot(proj("q_proj", nh)), rot(proj("k_proj", nkv)), proj("v_proj", nkv), None).reshape(
+        T, nh * d) @ w["model.layers.0.self_attn.o_proj.weight"].T
+    n = plain.rms_norm(x, w["model.layers.0.post_attention_layernorm.weight"], 1e-6)
+    x = x + plain.dense_block(n, w, 0)
+    return plain.rms_norm(x, w["model.norm.weight"], 1e-6) @ w["model.embed_tokens.weight"].T
+
+
+# ------------------------------------------------------------------ a mixer whose pages hold one vector per position
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    hidden: int
+    latent: int
+    window: object
+    prefix: str
+    kind: str = "toy_latent_attention"
+
+
+def _register_latent_mixer():
+    from ferrox_b200 import register_part
+    from ferrox_b200.cache.specs import CacheSpec, PagedSpec, PagedTensorSpec
+    from ferrox_b200.parts.base import Mixer
+    from ferrox_b200.weights.loader import TensorDecl
+
+    class LatentAttention(Mixer):
+        """c_t = Wc x_t is all a position stores (one vector, no separate keys and values); the output at t is
+        Wo . softmax_s(c_t . c_s / sqrt(latent)) c_s over the visible positions s of its request."""
+
+        def cache_spec(self):
+            s = self.spec
+            return CacheSpec(paged=PagedSpec((PagedTensorSpec("latent", (s.latent,), dtype=torch.float32),), s.window))
+
+        def tensor_decls(self):
+            s = self.spec
+            return [TensorDecl(s.prefix + "down.weight", (s.latent, s.hidden)),
+                    TensorDecl(s.prefix + "up.weight", (s.hidden, s.latent))]
+
+        def load(self, src, rt):
+            super().load(src, rt)
+            self.w_c = src.get(self.spec.prefix + "down.weight").float()
+            self.w_o = src.get(self.spec.prefix + "up.weight").float()
+
+        def forward_add(self, x, h, batch, cache):
+            pages, ps, W = cache.pages["latent"], cache.page_size, self.spec.window
+            t = 0
+            for e in batch.entries:
+                n = len(e.tokens)
+                c = x[t:t + n].float() @ self.w_c.T
+                row = cache.block_table[e.slot].long()
+                new = torch.arange(e.start, e.start + n, device=x.device)
+                assert int(row[new // ps].min()) >= 0
+                pages[row[new // ps], new % ps] = c
+                lo = 0 if W is None else max(0, e.start - W + 1)
+                old = torch.arange(lo, e.start + n, device=x.device)
+                assert int(row[old // ps].min()) >= 0, "a position inside the window has lost its page"
+                ctx = pages[row[old // ps], old % ps]                     # [keys, latent], read back from the pages
+                sc = (c @ ctx.T) / math.sqrt(self.spec.latent)
+                vis = old[None, :] <= new[:, None]
+                if W is not None:
+                    vis &= old[None, :] > new[:, None] - W
+                p = torch.softmax(sc.masked_fill(~vis, float("-inf")), dim=-1)
+                h[t:t + n] += (p @ ctx) @ self.w_o.T
+                t += n
+
+    register_part("toy_latent_attention", LatentAttention, replace=True)
+
+
+@pytest.mark.parametrize("window", [None, 6])
+def test_toy_mixer_with_one_vector_per_position_in_pages(tmp_path, window):
+    """A mixer declares its own paged payload (one 24-wide vector per position, 32-bit, no keys and values); the
+    manager gives it pages and a block table like any other layer, in a group of its own when its window differs,
+    gives pages back past the window and at the end, and another request uses them again."""
+    import ferrox_b200
+    import replay_util as ru
+    from ferrox_b200 import Engine, register_architecture
+    from ferrox_b200.parts.specs import AttentionSpec, BlockSpec, DenseMlpSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry
+
+    _register_latent_mixer()
+    H, L = 40, 24
+
+    def model_spec(c):
+        def block(l, mixer):
+            p = f"model.layers.{l}."
+            return BlockSpec(NormSpec(H, 1e-6, p + "input_layernorm."), mixer, NormSpec(H, 1e-6, p + "post_attention_layernorm."),
+                             DenseMlpSpec(H, 56, p + "mlp."))
+
+        attn = AttentionSpec(hidden=H, n_heads=2, n_kv_heads=2, head_dim=16, qkv_bias=False,
+                             position=PositionSpec(16, 10000.0), window=None, prefix="model.layers.1.self_attn.")
+        layers = (block(0, LatentAttentionSpec(H, L, window, "model.layers.0.mix.")), block(1, attn))
+        return ModelSpec(architecture="ToyLatentForCausalLM", vocab_size=83, hidden=H, max_positions=64, layers=layers,
+                         schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1)),
+                         final_norm=NormSpec(H, 1e-6, "model.norm."), head_name="lm_head.weight")
+
+    register_architecture("ToyLatentForCausalLM", dict, model_spec, replace=True)
+    folder = ferrox_b200.write_random_model(str(tmp_path / "toy4"), dict(architectures=["ToyLatentForCausalLM"]),
+                                            seed=8, std=0.3, norm_init="around_one")
+    w = {k: v.float() for k, v in plain.read_safetensors(folder + "/model.safetensors").items()}
+    acfg = dict(num_attention_heads=2, num_key_value_heads=2, head_dim=16, hidden_size=H, rope_theta=10000.0,
+                num_hidden_layers=2)
+
+    def whole(toks):
+        T = len(toks)
+        x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+        n = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], 1e-6)
+        c = n @ w["model.layers.0.mix.down.weight"].T
+        t = torch.arange(T)
+        vis = t[None, :] <= t[:, None]
+        if window is not None:
+            vis &= t[None, :] > t[:, None] - window
+        p = torch.softmax(((c @ c.T) / math.sqrt(L)).masked_fill(~vis, float("-inf")), dim=-1)
+        x = x + (p @ c) @ w["model.layers.0.mix.up.weight"].T
+        x = x + plain.dense_block(plain.rms_norm(x, w["model.layers.0.post_attention_layernorm.weight"], 1e-6), w, 0)
+        n = plain.rms_norm(x, w["model.layers.1.input_layernorm.weight"], 1e-6)
+        x = x + plain.attention_block(n, w, acfg, 1, t)
+        x = x + plain.dense_block(plain.rms_norm(x, w["model.layers.1.post_attention_layernorm.weight"], 1e-6), w, 1)
+        return plain.rms_norm(x, w["model.norm.weight"], 1e-6) @ w["lm_head.weight"].T
+
+    g = torch.Generator().manual_seed(1)
+    prompts = {f"r{i}": torch.randint(0, 83, (n,), generator=g).tolist() for i, n in enumerate((31, 9, 22, 40, 17))}
+    want = {r: whole(t) for r, t in prompts.items()}
+    # so few pages that they are used again: 3 live requests of up to 40 positions, pages of 4
+    eng = Engine.from_folder(folder, dtype="float32", page_size=4, n_pages=3 * 10, max_slots=3)
+    assert set(eng.cache.groups) == ({None} if window is None else {None, window})
+    lat = eng.cache.layer_cache(0)
+    assert lat.k is None and lat.pages["latent"].shape == (30, 4, L) and lat.pages["latent"].dtype == torch.float32
+    got = ru.run_mixed(eng, prompts, seed=3, max_live=3, max_portion=7)
+    for r in prompts:
+        assert rel(got[r], want[r]) < 3e-5, r
+    assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())
+    if window is not None:
+        assert eng.cache.peak_pages[window] < eng.cache.peak_pages[None]   # the windowed group gave pages back early

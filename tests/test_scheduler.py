@@ -26,7 +26,7 @@ class FakeEngine:
     """Keeps each slot's token history as the cache would keep keys and values."""
 
     def __init__(self, n_pages=8, page_size=4, max_slots=3, max_positions=64, window=None):
-        specs = [CacheSpec(kv=KvCacheSpec(1, 2, None)), CacheSpec(kv=KvCacheSpec(1, 2, window))]
+        specs = [CacheSpec(paged=KvCacheSpec(1, 2, None)), CacheSpec(paged=KvCacheSpec(1, 2, window))]
         self.cache = CacheManager(specs, page_size=page_size, n_pages=n_pages, max_slots=max_slots,
                                   max_positions=max_positions, device="cpu", dtype=torch.float32)
         self.history = {}

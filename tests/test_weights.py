@@ -145,3 +145,21 @@ def test_random_mode_is_seeded_and_order_free(tmp_path):
         json.dump({"weight_map": {n: ("p1.safetensors" if n in half else "p2.safetensors") for n in ta}}, f)
     mf = ModelFiles(str(tmp_path / "s"))
     assert all(torch.equal(mf.tensor(n), ta[n]) for n in ta)
+
+
+def test_the_random_rule_is_a_function_of_key_and_index_only():
+    """A tensor's values depend on (seed, name, element index) alone: a longer draw starts with the shorter one, an
+    odd length ends inside a pair, and the stream looks like N(mean, std)."""
+    from ferrox_b200.weights import random_init as ri
+
+    key = ri.tensor_key(3, "model.layers.0.mlp.gate.weight")
+    assert key == ri.tensor_key(3, "model.layers.0.mlp.gate.weight") != ri.tensor_key(4, "model.layers.0.mlp.gate.weight")
+    long = ri.normal_cpu(key, 200_001, 0.0, 1.0)
+    assert torch.equal(ri.normal_cpu(key, 777, 0.0, 1.0), long[:777])
+    assert abs(float(long.mean())) < 0.01 and abs(float(long.std()) - 1.0) < 0.01
+    assert 3.5 < float(long.abs().max()) < 6.5
+    # a normal's fourth moment, and no correlation inside the pairs that share a radius
+    assert abs(float((long ** 4).mean()) - 3.0) < 0.15
+    assert abs(float((long[0:-1:2] * long[1::2]).mean())) < 0.01
+    shifted = ri.normal_cpu(key, 1000, 1.0, 0.02)
+    assert abs(float(shifted.mean()) - 1.0) < 0.003 and abs(float(shifted.std()) - 0.02) < 0.003
