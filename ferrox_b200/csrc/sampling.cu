@@ -122,13 +122,13 @@ __global__ void __launch_bounds__(NT) sample_kernel(float* __restrict__ work, lo
     }
     float* p = work + (long)r * ld;
     const float* src = scores ? scores + (long)r * lds : p;
-    const float inv_t = 1.0f / temperature[r];
+    const float temp = temperature[r];   // the scores are divided by it, as the reference does (sampling.rs:129-131)
 
     float mx = -INFINITY;
-    for (int i = threadIdx.x; i < vocab; i += NT) mx = fmaxf(mx, src[i] * inv_t);
+    for (int i = threadIdx.x; i < vocab; i += NT) mx = fmaxf(mx, src[i] / temp);
     mx = block_max(mx, scratch);
     float sum = 0.f;
-    for (int i = threadIdx.x; i < vocab; i += NT) { const float e = expf(src[i] * inv_t - mx); p[i] = e; sum += e; }
+    for (int i = threadIdx.x; i < vocab; i += NT) { const float e = expf(src[i] / temp - mx); p[i] = e; sum += e; }
     sum = block_sum(sum, scratch);
     for (int i = threadIdx.x; i < vocab; i += NT) p[i] = sum > 0.f ? p[i] / sum : 1.0f / (float)vocab;
     __syncthreads();

@@ -66,15 +66,18 @@ def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True, grap
         last_h2d_bytes = batch.h2d_bytes
         with ops.stream_scope(batch.stream):
             logits = model.forward(batch, lambda entry: cache.layer_cache(entry.cache, entry.writes_cache))
-    for e in entries:
-        cache.commit(e.slot, e.start + len(e.tokens))
     if check:
         code = int(status.item())
         if code:
+            # The requests' lengths have not advanced: the step counts as not run (its pages stay mapped, which a
+            # later step of the same requests finds done).  Parts put back what an aborted kernel may have left.
             status.zero_()
+            model.reset_after_fault()
             what = {1: "a token id outside the vocabulary", 2: "a position without a cache page",
                     3: "a bounded wait that ran out inside a tensor-core kernel"}.get(code, code)
             raise StepFault(f"step met {what}")
+    for e in entries:
+        cache.commit(e.slot, e.start + len(e.tokens))
     return logits
 
 
@@ -306,4 +309,5 @@ class DecodeAhead:
         code = int(status.item())
         if code:
             status.zero_()
+            self.model.reset_after_fault()
             raise StepFault(f"a step issued ahead met fault code {code}")

@@ -106,6 +106,12 @@ class GqaAttention(Mixer):
         self._range_counters = (torch.zeros(RANGE_COUNTERS, dtype=torch.int32, device=rt.device)
                                 if rt.device.type == "cuda" else None)
 
+    def reset_after_fault(self):
+        # blocks that gave up never counted themselves: the counters of the merge must start at zero again
+        if self._range_counters is not None:
+            self._range_counters.zero_()
+        self.position.reset_after_fault()
+
     def forward_add(self, x, h, batch, cache):
         s = self.spec
         T = x.shape[0]

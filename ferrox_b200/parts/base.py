@@ -52,6 +52,10 @@ class Part:
     def load(self, src, rt: Runtime) -> None:
         self.rt = rt
 
+    def reset_after_fault(self) -> None:
+        """Called after a step whose kernels raised the status word: put back any device-side scratch that an
+        aborted kernel may have left half-used.  Parts that own parts pass the call on."""
+
 
 class Norm(Part):
     def forward(self, h: torch.Tensor, rows=None) -> torch.Tensor:  # pragma: no cover - interface

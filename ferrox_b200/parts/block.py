@@ -29,6 +29,10 @@ class PreNormBlock(Block):
         for part in (self.norm1, self.mixer, self.norm2, self.ffn):
             part.load(src, rt)
 
+    def reset_after_fault(self):
+        for part in (self.norm1, self.mixer, self.norm2, self.ffn):
+            part.reset_after_fault()
+
     @property
     def graph_safe(self):
         return all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.ffn))

@@ -61,6 +61,11 @@ class DecoderModel(Part):
         self.final_norm.load(src, rt)
         self.head = self.embedding if s.head_name is None else src.get(s.head_name)
 
+    def reset_after_fault(self) -> None:
+        for layer in self.layers:
+            layer.reset_after_fault()
+        self.final_norm.reset_after_fault()
+
     def graph_safe(self) -> bool:
         return all(l.graph_safe for l in self.layers) and self.final_norm.graph_safe
 

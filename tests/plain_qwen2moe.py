@@ -182,13 +182,49 @@ def router_margins(x, w, cfg, l):
 def moe_block(x, w, cfg, l, chosen=None):
     """Router, routed experts summed in rank order, shared expert scaled by
     sigmoid(w_sg . x) (crates/ferrox-moe/src/lib.rs:735-752;
-    crates/ferrox-models/src/decoder.rs:2660-2681)."""
+    crates/ferrox-models/src/decoder.rs:2660-2681).  The tokens that chose an expert go
+    through it together (the reference buckets tokens by expert the same way,
+    decoder.rs:2792-2890); every token's outputs are then added in the order of its ranks."""
+    p = f"model.layers.{l}.mlp."
+    T = x.shape[0]
+    k, renorm = cfg["num_experts_per_tok"], cfg.get("norm_topk_prob", False)
+    router_logits = x @ w[p + "gate.weight"].T
+    picks = [route(router_logits[t], k, renorm, chosen) for t in range(T)]
+    by_expert = {}
+    for t, (experts, _) in enumerate(picks):
+        for e in experts:
+            by_expert.setdefault(e, []).append(t)
+    expert_out = {}
+    for e, rows in by_expert.items():
+        y = swiglu_mlp(x[rows], w[p + f"experts.{e}.gate_proj.weight"], w[p + f"experts.{e}.up_proj.weight"],
+                       w[p + f"experts.{e}.down_proj.weight"])
+        for i, t in enumerate(rows):
+            expert_out[(t, e)] = y[i]
+    out = torch.zeros_like(x)
+    for t, (experts, wts) in enumerate(picks):
+        y = torch.zeros_like(x[t])
+        for e, wt in zip(experts, wts):
+            y = y + wt * expert_out[(t, e)]
+        out[t] = y
+    if p + "shared_expert.gate_proj.weight" in w:
+        s = swiglu_mlp(x, w[p + "shared_expert.gate_proj.weight"], w[p + "shared_expert.up_proj.weight"],
+                       w[p + "shared_expert.down_proj.weight"])
+        if p + "shared_expert_gate.weight" in w:
+            g = torch.sigmoid(x @ w[p + "shared_expert_gate.weight"].reshape(-1))
+            s = s * g[:, None]
+        out = out + s
+    return out
+
+
+def moe_block_token_by_token(x, w, cfg, l):
+    """The same block one token at a time, as the reference's single-token path runs it
+    (crates/ferrox-moe/src/lib.rs:735-752); kept to check the bucketed form above."""
     p = f"model.layers.{l}.mlp."
     out = torch.zeros_like(x)
     k, renorm = cfg["num_experts_per_tok"], cfg.get("norm_topk_prob", False)
     router_logits = x @ w[p + "gate.weight"].T
     for t in range(x.shape[0]):
-        experts, wts = route(router_logits[t], k, renorm, chosen)
+        experts, wts = route(router_logits[t], k, renorm)
         y = torch.zeros_like(x[t])
         for e, wt in zip(experts, wts):
             y = y + wt * swiglu_mlp(

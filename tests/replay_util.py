@@ -15,13 +15,28 @@ def plain_logits(folder: str, prompts: Dict[str, List[int]], dtype=torch.float32
     return {rid: plain.forward(cfg, w, toks).to(torch.float32) for rid, toks in prompts.items()}
 
 
+def drawn_model(cfg: dict, seed: int, std: float = 0.02, norm_init: str = "around_one", device="cuda:0"):
+    """(cfg, tensors) for the plain implementation, without a folder: the values that the random-weights mode gives
+    this configuration and seed (stored as bfloat16, as a folder written by it holds them), drawn on the device,
+    where a model of the real widths takes a moment, and copied to the host in 32 bits.  The engine made by
+    ``Engine.from_random(cfg, seed=..., on_device=True)`` with the same arguments holds the same values."""
+    from ferrox_b200.config.registry import resolve
+    from ferrox_b200.parts.build import build_model
+    from ferrox_b200.weights.random_init import random_tensors
+
+    decls = build_model(resolve(cfg)[1]).tensor_decls()
+    w = {n: t.cpu().float() for n, t in random_tensors(decls, seed, torch.bfloat16, std, norm_init, device)}
+    return cfg, w
+
+
 class Expected:
     """Plain logits per request plus, per position, the router's smallest relative
     margin over the layers (see plain.router_margins)."""
 
-    def __init__(self, folder: str, prompts: Dict[str, List[int]], one_layer: bool = False):
-        """``one_layer``: keep what `close_to_a_choice` needs (a model of one layer only)."""
-        self.cfg, self.w = plain.load_model(folder, torch.float32)
+    def __init__(self, model, prompts: Dict[str, List[int]], one_layer: bool = False):
+        """``model``: a model folder, or (cfg, tensors) as :func:`drawn_model` gives them.
+        ``one_layer``: keep what `close_to_a_choice` needs (a model of one layer only)."""
+        self.cfg, self.w = plain.load_model(model, torch.float32) if isinstance(model, str) else model
         self.logits, self.margins, self.ffn_inputs = {}, {}, {}
         for rid, toks in prompts.items():
             if one_layer:

@@ -70,3 +70,16 @@ def test_reference_generator():
     assert h.next_u64() == s
     draws = [XorShift64(5).next_f32() for _ in range(3)]
     assert draws[0] == draws[1] and all(0.0 <= d < 1.0 for d in draws)
+
+
+def test_experts_in_buckets_equal_experts_token_by_token(tmp_path):
+    """The feed-forward with the tokens of an expert taken together against the same block one token at a time
+    (the reference runs both forms: crates/ferrox-moe/src/lib.rs:735-752 and decoder.rs:2792-2890)."""
+    from ferrox_b200 import write_random_model
+    from tiny_configs import TINY_B
+
+    folder = write_random_model(str(tmp_path / "b"), TINY_B, seed=1, std=0.3, norm_init="around_one")
+    cfg, w = plain.load_model(folder, torch.float64)
+    x = torch.randn(23, TINY_B["hidden_size"], dtype=torch.float64, generator=torch.Generator().manual_seed(2))
+    a, b = plain.moe_block(x, w, cfg, 1), plain.moe_block_token_by_token(x, w, cfg, 1)
+    assert float((a - b).abs().max()) < 1e-12 * float(b.abs().max())

@@ -171,3 +171,56 @@ def test_the_same_trace_twice_gives_the_same_bits(folders, dtype):
         runs.append(ru.run_mixed(eng, prompts, seed=4))
     for rid in prompts:
         assert torch.equal(runs[0][rid], runs[1][rid]) and torch.equal(runs[0][rid], runs[2][rid])
+
+
+def test_a_fault_leaves_the_requests_where_they_were(folders, expected):
+    """A step whose kernels raised the status word (here: set by hand, no kernel is made to fault) counts as not
+    run: StepFault, the requests' lengths unchanged, the decode attention's merge counters zeroed again, and the
+    same tokens fed once more give the plain logits."""
+    from ferrox_b200 import StepEntry
+    from ferrox_b200.engine import step as stepmod
+
+    eng = engine(folders["A"], "bfloat16", page_size=64, n_pages=8, max_slots=2)
+    toks = prompts_for("A")["r2"]
+    slot = eng.open_request()
+    first = eng.step([StepEntry(slot, toks[:40], want=list(range(40)))]).cpu()
+    status = stepmod._status(eng.rt.device)
+    counters = eng.model.layers[0].mixer._range_counters
+    counters[:3] = 1          # what blocks that gave up half-way would leave behind
+    status.fill_(3)
+    with pytest.raises(stepmod.StepFault, match="bounded wait"):
+        eng.step([StepEntry(slot, toks[40:42], want=[0, 1])])
+    assert eng.cache.seq_len[slot] == 40 and int(status) == 0 and int(counters.abs().sum()) == 0
+    rest = [eng.step([StepEntry(slot, toks[i:i + 1], want=[0])]).cpu().clone() for i in range(40, len(toks))]
+    got = {"r2": torch.cat([first] + rest)}
+    compare(got, _Only(expected["A"], "r2"), TOL["bfloat16"], "after-fault/A/bfloat16")
+    eng.close_request(slot)
+    eng.cache.check_invariants()
+
+
+class _Only:
+    def __init__(self, want, rid):
+        self._want, self._rid, self.margins = want, rid, want.margins
+
+    def __iter__(self):
+        return iter([self._rid])
+
+    def __getitem__(self, rid):
+        return self._want[rid]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_head_size_that_is_no_multiple_of_16(tmp_path, dtype):
+    """head_dim 40: in bfloat16 neither tensor-core attention kernel takes it; prompts go through the general kernel
+    and decoding through the CUDA-core split-key kernel, against plain under mixed cuts."""
+    from ferrox_b200 import write_random_model
+    from tiny_configs import TINY_C
+
+    cfg = dict(TINY_C, head_dim=40)
+    folder = write_random_model(str(tmp_path / "c40"), cfg, seed=4, norm_init="around_one")
+    rng = random.Random(2)
+    prompts = {f"r{i}": [rng.randrange(cfg["vocab_size"]) for _ in range(n)] for i, n in enumerate((70, 2, 33, 96, 17))}
+    want = ru.Expected(folder, prompts)
+    eng = engine(folder, dtype, page_size=16, n_pages=4 * 6, max_slots=4)
+    compare(ru.run_mixed(eng, prompts, seed=8), want, TOL[dtype], f"mixed/head40/{dtype}")
+    compare(ru.run_tail_decode(eng, prompts, tail=20), want, TOL[dtype], f"tail/head40/{dtype}")
