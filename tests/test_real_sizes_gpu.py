@@ -285,5 +285,24 @@ def test_full_size_fp32_window_2048_sixteen_prompts_served_mixed():
     eng = Engine.from_random(cfg, seed=1, norm_init="around_one", dtype="float32", on_device=True, page_size=64,
                              n_pages={None: 4 * 47 + 4, W: 4 * 43 + 4}, max_slots=4)
     got = ru.run_mixed(eng, prompts, seed=17, max_live=4, max_portion=300)
-    check(got, want, 1e-4, False)
+    # Every position is compared.  Among 26,000 positions x 24 routers a few separate the fourth expert from the
+    # fifth by less than 32-bit sums taken in another order differ (the logits of long requests differ by 2e-5 at
+    # the end of 24 layers): there either choice is right, and the logits of that one position differ by parts in a
+    # thousand.  A position beyond the tolerance is excused only if plain's own router gap there is under 1e-4 of the
+    # token's largest router logit, and at most one position in a thousand may need the excuse.
+    tol, floor, tipped, total, worst, wrong = 1e-4, 1e-4, 0, 0, 0.0, []
+    for rid in prompts:
+        diff = (got[rid] - want[rid]).abs().max(dim=1).values / want[rid].abs().max()
+        total += diff.numel()
+        for t in (diff >= tol).nonzero().flatten().tolist():
+            if float(want.margins[rid][t]) < floor:
+                tipped += 1
+                diff[t] = 0.0
+            else:
+                wrong.append((rid, t, f"{float(diff[t]):.2e}", f"margin {float(want.margins[rid][t]):.2e}"))
+        worst = max(worst, float(diff.max()))
+    assert not wrong, (len(wrong), wrong[:40])
+    assert tipped <= total // 1000, (tipped, total)
+    left_out = tipped
+    print(f"full size: {total} positions, {left_out} excused for an undecided router, worst relative error {worst:.2e}")
     assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())
