@@ -1,15 +1,19 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape a2.7b|a14b]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape a2.7b|a14b] [--repeats 3]
 
 Default workload: the layer sizes of the Qwen1.5-MoE-A2.7B shape (24 layers, hidden
 2048, 16 heads of 128, 60 experts top-4 of width 1408, shared expert 5632, vocab
 151936) with random bfloat16 weights, 8 requests whose prompts of 2,048 random
 tokens are prefilled first and which then decode inside a 4,096-token context.  A
 "step" is one decode step of the whole batch.  ``value`` is decoded tokens per
-second timed on the device with CUDA events; ``e2e`` is the same through
-``Engine.generate`` with host token lists in and out.  One JSON line is printed.
+second timed on the device with CUDA events: the region of K steps is timed
+``--repeats`` times (the requests go on decoding) and the median region counts, with
+the spread of the regions beside it; ``e2e`` is the same through ``Engine.generate``
+with host token lists in and out.  Every point (the headline batch, batch 1 and 64,
+the prompt) carries its time, its bytes or flops and its fraction of the measured
+peak.  One JSON line is printed.
 The weights (tens of GB) and the cache are far larger than L2, so no flush between
 steps is needed.  ``--gpus N`` with N > 1 is not built: one line says so, exit 2.
 """
@@ -162,6 +166,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="further decode batch sizes for 'points' ('' = none)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--repeats", type=int, default=3, help="timed regions of --steps steps each; the median counts")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -183,7 +188,8 @@ def main() -> int:
     cfg = dict(shape, num_hidden_layers=args.layers)
     point_batches = [int(b) for b in args.points.split(",") if b.strip()]
     max_batch = max([args.batch] + point_batches)
-    total_new = args.warmup + args.steps + 2
+    args.repeats = max(1, args.repeats)
+    total_new = args.warmup + args.repeats * args.steps + 2
     ps = args.page_size
     pages_per_req = (PREFILL_TOKENS + 2 * total_new + 8 + ps - 1) // ps + 1
     t_load = time.time()
@@ -224,10 +230,19 @@ def main() -> int:
     pre_ms = statistics.median(pre_runs)
     pre_flops = prefill_flops(eng.config, PREFILL_TOKENS, args.layers)
     prefill = {"value": PREFILL_TOKENS / (pre_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
-               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
+               # a prompt of some 10 ms is neither a burst nor a seconds-long loop: the fraction is of the burst
+               # figure (the larger denominator); the one of the sustained figure stands beside it
+               "of": pk["source"] + " burst", "peak_tflops": pk["bf16_tflops"],
+               "frac_of_sustained": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12),
+               "flops": pre_flops, "runs_ms": pre_runs,
+               "spread_pct": 100.0 * (max(pre_runs) - min(pre_runs)) / pre_ms}
 
     # ---- decode ------------------------------------------------------------------
-    def decode_run(batch, steps, warmup, sample_clocks=False):
+    def decode_run(batch, steps, warmup, repeats, sample_clocks=False):
+        """``repeats`` timed regions of ``steps`` decode steps each, back to back on the same requests.  Returns the
+        regions' (ms per step, context length in the middle of the region), the kernels launched in one region and
+        the clock record over all regions."""
         slots = []
         for _ in range(batch):
             slot = eng.open_request()
@@ -241,44 +256,65 @@ def main() -> int:
             logits = eng.step([StepEntry(s, [t], want=[0]) for s, t in zip(slots, ids)], check=False)
             ids = ops.argmax(logits, out).tolist()
 
+        run_ids = [ids]
+
         def k_steps():
             # the engine's own way of decoding greedily: steps replayed from the CUDA graph of this batch size, issued
             # one ahead of the host, every step's tokens read back (one step late) from pinned memory
-            run = eng.decode_ahead(slots, ids)
+            run = eng.decode_ahead(slots, run_ids[0])
             if run is None:
                 for _ in range(steps):
                     one_step()
+                run_ids[0] = ids
                 return
+            last = run_ids[0]
             for _ in range(steps):
                 run.issue()
                 if run.issued - run.collected == 2:
-                    run.collect()
+                    last = run.collect()
             while run.collected < run.issued:
-                run.collect()
+                last = run.collect()
             run.close()
+            run_ids[0] = last
 
         for _ in range(warmup):
             one_step()
+        run_ids[0] = ids
         clocks = ClockSampler()
         if sample_clocks:
             clocks.start()
-        before = ops.launch_count()
-        ms = timed(k_steps)
-        launches = ops.launch_count() - before
+        regions, launches = [], 0
+        for r in range(repeats):
+            before = ops.launch_count()
+            ms = timed(k_steps)
+            launches = ops.launch_count() - before
+            ids = run_ids[0]
+            regions.append((ms / steps, PREFILL_TOKENS + warmup + r * steps + steps // 2))
         clk = clocks.stop() if sample_clocks else None
-        ctx_mid = PREFILL_TOKENS + warmup + steps // 2
         for s in slots:
             eng.close_request(s)
-        return ms / steps, launches, clk, ctx_mid
+        return regions, launches, clk
 
-    ms_step, launches, clk, ctx_mid = decode_run(args.batch, args.steps, args.warmup, sample_clocks=True)
-    value = args.batch / (ms_step / 1e3)
-    need = decode_bytes(eng.model, eng, args.batch, ctx_mid, args.layers)
-    achieved = need / (ms_step / 1e3) / 1e9
-    points = {}
+    def point(batch, regions):
+        """The median region of a decode point with its bytes, its fraction of the HBM peak and the regions' spread."""
+        order = sorted(regions)
+        ms, ctx = order[len(order) // 2]
+        need = decode_bytes(eng.model, eng, batch, ctx, args.layers)
+        achieved = need / (ms / 1e3) / 1e9
+        return {"value": batch / (ms / 1e3), "ms_per_step": ms, "context_at_timing": ctx, "bytes_per_step": need,
+                "achieved_gbs": achieved, "frac": achieved / pk["hbm_gbs"], "of": pk["source"], "repeats": len(regions),
+                "ms_per_step_all": [r[0] for r in regions],
+                "spread_pct": 100.0 * (order[-1][0] - order[0][0]) / ms}
+
+    regions, launches, clk = decode_run(args.batch, args.steps, args.warmup, args.repeats, sample_clocks=True)
+    head = point(args.batch, regions)
+    ms_step, value, ctx_mid, need, achieved = (head["ms_per_step"], head["value"], head["context_at_timing"],
+                                               head["bytes_per_step"], head["achieved_gbs"])
+    points, points_detail = {}, {}
     for b in point_batches:
-        pm, _, _, _ = decode_run(b, max(8, args.steps // 2), 3)
-        points[f"decode_b{b}"] = b / (pm / 1e3)
+        pr, _, _ = decode_run(b, args.steps, 3, args.repeats)
+        points_detail[f"decode_b{b}"] = point(b, pr)
+        points[f"decode_b{b}"] = points_detail[f"decode_b{b}"]["value"]
 
     # ---- end to end through Engine.generate ------------------------------------------
     e2e = None
@@ -313,10 +349,11 @@ def main() -> int:
             "prompt_tokens": PREFILL_TOKENS, "context_at_timing": ctx_mid, "page_size": ps, "parallelism": "single GPU",
             "l2": "weights and cache exceed L2, no flush", "load_s": round(load_s, 1),
         },
+        "repeats": args.repeats, "ms_per_step_all": head["ms_per_step_all"], "spread_pct": head["spread_pct"],
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "of": pk["source"], "bytes_per_step": need},
-        "points": points, "e2e": e2e, "gpu_launches": launches, "clocks": clk,
+        "points": points, "points_detail": points_detail, "e2e": e2e, "gpu_launches": launches, "clocks": clk,
     }
     print(json.dumps(line))
     return 0

@@ -225,6 +225,28 @@ class CacheManager:
         reads from new_len - W + 1 on."""
         self._ok(self._lib.fxh_commit(self._h, int(slot), int(new_len)), slot)
 
+    def reserve_step(self, slots: Sequence[int], counts: Sequence[int]) -> Optional[List[int]]:
+        """A whole step in one call: request ``slots[i]`` is to grow by ``counts[i]`` positions.  Pages are mapped for
+        every request or for none.  Returns the requests' lengths before the step, or None when the pages do not
+        suffice (nothing has been changed)."""
+        n = len(slots)
+        arr = (ctypes.c_int * (3 * n))(*slots, *counts)
+        ip = ctypes.cast(arr, ctypes.POINTER(ctypes.c_int))
+        rc = self._lib.fxh_reserve_step(self._h, n, ip, ctypes.cast(ctypes.addressof(arr) + 4 * n, type(ip)),
+                                        ctypes.cast(ctypes.addressof(arr) + 8 * n, type(ip)))
+        if rc == 1:
+            return None
+        self._ok(rc, list(slots))
+        return list(arr[2 * n:3 * n])
+
+    def commit_step(self, slots: Sequence[int], counts: Sequence[int]) -> None:
+        """The step has run: every request holds ``counts[i]`` positions more."""
+        n = len(slots)
+        arr = (ctypes.c_int * (2 * n))(*slots, *counts)
+        ip = ctypes.cast(arr, ctypes.POINTER(ctypes.c_int))
+        self._ok(self._lib.fxh_commit_step(self._h, n, ip, ctypes.cast(ctypes.addressof(arr) + 4 * n, type(ip))),
+                 list(slots))
+
     def held_pages(self, slot: int) -> Dict[object, List[int]]:
         out = {}
         for g in self._order:

@@ -182,6 +182,44 @@ int fxh_commit(void* h, int slot, int new_len)
     return FXH_OK;
 }
 
+// One step's reservation in one call: request slots[i] grows by add[i] positions.  Pages are mapped for all of them or
+// for none (FXH_NO: nothing has been changed); starts[i] receives the request's length before the step.  The slots
+// must be distinct.
+int fxh_reserve_step(void* h, int n, const int* slots, const int* add, int* starts)
+{
+    Cache* c = static_cast<Cache*>(h);
+    for (int i = 0; i < n; ++i) {
+        if (!check_live(c, slots[i]) || add[i] < 0) return FXH_BAD_SLOT;
+        if (c->seq_len[slots[i]] + add[i] > c->max_positions) return FXH_TOO_LONG;
+    }
+    for (const Group& G : c->groups) {
+        long need = 0;
+        for (int i = 0; i < n; ++i) {
+            const int d = pages_for(*c, c->seq_len[slots[i]] + add[i]) - G.n_logical[slots[i]];
+            if (d > 0) need += d;
+        }
+        if (need > (long)G.free_list.size()) return FXH_NO;
+    }
+    for (int i = 0; i < n; ++i) {
+        starts[i] = c->seq_len[slots[i]];
+        const int rc = fxh_reserve(h, slots[i], starts[i] + add[i]);
+        if (rc != FXH_OK) return rc < 0 ? rc : FXH_CORRUPT;   // cannot happen after the count above
+    }
+    return FXH_OK;
+}
+
+// The step has run: every request's length advances by add[i] (windowed groups give back what fell out).
+int fxh_commit_step(void* h, int n, const int* slots, const int* add)
+{
+    Cache* c = static_cast<Cache*>(h);
+    for (int i = 0; i < n; ++i) {
+        if (!check_live(c, slots[i])) return FXH_BAD_SLOT;
+        const int rc = fxh_commit(h, slots[i], c->seq_len[slots[i]] + add[i]);
+        if (rc != FXH_OK) return rc;
+    }
+    return FXH_OK;
+}
+
 int32_t* fxh_table(void* h, int group) { return static_cast<Cache*>(h)->groups[group].table.data(); }
 int fxh_free_pages(void* h, int group) { return (int)static_cast<Cache*>(h)->groups[group].free_list.size(); }
 int fxh_peak_pages(void* h, int group) { return static_cast<Cache*>(h)->groups[group].peak; }

@@ -40,20 +40,16 @@ def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True, grap
         if len(e.tokens) == 0:
             raise ValueError("an entry must bring at least one token")
         seen.add(e.slot)
-        e.start = cache.seq_len[e.slot]
         vocab = model.spec.vocab_size
         if min(e.tokens) < 0 or max(e.tokens) >= vocab:
             raise ValueError(f"token id outside the vocabulary of {vocab}")
-    # all-or-nothing reservation across the entries
-    wanted = {}
-    for e in entries:
-        for key, n in cache.pages_needed(e.slot, e.start + len(e.tokens)).items():
-            wanted[key] = wanted.get(key, 0) + n
-    if not cache.can_reserve(wanted):
-        raise OutOfPages(f"step needs {wanted} pages, free: {cache.free_pages()}")
-    for e in entries:
-        ok = cache.reserve(e.slot, e.start + len(e.tokens))
-        assert ok
+    # all-or-nothing reservation across the entries, in one call of the native book-keeping
+    slots, counts = [e.slot for e in entries], [len(e.tokens) for e in entries]
+    starts = cache.reserve_step(slots, counts)
+    if starts is None:
+        raise OutOfPages(f"step of {sum(counts)} tokens does not fit the free pages {cache.free_pages()}")
+    for e, st in zip(entries, starts):
+        e.start = st
     cache.sync_tables()
 
     status = _status(model.rt.device)
@@ -76,8 +72,7 @@ def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True, grap
             what = {1: "a token id outside the vocabulary", 2: "a position without a cache page",
                     3: "a bounded wait that ran out inside a tensor-core kernel"}.get(code, code)
             raise StepFault(f"step met {what}")
-    for e in entries:
-        cache.commit(e.slot, e.start + len(e.tokens))
+    cache.commit_step(slots, counts)
     return logits
 
 
@@ -256,6 +251,7 @@ class DecodeAhead:
         self.model, self.cache, self.graphs = model, cache, graphs
         self.slots, self.first_tokens = list(slots), list(tokens)
         self.B = len(self.slots)
+        self._ones = [1] * self.B
         self.issued = self.collected = 0
         self.sampling = None
         if sampling is not None and any(not p.greedy for p, _ in sampling):
@@ -273,16 +269,9 @@ class DecodeAhead:
         replays the step."""
         global last_h2d_bytes
         cache = self.cache
-        starts = [cache.seq_len[s] for s in self.slots]
-        wanted = {}
-        for s, st in zip(self.slots, starts):
-            for key, n in cache.pages_needed(s, st + 1).items():
-                wanted[key] = wanted.get(key, 0) + n
-        if not cache.can_reserve(wanted):
-            raise OutOfPages(f"step needs {wanted} pages, free: {cache.free_pages()}")
-        for s, st in zip(self.slots, starts):
-            ok = cache.reserve(s, st + 1)
-            assert ok
+        starts = cache.reserve_step(self.slots, self._ones)
+        if starts is None:
+            raise OutOfPages(f"a decode step of {self.B} requests does not fit the free pages {cache.free_pages()}")
         cache.sync_tables()
         first = self.issued == 0
         step_sampling = None
@@ -294,8 +283,7 @@ class DecodeAhead:
         self.graphs.replay_ahead(self.B, starts, self.slots, self.first_tokens if first else None, self.issued & 1,
                                  step_sampling)
         last_h2d_bytes = ((20 if first else 16) + (20 if step_sampling else 0)) * self.B
-        for s, st in zip(self.slots, starts):
-            cache.commit(s, st + 1)
+        cache.commit_step(self.slots, self._ones)
         self.issued += 1
 
     def collect(self):

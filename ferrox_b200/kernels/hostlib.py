@@ -68,6 +68,7 @@ def load() -> ctypes.CDLL:
                 "fxh_open": ([P], I), "fxh_close": ([P, I], I),
                 "fxh_pages_needed": ([P, I, I, IP], I),
                 "fxh_reserve": ([P, I, I], I), "fxh_commit": ([P, I, I], I),
+                "fxh_reserve_step": ([P, I, IP, IP, IP], I), "fxh_commit_step": ([P, I, IP, IP], I),
                 "fxh_table": ([P, I], ctypes.POINTER(ctypes.c_int32)),
                 "fxh_free_pages": ([P, I], I), "fxh_peak_pages": ([P, I], I), "fxh_free_slots": ([P], I),
                 "fxh_seq_len": ([P, I], I), "fxh_first_page": ([P, I, I], I), "fxh_n_logical": ([P, I, I], I),

@@ -131,3 +131,29 @@ def test_random_orders_lose_nothing(seed):
         m.close_request(s)
     m.check_invariants()
     assert all(n == m.groups[k].pool.n_pages for k, n in m.free_pages().items())
+
+
+def test_a_whole_step_is_reserved_for_all_requests_or_for_none():
+    """The step function's one call: several requests grow together; if the pages do not suffice for all of them,
+    none gets any; the lengths advance only at commit, and a windowed group then lets go of what fell out."""
+    m = manager(n_pages=6, page_size=4, window=6, max_slots=3)
+    a, b, c = m.open_request(), m.open_request(), m.open_request()
+    assert m.reserve_step([a, b], [9, 4]) == [0, 0]          # 3 + 1 pages in both groups
+    assert m.free_pages() == {None: 2, 6: 2} and m.seq_len[a] == 0
+    m.commit_step([a, b], [9, 4])
+    assert (m.seq_len[a], m.seq_len[b]) == (9, 4)
+    assert m.held_pages(a) == {None: [0, 1, 2], 6: [1, 2]}   # the next query at 9 reads from 4 on
+    before = (m.free_pages(), m.held_pages(a), m.held_pages(b), m.held_pages(c))
+    # a needs 1 page more, b 1, c 2: four pages where the full group has two free
+    assert m.reserve_step([a, b, c], [4, 4, 5]) is None
+    assert before == (m.free_pages(), m.held_pages(a), m.held_pages(b), m.held_pages(c))
+    assert m.reserve_step([a, b], [4, 4]) == [9, 4]
+    m.commit_step([a, b], [4, 4])
+    assert (m.seq_len[a], m.seq_len[b]) == (13, 8) and m.free_pages()[None] == 0
+    with pytest.raises(CacheError):
+        m.reserve_step([a, 7], [1, 1])                        # a slot no request holds
+    m.check_invariants()
+    for s in (a, b, c):
+        m.close_request(s)
+    assert m.free_pages() == {None: 6, 6: 6}
+    m.check_invariants()
