@@ -27,7 +27,7 @@ import time
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="ferrox", description="Qwen2-MoE generation on one B200")
+    ap = argparse.ArgumentParser(prog="ferrox", description="generation on one B200 with the model that config.json names")
     ap.add_argument("-m", "--model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("--random", metavar="CONFIG_JSON", help="random weights for this config.json instead of -m")
     ap.add_argument("--weights-seed", type=int, default=0, help="seed of --random")
@@ -44,6 +44,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("-e", "--escape", action="store_true", help="process \\n \\t \\r \\\\ in -p")
     ap.add_argument("--ignore-eos", action="store_true", help="do not stop at the end-of-sequence token")
     ap.add_argument("--verbose-prompt", action="store_true", help="print the prompt's token ids first")
+    ap.add_argument("--trace-kernels", action="store_true",
+                    help="sum the device time of every class of kernel and print the table to stderr at the end "
+                         "(launches then run one by one, without CUDA graphs: for looking, not for speed)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--num-pages", type=int, default=0, help="cache pages per layer group (0 = one context's worth)")
@@ -69,6 +72,8 @@ def main(argv=None) -> int:
     from .engine.scheduler import Scheduler, encode_prompt
     from .sampling.sampler import SamplingParams
 
+    if args.trace_kernels:
+        Engine.trace_start()   # before the engine is made: it then leaves CUDA graphs off
     t0 = time.time()
     cache = dict(page_size=args.page_size, max_slots=4)
     if args.ctx_size:
@@ -149,6 +154,12 @@ def main(argv=None) -> int:
     ptps = len(prompt) / prefill_secs if prefill_secs > 0 else 0.0
     dtps = max(0, n_gen - 1) / decode_secs if decode_secs > 0 else 0.0
     print(f"ferrox: prompt {len(prompt)} tokens, {ptps:.2f} t/s; predict {n_gen} tokens, {dtps:.2f} t/s", file=sys.stderr)
+    if args.trace_kernels:
+        times = Engine.trace_stop()
+        total = sum(ms for _, ms in times.values()) or 1.0
+        print("ferrox: device time by part and entry point (launches one by one, no graphs):", file=sys.stderr)
+        for key, (n, ms) in sorted(times.items(), key=lambda kv: -kv[1][1]):
+            print(f"ferrox:   {key:40s} {n:7d} launches {ms:10.3f} ms {100.0 * ms / total:5.1f} %", file=sys.stderr)
     return 0
 
 

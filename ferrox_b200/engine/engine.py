@@ -60,8 +60,12 @@ class Engine:
             model.cache_specs(), page_size=page_size, n_pages=n_pages, max_slots=max_slots,
             max_positions=max_positions, device=self.rt.device, dtype=self.rt.dtype,
         )
-        # decode steps replay CUDA graphs when every part of the model can be captured
-        self.graphs = GraphedDecode(model, self.cache) if cuda_graphs and model.graph_safe() else None
+        # decode steps replay CUDA graphs when every part of the model can be captured (and no kernel trace is on:
+        # a replayed graph's kernels cannot be timed one by one)
+        from ..kernels import ops
+
+        traced = ops.trace_enabled()
+        self.graphs = GraphedDecode(model, self.cache) if cuda_graphs and not traced and model.graph_safe() else None
 
     # ---- construction ---------------------------------------------------------
     @classmethod
@@ -119,6 +123,21 @@ class Engine:
         if not DecodeAhead.ready(self.graphs, len(slots)):
             return None
         return DecodeAhead(self.model, self.cache, self.graphs, slots, tokens, sampling)
+
+    # ---- tracing ------------------------------------------------------------------
+    @staticmethod
+    def trace_start() -> None:
+        """Device time per class of kernel from now on (see ``kernels.ops``): call before the engine is made, so
+        that it leaves CUDA graphs off; :meth:`trace_stop` returns the sums."""
+        from ..kernels import ops
+
+        ops.trace_start()
+
+    @staticmethod
+    def trace_stop() -> dict:
+        from ..kernels import ops
+
+        return ops.trace_stop()
 
     # ---- generation -------------------------------------------------------------
     def generate(self, prompts, max_new_tokens=128, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0,

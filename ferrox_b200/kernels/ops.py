@@ -33,6 +33,7 @@ class KernelError(RuntimeError):
 
 _P, _I, _L, _F = c_void_p, c_int, c_long, c_float
 _SIGNATURES = {
+    "fx_set_pdl": [_I],
     "fx_gemm": [_P, _I, _L, _P, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P, _I, _L, _P],
     "fx_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
     "fx_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
@@ -100,11 +101,72 @@ def register_signature(name: str, argtypes) -> None:
 def call(name: str, *args) -> None:
     global _launches
     _launches += _KERNELS.get(name, 1)
+    if _trace is not None:
+        return _call_traced(name, args)
     rc = _get(name)(*args)
     if rc != 0:
         if rc > 0:
             raise KernelError(f"{name}: CUDA error {rc} at launch ({torch.cuda.get_device_name()})")
         raise KernelError(f"{name}: refused: {_ERRORS.get(rc, rc)}")
+
+
+# ---- tracing: device time per class of kernel, behind a switch -------------------------------------------
+# The reference prints phase rates only (crates/ferrox-cli/src/run.rs:680-695); with the switch on, every entry
+# point's launches are bracketed by CUDA events on their own stream and summed by (scope, entry point), where the
+# scope is what the parts announce with :class:`trace_scope` (mixer, feed-forward, norm, head ...).  Launches then
+# run without programmatic dependent launch, so that a kernel's time is its own; the engine leaves CUDA graphs off.
+_trace = None          # None: off; else {key: [n_calls, [(start event, end event), ...]]}
+_trace_scope = []
+
+
+def trace_enabled() -> bool:
+    return _trace is not None
+
+
+def trace_start() -> None:
+    global _trace
+    _trace = {}
+    _get("fx_set_pdl")(0)
+
+
+def trace_stop() -> dict:
+    """Ends tracing; returns {"scope:entry point": (launches, milliseconds on the device)}."""
+    global _trace
+    t, _trace = _trace or {}, None
+    _get("fx_set_pdl")(1)
+    torch.cuda.synchronize()
+    return {k: (n, sum(a.elapsed_time(b) for a, b in evs)) for k, (n, evs) in t.items()}
+
+
+class trace_scope:
+    """Names the part whose kernels follow (no cost while tracing is off)."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _trace is not None:
+            _trace_scope.append(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if _trace is not None and _trace_scope:
+            _trace_scope.pop()
+        return False
+
+
+def _call_traced(name: str, args) -> None:
+    stream = torch.cuda.ExternalStream(args[-1]) if args and isinstance(args[-1], int) and args[-1] else torch.cuda.current_stream()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    rc = _get(name)(*args)
+    b.record(stream)
+    if rc != 0:
+        raise KernelError(f"{name}: status {rc}")
+    key = f"{_trace_scope[-1] if _trace_scope else '-'}:{name}"
+    rec = _trace.setdefault(key, [0, []])
+    rec[0] += _KERNELS.get(name, 1)
+    rec[1].append((a, b))
 
 
 _scoped_stream = None

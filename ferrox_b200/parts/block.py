@@ -8,6 +8,7 @@ whatever norm, mixer and feed-forward its spec names.
 """
 from __future__ import annotations
 
+from ..kernels import ops
 from .base import Block, build_part, register_part
 
 
@@ -42,11 +43,17 @@ class PreNormBlock(Block):
     def forward(self, h, batch, cache, x=None, then_norm=None):
         """``x``: norm1(h) if the block before has computed it.  ``then_norm``: the first norm of the block that runs
         next; its output on the new h is returned if the feed-forward's last kernel applied it, else None."""
-        self.mixer.forward_add(x if x is not None else self.norm1.forward(h), h, batch, cache)
-        x2 = self.norm2.forward(h)
-        if then_norm is not None and self.ffn.fuses_norm:
-            return self.ffn.forward_add(x2, h, batch, then_norm=then_norm)
-        self.ffn.forward_add(x2, h, batch)
+        if x is None:
+            with ops.trace_scope("norm"):
+                x = self.norm1.forward(h)
+        with ops.trace_scope("mixer"):
+            self.mixer.forward_add(x, h, batch, cache)
+        with ops.trace_scope("norm"):
+            x2 = self.norm2.forward(h)
+        with ops.trace_scope("feed-forward"):
+            if then_norm is not None and self.ffn.fuses_norm:
+                return self.ffn.forward_add(x2, h, batch, then_norm=then_norm)
+            self.ffn.forward_add(x2, h, batch)
         return None
 
 

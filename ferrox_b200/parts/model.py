@@ -92,7 +92,8 @@ class DecoderModel(Part):
         """``caches(entry) -> LayerCache``.  Returns [len(want_rows), vocab] float32."""
         s, rt = self.spec, self.rt
         h = rt.empty(batch.n_tokens, s.hidden, dtype=torch.float32)
-        ops.embed(self.embedding, batch.token_ids, h, status=batch.status, stream=batch.stream)
+        with ops.trace_scope("embedding"):
+            ops.embed(self.embedding, batch.token_ids, h, status=batch.status, stream=batch.stream)
         x = None    # the next block's first norm of h, when the block before it has computed it
         for i, entry in enumerate(s.schedule):
             block = self.layers[entry.layer]
@@ -105,7 +106,8 @@ class DecoderModel(Part):
             x = block.forward(h, batch, caches(entry), x=x, then_norm=then)
         if batch.n_want == 0:
             return rt.empty(0, s.vocab_size, dtype=torch.float32)
-        x = self.final_norm.forward(h, rows=batch.want_rows)
-        logits = rt.empty(batch.n_want, s.vocab_size, dtype=torch.float32)
-        ops.linear(x, self.head, logits, status=batch.status, stream=batch.stream)
+        with ops.trace_scope("head"):
+            x = self.final_norm.forward(h, rows=batch.want_rows)
+            logits = rt.empty(batch.n_want, s.vocab_size, dtype=torch.float32)
+            ops.linear(x, self.head, logits, status=batch.status, stream=batch.stream)
         return logits

@@ -369,3 +369,25 @@ def test_trace_run_from_a_configuration_and_a_seed(folders, tmp_path):
         assert r.returncode == 0, r.stderr
         outs.append([np.fromfile(out / f"{k}.f32", dtype="<f4") for k in (0, 1)])
     assert all(np.array_equal(a, b) for a, b in zip(*outs)) and outs[0][0].size == 2 * TINY_B["vocab_size"]
+
+
+def test_kernel_trace_behind_its_switch(folders):
+    """With the switch on, device time is summed per part and entry point and generation gives the same tokens
+    (without graphs); with it off nothing is recorded."""
+    from ferrox_b200 import Engine
+    from ferrox_b200.kernels import ops
+
+    prompt = [5, 9, 200, 31]
+    want = engine(folders["A"]).generate([prompt], max_new_tokens=6)[0]
+    assert not ops.trace_enabled()
+    Engine.trace_start()
+    try:
+        eng = engine(folders["A"])
+        assert eng.graphs is None
+        got = eng.generate([prompt], max_new_tokens=6)[0]
+    finally:
+        times = Engine.trace_stop()
+    assert got == want and not ops.trace_enabled()
+    assert any(k.startswith("mixer:fx_decode_attention") for k in times) and "head:fx_rmsnorm" in times
+    assert all(n > 0 and ms > 0.0 for n, ms in times.values())
+    assert engine(folders["A"]).graphs is not None

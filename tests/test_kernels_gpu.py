@@ -564,7 +564,8 @@ def test_gemm_tc_gated(M, I, K):
 
 
 @pytest.mark.parametrize("counts", [[0, 130, 1, 0, 128, 255], [3, 0, 0, 0, 0, 700], [64, 64, 64, 64, 64, 64],
-                                    [137, 0, 512, 9] * 15])
+                                    [137, 0, 512, 9] * 15, [136] * 60, [129, 8, 260, 256, 257, 1, 384, 385, 127, 128],
+                                    [1000, 0, 0, 513]])
 def test_gemm_tc_grouped(counts):
     o = ops()
     G = len(counts)
