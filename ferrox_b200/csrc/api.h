@@ -38,9 +38,10 @@ int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void*
                        int n_kv_heads, int head_dim, int window, float scale, void* stream);
 
 int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
-                            const int* block_table, int table_width, int page_size, const int* tiles, int n_tiles,
+                            const int* block_table, int table_width, int page_size, const int* items, int n_items,
                             const int* seq_slot, void* out, long ldo, int n_heads, int n_kv_heads, int head_dim,
-                            int window, float scale, int* status, void* stream);
+                            int window, float scale, int* status, float* part_o, float* part_ml, const int* merges,
+                            int n_merges, void* stream);
 int fx_prefill_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table,
                          int table_width, int page_size, const int* tiles, int n_tiles, const int* seq_slot, void* out,
                          long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale, void* stream);

@@ -28,6 +28,14 @@
 // multiplied (with weight 0); the half of a block that lies beyond the request's pages is read from
 // page 0, which always holds finite values.
 //
+// A work item is a tile of queries, a head and a run of key blocks [kb_begin, kb_end).  The host cuts the
+// key blocks of long tiles into runs (the last 256 queries of a long prompt see many times the keys the
+// first see, and a portion behind a long cached prefix is a single tile with all of them), so that the
+// items are of similar length and there are enough of them for every SM; the heavy ones come first in the
+// table.  An item that holds all of its tile's key blocks writes the tile's output.  Any other writes what
+// it has (the unnormalised sums in 32 bits, and each row's reference maximum and sum of weights) into
+// scratch memory, and a second kernel (prefill_merge_kernel) adds a tile's runs up in their order.
+//
 // Reference: crates/ferrox-core/src/attention.rs:531-563 (query t over keys 0..=t), :146-175 (online
 // softmax), :484-524 (window), :572-610 (pages), :432-449 (grouped heads).  The mma.sync kernel of
 // attention_prefill.cu remains for other head sizes and page sizes.
@@ -47,10 +55,13 @@ __device__ __forceinline__ float fast_exp2(float x) {   // 2^x, approximate; -in
     return y;
 }
 
+constexpr int ITEM_INTS = 8;   // a work item: first flat token, rows, entry, first position, kb_begin, kb_end, part, -
+
 struct AttnArgs {
     const int* block_table; int table_width; int page_size;
     const int* tiles; const int* seq_slot;
     bf16* out; long ldo;
+    float* part_o; float* part_ml;   // partial results of items that hold a run of their tile's key blocks only
     int n_heads, n_kv_heads, window;
     float scale_log2e;
     int* status;
@@ -78,10 +89,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
     __shared__ uint32_t tmem_base_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // heavy tiles (late in their request) first
-    const int tile = gridDim.x - 1 - blockIdx.x;
-    const int tok0 = a.tiles[tile * 4], rows = a.tiles[tile * 4 + 1], entry = a.tiles[tile * 4 + 2], pos0 = a.tiles[tile * 4 + 3];
-    const int head = blockIdx.y;
+    // The host lists heavy items first, and blocks are handed out with blockIdx.x running fastest: every head's
+    // heaviest item, then every head's next one, so that the light items fill the gaps at the end.
+    const int* item = a.tiles + (long)blockIdx.y * ITEM_INTS;
+    const int tok0 = item[0], rows = item[1], entry = item[2], pos0 = item[3];
+    const int kb_begin = item[4], kb_end = item[5], part = item[6];
+    const int head = blockIdx.x;
     const int kvh = head / (a.n_heads / a.n_kv_heads);
     const int last_pos = pos0 + rows - 1;
     // sub-tile t: rows_of(t) rows from position pos0 + 128 t; it needs the key blocks blk_lo(t) .. blk_hi(t)
@@ -92,8 +105,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
         return (a.window > 0 && p - a.window + 1 > 0 ? p - a.window + 1 : 0) / BKEY;
     };
     auto blk_hi = [&](int t) { return (pos0 + t * BQ + rows_of(t) - 1) / BKEY; };
-    const int first_blk = blk_lo(0), last_blk = blk_hi(nt - 1);
-    auto active = [&](int t, int j) { return t < nt && j >= blk_lo(t) && j <= blk_hi(t); };
+    // the key blocks of sub-tile t inside this item's run: lo_t[t] .. hi_t[t] (none if lo > hi)
+    const int lo0 = max(blk_lo(0), kb_begin), hi0 = min(blk_hi(0), kb_end - 1);
+    const int lo1 = nt > 1 ? max(blk_lo(1), kb_begin) : 1, hi1 = nt > 1 ? min(blk_hi(1), kb_end - 1) : 0;
+    auto lo_of = [&](int t) { return t ? lo1 : lo0; };
+    auto hi_of = [&](int t) { return t ? hi1 : hi0; };
+    const bool act0 = lo0 <= hi0, act1 = lo1 <= hi1;
+    const int first_blk = act0 && act1 ? min(lo0, lo1) : act0 ? lo0 : lo1;
+    const int last_blk = act0 && act1 ? max(hi0, hi1) : act0 ? hi0 : hi1;
+    auto active = [&](int t, int j) { return t < 2 && j >= lo_of(t) && j <= hi_of(t); };
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar0 = base + L::BAR_OFF;
@@ -211,7 +231,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
                             tc_mma_ts(tmem_o(t), tmem_s(t) + 8u * ks, dv, idesc_o, (n_p[t] | ks) != 0);
                         }
                         ++n_p[t];
-                        if (j == blk_hi(t)) tc_commit(o_done(t));
+                        if (j == hi_of(t)) tc_commit(o_done(t));
                     }
                     if (t == nt - 1) tc_commit(kv_empty(b));   // every product that reads this stage has been issued
                     if (active(t, j + 1)) ok = issue_s(t, j + 1);
@@ -234,8 +254,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
             float m = -INFINITY, l = 0.f;
             bool ok = true;
             int cnt = 0;
-            const int hi = blk_hi(t);
-            for (int j = blk_lo(t); j <= hi; ++j, ++cnt) {
+            const int hi = hi_of(t);
+            for (int j = lo_of(t); j <= hi; ++j, ++cnt) {
                 ok = __all_sync(0xffffffffu, mbar_wait(s_full(t), (uint32_t)(cnt & 1), abort_flag));
                 if (!ok) break;
                 tc_fence_after();
@@ -316,8 +336,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full(t));
             }
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done(t), 0, abort_flag));
-            if (ok) {
+            const bool has_blocks = lo_of(t) <= hi_of(t);
+            if (ok && has_blocks) ok = __all_sync(0xffffffffu, mbar_wait(o_done(t), 0, abort_flag));
+            if (ok && part >= 0) {
+                // a run of the tile's key blocks: the sums as they are, each row's reference and sum of weights
+                tc_fence_after();
+                const long slot = ((long)part * a.n_heads + head) * (2 * BQ) + t * BQ + r;
+                if (r < rows_t) { a.part_ml[slot * 2] = has_blocks ? m : -INFINITY; a.part_ml[slot * 2 + 1] = has_blocks ? l : 0.f; }
+                if (has_blocks) {
+                    float* dst = a.part_o + slot * D;
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t ob[32];
+                        tc_ld32(to + c * 32, ob);
+                        tc_ld_wait();
+                        if (r < rows_t) {
+#pragma unroll
+                            for (int k = 0; k < 32; k += 4)
+                                *reinterpret_cast<uint4*>(dst + c * 32 + k) = make_uint4(ob[k], ob[k + 1], ob[k + 2], ob[k + 3]);
+                        }
+                    }
+                }
+            } else if (ok && has_blocks) {
                 tc_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 bf16* dst = a.out + (long)(tok0 + t * BQ + r) * a.ldo + (long)head * D;
@@ -354,6 +394,52 @@ __global__ void __launch_bounds__(NTHREADS, 1) prefill_attention_tc_kernel(const
     if (threadIdx.x == 0 && abort_flag_s && a.status) atomicExch(a.status, STATUS_TC_TIMEOUT);
 }
 
+// Adds up the runs of key blocks of the tiles that were cut: row r of a tile has, from run c, the sums o_c (32-bit,
+// relative to the reference m_c) and the sum of weights l_c; with M = max m_c the result is
+// sum_c o_c 2^((m_c - M) s) / sum_c l_c 2^((m_c - M) s), the runs taken in their order.  A run without visible keys
+// for the row has m_c = -inf and is skipped.  merges: int32 [n, 4] = (first flat token, rows, first part, runs).
+template <int D>
+__global__ void __launch_bounds__(128) prefill_merge_kernel(const int* __restrict__ merges, const float* __restrict__ part_o,
+                                                            const float* __restrict__ part_ml, bf16* __restrict__ out, long ldo,
+                                                            int n_heads, float scale_log2e)
+{
+    fx_pdl_wait();
+    const int* mg = merges + (long)blockIdx.x * 4;
+    const int tok0 = mg[0], rows = mg[1], part0 = mg[2], runs = mg[3];
+    const int head = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int PER = D / 32;   // elements of a row per lane
+    const int r = blockIdx.z * 4 + warp;   // a warp a row: all of a row's loads are on their way together
+    if (r >= rows) return;
+    const long slot0 = ((long)part0 * n_heads + head) * (2 * BQ) + r;
+    const long run_stride = (long)n_heads * (2 * BQ);          // slots from one run to the next
+    // lane c holds run c's reference and sum (runs <= 32)
+    float m_c = -INFINITY, l_c = 0.f;
+    if (lane < runs) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (slot0 + lane * run_stride) * 2);
+        m_c = ml.x; l_c = ml.y;
+    }
+    const float mx = warp_max(m_c);
+    const float w_c = m_c == -INFINITY ? 0.f : fast_exp2((m_c - mx) * scale_log2e);
+    float acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+    float l = 0.f;
+#pragma unroll 4
+    for (int c = 0; c < runs; ++c) {
+        const float w = __shfl_sync(0xffffffffu, w_c, c);
+        l = fmaf(__shfl_sync(0xffffffffu, l_c, c), w, l);
+        if (w == 0.f) continue;    // a run without visible keys for this row wrote no sums
+        const float* src = part_o + (slot0 + c * run_stride) * D + lane * PER;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] = fmaf(src[i], w, acc[i]);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    bf16* dst = out + (long)(tok0 + r) * ldo + (long)head * D + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) dst[i] = __float2bfloat16_rn(acc[i] * inv);
+}
+
 bool encode(CUtensorMap* map, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box)
 {
     EncodeTiledFn fn = encode_fn();
@@ -380,21 +466,27 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 
 }  // namespace
 
-// tiles: int32 [n_tiles, 4] = (first flat token, rows <= 256, entry index, absolute position of the first row).
+// items: int32 [n_items, 8] = (first flat token, rows <= 256, entry index, absolute position of the first row, first
+// key block of 128 positions, end of the key blocks, part or -1, unused), the heavy ones first.  An item with part -1
+// holds every key block its tile sees and writes the tile's output; the items of a tile that was cut write their
+// partial results to part_o [parts, n_heads, 256, head_dim] and part_ml [parts, n_heads, 256, 2] (32-bit), and
+// merges: int32 [n_merges, 4] = (first flat token, rows, first part, runs) tells the second kernel which to add up
+// (a tile's runs have consecutive parts, in the order of their keys).
 // q is the fused [tokens, ldq] buffer whose rows start with the query heads; n_tokens its number of rows.
 // Refuses (FX_ERR_SIZE / FX_ERR_ALIGN) what it does not take; the caller then uses the mma.sync kernel.
 extern "C" int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages,
                                        int n_pages, const int* block_table, int table_width, int page_size,
                                        const int* tiles, int n_tiles, const int* seq_slot, void* out, long ldo,
                                        int n_heads, int n_kv_heads, int head_dim, int window, float scale, int* status,
-                                       void* stream)
+                                       float* part_o, float* part_ml, const int* merges, int n_merges, void* stream)
 {
     if (n_tiles <= 0) return FX_OK;
+    if (n_merges > 0 && (!part_o || !part_ml || !merges || (uintptr_t)part_o % 16)) return FX_ERR_ALIGN;
     if ((head_dim != 64 && head_dim != 128) || page_size < 64 || page_size % 64 || n_kv_heads <= 0 || n_heads % n_kv_heads)
         return FX_ERR_SIZE;
     if (ldq % 8 || ldo % 8 || (uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16 || (uintptr_t)out % 16)
         return FX_ERR_ALIGN;
-    if (n_heads > 65535) return FX_ERR_SIZE;
+    if (n_tiles > 65535) return FX_ERR_SIZE;
     CUtensorMap mq, mk, mv;
     {
         cuuint64_t dims[2] = {(cuuint64_t)n_heads * head_dim, (cuuint64_t)n_tokens};
@@ -414,7 +506,17 @@ extern "C" int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, co
     a.tiles = tiles; a.seq_slot = seq_slot; a.out = (bf16*)out; a.ldo = ldo;
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f; a.status = status;
-    dim3 grid(n_tiles, n_heads);
+    a.part_o = part_o; a.part_ml = part_ml;
+    dim3 grid(n_heads, n_tiles);
     cudaStream_t s = (cudaStream_t)stream;
-    return head_dim == 64 ? launch<64>(mq, mk, mv, a, grid, s) : launch<128>(mq, mk, mv, a, grid, s);
+    const int rc = head_dim == 64 ? launch<64>(mq, mk, mv, a, grid, s) : launch<128>(mq, mk, mv, a, grid, s);
+    if (rc != FX_OK || n_merges <= 0) return rc;
+    dim3 mgrid(n_merges, n_heads, 2 * BQ / 4);
+    if (head_dim == 64)
+        fx_launch_pdl(prefill_merge_kernel<64>, mgrid, 128, 0, s, merges, (const float*)part_o, (const float*)part_ml, (bf16*)out,
+                      ldo, n_heads, a.scale_log2e);
+    else
+        fx_launch_pdl(prefill_merge_kernel<128>, mgrid, 128, 0, s, merges, (const float*)part_o, (const float*)part_ml,
+                      (bf16*)out, ldo, n_heads, a.scale_log2e);
+    return fx_launch_status();
 }

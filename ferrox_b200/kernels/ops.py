@@ -51,7 +51,8 @@ _SIGNATURES = {
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P],
-    "fx_prefill_attention_tc": [_P, _L, _I, _P, _P, _I, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P, _P],
+    "fx_prefill_attention_tc": [_P, _L, _I, _P, _P, _I, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P, _P, _P,
+                                _P, _I, _P],
     "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P],
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
@@ -368,15 +369,98 @@ def prefill_tc_ok(q, out, k_pages, page_size, head_dim) -> bool:
             and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
-def prefill_attention_tc(q, k_pages, v_pages, block_table, page_size, tiles, seq_slot, out, n_heads, n_kv_heads,
-                         head_dim, window, scale, status=None, stream=None):
+PREFILL_KEY_BLOCK = 128          # positions per key block of the tcgen05 prompt attention kernel
+PREFILL_MAX_RUNS = 32            # runs of key blocks a tile may be cut into (a lane of the merging warp each)
+# The planner's cost model, in units of the time a block of 128 keys takes a tile (measured on a B200, 16 heads of
+# 128: 2.7 us): what an item costs beside its key blocks (set-up, the first block's latency, its output), and the
+# second kernel that adds the runs of cut tiles up.
+PREFILL_ITEM_OVERHEAD, PREFILL_MERGE_COST = 5, 3
+PREFILL_RUN_CHOICES = (0, 16, 12, 8, 6, 4)   # key blocks a run (0: tiles stay whole)
+
+
+def _prefill_items(tiles, run: int):
+    items, merges, parts = [], [], 0
+    for tok0, rows, b, pos0, first, end in tiles:
+        n_blk = end - first
+        runs = min(PREFILL_MAX_RUNS, -(-n_blk // run)) if run > 0 else 1
+        if runs <= 1:
+            items.append((tok0, rows, b, pos0, first, end, -1, 0))
+            continue
+        per = -(-n_blk // runs)
+        first_part = parts
+        for kb in range(first, end, per):
+            items.append((tok0, rows, b, pos0, kb, min(end, kb + per), parts, 0))
+            parts += 1
+        merges.append((tok0, rows, first_part, parts - first_part))
+    items.sort(key=lambda it: it[4] - it[5])      # most key blocks first (stable: ties stay in order)
+    return items, merges, parts
+
+
+def _prefill_makespan(items, parts: int, n_heads: int, sms: int) -> float:
+    """How long the items take on ``sms`` SMs that take them heaviest first, each head its own copy of every item:
+    no less than the heaviest item, than an even share of all work, and than the two items that must share an SM once
+    there are more items than SMs; plus the adding up of the parts."""
+    costs = [it[5] - it[4] + PREFILL_ITEM_OVERHEAD for it in items]           # descending already
+    n = len(costs) * n_heads
+    est = max(costs[0], sum(costs) * n_heads / sms)
+    if n > sms:
+        est = max(est, costs[(sms - 1) // n_heads] + costs[sms // n_heads])
+    return est + (PREFILL_MERGE_COST if parts else 0)
+
+
+def prefill_tc_plan(entries, window, n_heads: int, sms: int = 0, run_blocks: int = -1):
+    """The work items of the tcgen05 prompt attention kernel for a step.  ``entries``: (tokens, first position) of
+    each entry, in the order of the flattened batch.  A tile is up to 256 queries of one entry; it sees the key blocks
+    (of 128 positions) from its first query's first visible key to its last query's own.  Tiles with many key blocks
+    may be cut into runs whose partial results a second kernel adds up: a portion behind a long cached prefix is one
+    tile with all the keys, and without the cut it would keep as many SMs busy as there are heads.  A cut item costs
+    (PREFILL_ITEM_OVERHEAD), so the run length is the one of PREFILL_RUN_CHOICES whose items finish first by
+    :func:`_prefill_makespan`, and whole tiles stay unless a cut is 15 % faster by that estimate.  Returns (items int32 [n, 8], merges int32 [m, 4], parts) as
+    ``fx_prefill_attention_tc`` takes them: heavy items first; a tile's runs have consecutive parts in the order of
+    their keys.  ``run_blocks`` >= 0: this many key blocks a run instead of the choice (0: no cut; tests)."""
+    import numpy as np
+
+    sms = sms or sm_count()
+    W = int(window or 0)
+    tiles, flat = [], 0
+    for b, (n, start) in enumerate(entries):
+        for i in range(0, n, WIDE_PREFILL_TILE):
+            rows, pos0 = min(WIDE_PREFILL_TILE, n - i), start + i
+            first = (max(0, pos0 - W + 1) if W > 0 else 0) // PREFILL_KEY_BLOCK
+            end = (pos0 + rows - 1) // PREFILL_KEY_BLOCK + 1
+            tiles.append((flat + i, rows, b, pos0, first, end))
+        flat += n
+    best = first = None
+    whole = 0.0
+    for run in (PREFILL_RUN_CHOICES if run_blocks < 0 else (run_blocks,)):
+        items, merges, parts = _prefill_items(tiles, run)
+        if run > 0 and not parts and best is not None:
+            continue                                  # nothing was cut: the same items as the whole tiles
+        est = _prefill_makespan(items, parts, n_heads, sms)
+        # (whole tiles stay unless a cut promises a clear gain: the model is good to a tenth or so)
+        if best is None or est < (0.85 * whole if best[1] is first else best[0] - 1e-9):
+            best = (est, items, merges, parts)
+            if first is None:
+                first, whole = items, est
+    _, items, merges, parts = best
+    return (np.asarray(items, dtype=np.int32).reshape(-1, 8), np.asarray(merges, dtype=np.int32).reshape(-1, 4), parts)
+
+
+def prefill_attention_tc(q, k_pages, v_pages, block_table, page_size, items, seq_slot, out, n_heads, n_kv_heads,
+                         head_dim, window, scale, status=None, stream=None, merges=None, part_o=None, part_ml=None):
     """Flash attention of prompt portions on the tcgen05 tensor cores (bfloat16, head_dim 64 or 128, pages of a
-    multiple of 64 positions).  ``tiles``: int32 [n, 4] rows of (first flat token, rows <= 256, entry index,
-    absolute position of the first row)."""
+    multiple of 64 positions).  ``items``, ``merges``: device copies of what :func:`prefill_tc_plan` returns;
+    ``part_o`` float32 [parts, n_heads, 256, head_dim] and ``part_ml`` float32 [parts, n_heads, 256, 2]: scratch for the
+    tiles that were cut into runs of key blocks (a second kernel adds the runs up)."""
+    global _launches
+    n_merges = merges.shape[0] if merges is not None else 0
+    if n_merges:
+        _launches += 1
     call("fx_prefill_attention_tc", _ptr(q), _rows(q), q.shape[0], _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
-         _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0], _ptr(seq_slot), _ptr(out),
+         _ptr(block_table), block_table.shape[1], page_size, _ptr(items), items.shape[0], _ptr(seq_slot), _ptr(out),
          _rows(out), n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(status),
-         stream if stream is not None else stream_ptr())
+         _ptr(part_o) if n_merges else None, _ptr(part_ml) if n_merges else None, _ptr(merges) if n_merges else None,
+         n_merges, stream if stream is not None else stream_ptr())
     return out
 
 

@@ -49,6 +49,19 @@ def query_tiles(batch, rows: int) -> torch.Tensor:
     return t
 
 
+def prefill_tc_plan(batch, window, n_heads: int):
+    """This step's work items for the tcgen05 prompt attention kernel (``ops.prefill_tc_plan``) on the device: made
+    once a step for each window and shared by the layers that have it."""
+    key = ("attention tcgen05 items", window, n_heads)
+    plan = batch.shared.get(key)
+    if plan is None:
+        items, merges, parts = ops.prefill_tc_plan([(len(e.tokens), e.start) for e in batch.entries], window, n_heads)
+        both = torch.from_numpy(np.concatenate([items.reshape(-1), merges.reshape(-1)])).to(batch.token_ids.device)
+        plan = (both[:items.size].view(-1, 8), both[items.size:].view(-1, 4) if merges.size else None, parts)
+        batch.shared[key] = plan
+    return plan
+
+
 class GqaAttention(Mixer):
     @property
     def graph_safe(self):
@@ -138,11 +151,16 @@ class GqaAttention(Mixer):
                 fresh_positions=batch.max_new,
             )
         elif ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
-            # prompt portions: tiles of 256 queries, tcgen05
+            # prompt portions: tiles of 256 queries (long ones cut into runs of key blocks), tcgen05
+            items, merges, parts = prefill_tc_plan(batch, s.window, s.n_heads)
+            part_o = part_ml = None
+            if parts:
+                part_o = self.rt.empty(parts, s.n_heads, ops.WIDE_PREFILL_TILE, s.head_dim, dtype=torch.float32)
+                part_ml = self.rt.empty(parts, s.n_heads, ops.WIDE_PREFILL_TILE, 2, dtype=torch.float32)
             ops.prefill_attention_tc(
-                qkv, cache.k, cache.v, cache.block_table, cache.page_size,
-                query_tiles(batch, ops.WIDE_PREFILL_TILE), batch.seq_slot, attn,
+                qkv, cache.k, cache.v, cache.block_table, cache.page_size, items, batch.seq_slot, attn,
                 s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, status=batch.status, stream=batch.stream,
+                merges=merges, part_o=part_o, part_ml=part_ml,
             )
         elif ops.prefill_ok(qkv, attn, cache.k, s.head_dim):
             # prompt portions, other head and page sizes: tiles of 64 queries, mma.sync

@@ -61,3 +61,53 @@ def test_decode_attention_by_tma_where_pages_and_heads_fit_its_boxes():
 def test_routing_in_one_block_only_for_small_steps():
     assert ops.ROUTE_SMALL_MAX_TOKENS <= 64      # the one-block kernel takes a token per warp and round
     assert 32 * ops.ROUTE_SMALL_MAX_EXPERTS * 4 + (2 * ops.ROUTE_SMALL_MAX_EXPERTS + 1) * 4 <= 48 * 1024   # its shared memory
+
+
+def test_prompt_attention_items_cover_every_key_block_once():
+    """The planner of the tcgen05 prompt attention: every tile's key blocks are covered exactly once by its items, in
+    order; a tile that was cut has consecutive parts and one merge row; heavy items come first; the cut depends on the
+    step's sizes alone."""
+    import random
+
+    rng = random.Random(0)
+    for trial in range(60):
+        entries = [(rng.randint(1, 3000), rng.choice([0, 0, 5, 127, 128, 1000, 4097])) for _ in range(rng.randint(1, 4))]
+        window = rng.choice([0, 0, 1, 100, 2048])
+        heads = rng.choice([1, 16, 28])
+        run_blocks = rng.choice([-1, -1, 0, 1, 2, 5])
+        items, merges, parts = ops.prefill_tc_plan(entries, window, heads, run_blocks=run_blocks)
+        again = ops.prefill_tc_plan(entries, window, heads, run_blocks=run_blocks)
+        assert (items == again[0]).all() and (merges == again[1]).all() and parts == again[2]
+        lengths = [int(it[5] - it[4]) for it in items]
+        assert lengths == sorted(lengths, reverse=True) and min(lengths) >= 1
+        by_tile = {}
+        for tok0, rows, b, pos0, kb, ke, part, _ in items.tolist():
+            by_tile.setdefault((tok0, rows, b, pos0), []).append((kb, ke, part))
+        flat, n_tiles = 0, 0
+        for b, (n, start) in enumerate(entries):
+            for i in range(0, n, 256):
+                rows, pos0 = min(256, n - i), start + i
+                runs = sorted(by_tile[(flat + i, rows, b, pos0)])
+                first = (max(0, pos0 - window + 1) if window else 0) // 128
+                end = (pos0 + rows - 1) // 128 + 1
+                assert runs[0][0] == first and runs[-1][1] == end
+                assert all(a[1] == c[0] for a, c in zip(runs, runs[1:]))            # no gap, no overlap
+                if len(runs) == 1:
+                    assert runs[0][2] == -1
+                else:
+                    ps = [r[2] for r in runs]
+                    assert ps == list(range(ps[0], ps[0] + len(runs))) and len(runs) <= ops.PREFILL_MAX_RUNS
+                    assert [flat + i, rows, ps[0], len(runs)] in merges.tolist()
+                n_tiles += 1
+            flat += n
+        assert len(by_tile) == n_tiles and parts == sum(m[3] for m in merges.tolist())
+    # a prompt of 2,048 tokens on 16 heads: 128 whole tiles fit the 148 SMs at once; cutting would cost more than it saves
+    items, merges, parts = ops.prefill_tc_plan([(2048, 0)], None, 16, sms=148)
+    assert len(items) == 8 and parts == 0 and len(merges) == 0
+    # a portion of 256 tokens behind 6,000 cached positions: one tile with 49 key blocks, cut so that all SMs work
+    items, merges, parts = ops.prefill_tc_plan([(256, 6000)], None, 16, sms=148)
+    assert parts == len(items) >= 6 and merges.tolist() == [[0, 256, 0, parts]]
+    assert max(int(it[5] - it[4]) for it in items) <= 8
+    # forced runs of four key blocks
+    items, merges, parts = ops.prefill_tc_plan([(2048, 0)], None, 16, sms=148, run_blocks=4)
+    assert len(items) == 20 and max(int(it[5] - it[4]) for it in items) == 4 and len(merges) == 6

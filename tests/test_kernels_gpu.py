@@ -731,28 +731,33 @@ TC_ATT_CASES = [
     (6, 2, 64, 128, 0, [700, 129]),
     (3, 1, 64, 64, 300, [900]),
     (2, 2, 128, 192, 129, [400, 2, 128]),
+    (4, 2, 128, 64, 0, [2300, 300]),
+    (2, 1, 128, 64, 0, [6000]),
+    (2, 2, 64, 64, 2048, [4300]),
 ]
 
 
+@pytest.mark.parametrize("run_blocks", [-1, 0, 1, 3])
 @pytest.mark.parametrize("case", TC_ATT_CASES)
-def test_prefill_attention_tcgen05(case):
+def test_prefill_attention_tcgen05(case, run_blocks):
     """Prompt portions through the tcgen05 kernel (tiles of 256 queries, blocks of 128 keys), whole prompts and
-    continuations after a cached prefix, against the plain per-query statement.  One far key of the longest
-    request is made to stand out for its last query, so that a block that is skipped or masked wrongly shows."""
+    continuations after a cached prefix, against the plain per-query statement; with the planner's own cut of
+    long tiles into runs of key blocks, and with runs of one and of three blocks (every tile with more is then added
+    up from partial results by the second kernel).  One far key of the longest request is made to stand out for its
+    last query, so that a block that is skipped or masked wrongly shows."""
     o = ops()
     nh, nkv, d, ps, window, lens = case
     dt = torch.bfloat16
     kp, vp, table, ks, vs = build_cache(dt, lens, nkv, d, ps, n_pages=sum(-(-L // ps) for L in lens) + 3, seed=5)
     # stale finite values in the unused places of every page, as pages that are used again hold
     starts = [0 if i % 2 == 0 else min(L - 1, max(1, L // 3)) for i, L in enumerate(lens)]
-    toks, tiles, flat = [], [], 0
+    toks = []
     for s, (L, st) in enumerate(zip(lens, starts)):
-        n = L - st
-        for i in range(0, n, o.WIDE_PREFILL_TILE):
-            tiles.append((flat + i, min(o.WIDE_PREFILL_TILE, n - i), s, st + i))
         toks += [(s, p) for p in range(st, L)]
-        flat += n
     T = len(toks)
+    items, merges, parts = o.prefill_tc_plan([(L - st, st) for L, st in zip(lens, starts)], window, nh, run_blocks=run_blocks)
+    if run_blocks == 1:
+        assert parts >= max(lens) // 128 and len(merges) >= 1
     if window:
         # pages that the window has left behind are given back before a later portion runs: no page there
         for s, st in enumerate(starts):
@@ -764,13 +769,16 @@ def test_prefill_attention_tcgen05(case):
     far = max(0, L0 - 1 - (window - 2 if window else L0))
     last0 = L0 - starts[0] - 1
     q[last0, :d] = (ks[0][far, 0] * 4).to(dt).to(DEV)
-    tiles_t = torch.tensor(tiles, dtype=torch.int32, device=DEV)
     seq_slot = torch.tensor([s + 1 for s in range(len(lens))], dtype=torch.int32, device=DEV)
     out = torch.zeros(T, nh * d, dtype=dt, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     scale = 1 / math.sqrt(d)
     assert o.prefill_tc_ok(q, out, kp, ps, d)
-    o.prefill_attention_tc(q, kp, vp, table, ps, tiles_t, seq_slot, out, nh, nkv, d, window, scale, status=status)
+    part_o = torch.full((max(parts, 1), nh, 256, d), float("nan"), device=DEV)      # what a run does not write is not read
+    part_ml = torch.full((max(parts, 1), nh, 256, 2), float("nan"), device=DEV)
+    o.prefill_attention_tc(q, kp, vp, table, ps, torch.from_numpy(items).to(DEV), seq_slot, out, nh, nkv, d, window, scale,
+                           status=status, merges=torch.from_numpy(merges).to(DEV) if parts else None, part_o=part_o,
+                           part_ml=part_ml)
     assert int(status) == 0
     assert torch.isfinite(out.float()).all()
     step = max(1, T // 40)  # a spread of tokens, plus tile edges
@@ -790,7 +798,7 @@ def test_prefill_attention_tcgen05_refuses_other_sizes():
     kp = torch.zeros(2, 1, 64, 48, dtype=torch.bfloat16, device=DEV)
     out = torch.zeros(4, 48, dtype=torch.bfloat16, device=DEV)
     assert not o.prefill_tc_ok(q, out, kp, 64, 48)
-    tiles = torch.tensor([[0, 4, 0, 0]], dtype=torch.int32, device=DEV)
+    tiles = torch.tensor([[0, 4, 0, 0, 0, 1, -1, 0]], dtype=torch.int32, device=DEV)
     table = torch.zeros(1, 2, dtype=torch.int32, device=DEV)
     slots = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(o.KernelError):
