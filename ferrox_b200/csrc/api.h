@@ -84,7 +84,7 @@ int fx_decode_split_tma(const void* q, long ldq, const void* k_pages, const void
                         const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml, int n_tokens,
                         int n_heads, int n_kv_heads, int head_dim, int window, float scale, int split_len,
                         int n_splits, int* status, void* out, long ldo, int* counters, int fresh_positions,
-                        void* stream);
+                        int store_new, int write_pages, const float* cos_sin, void* stream);
 // n_pages > 0 (the number of pages behind k_pages / v_pages) lets bfloat16 take the TMA kernel; status: the step's
 // status word (may be null).
 // fresh_positions: 0 makes no assumption about the kernel launched before this one on the stream: nothing is read until
@@ -92,12 +92,17 @@ int fx_decode_split_tma(const void* q, long ldq, const void* k_pages, const void
 // queries and the keys and values of at most the last N positions of each request (positions, token_seq, seq_slot and
 // the block table are older); the bfloat16 kernels then fetch tiles of older keys while that kernel still runs.  A
 // promise that does not hold gives stale keys without any error.
+// store_new = 1 (bfloat16, head sizes in steps of 64, pages of a multiple of 64 positions, one token a request; else
+// refused): `q` is the step's fused [q | k | v] rows as projected, and the kernel does the rotary kernel's work
+// itself: it rotates the queries (split-half pairs over the whole head; cos_sin [tokens][head_dim / 2][2] from
+// fx_rope_table, or null for no rotation), and rotates and stores each token's own key and value (into the pages only
+// if write_pages).  The kernel before it must then not write the pages at all.
 int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages, int dtype,
                         const int* block_table, int table_width, int page_size, const int* positions,
                         const int* token_seq, const int* seq_slot, void* out, long ldo, float* part_acc,
                         float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
                         float scale, int split_len, int n_splits, int* status, int* counters, int fresh_positions,
-                        void* stream);
+                        int store_new, int write_pages, const float* cos_sin, void* stream);
 
 // out[i] = mean + stdev * z_i, z the standard normal stream of `key` (random_init.cu; the host restates the rule
 // bit for bit).  dtype: FX_F32 or FX_BF16.

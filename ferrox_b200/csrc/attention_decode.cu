@@ -313,7 +313,8 @@ template <typename T>
 int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages, const int* block_table,
         int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot, void* out,
         long ldo, float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
-        float scale, int split_len, int n_splits, int* status, int* counters, int fresh, cudaStream_t s)
+        float scale, int split_len, int n_splits, int* status, int* counters, int fresh, int store_new, int write_pages,
+        const float* cos_sin, cudaStream_t s)
 {
     constexpr int N = Vec<T>::N;
     if (head_dim % N || head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -327,9 +328,11 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n
             rc_mma = fx_decode_split_tma(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size,
                                          positions, token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads,
                                          n_kv_heads, head_dim, window, scale, split_len, n_splits, status, out, ldo,
-                                         counters, fresh, (void*)s);
+                                         counters, fresh, store_new, write_pages, cos_sin, (void*)s);
             if (rc_mma == FX_OK && (counters || n_splits == 1)) return FX_OK;   // merged by the kernel's last blocks
         }
+        // only the kernel above rotates and stores the step's own keys and values itself
+        if (store_new && rc_mma != FX_OK) return rc_mma;
         if (rc_mma < 0)
             rc_mma = fx_decode_split_mma(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions,
                                          token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads, n_kv_heads,
@@ -341,6 +344,7 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n
         }
         if (rc_mma > 0) return rc_mma;   // a CUDA error; a refusal (< 0) falls through to the CUDA-core kernel
     }
+    if (store_new) return FX_ERR_DTYPE;
     const int group = n_heads / n_kv_heads;
     int gq = 1;
     while (gq < group && gq < MAXQ) gq <<= 1;
@@ -374,7 +378,8 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
                                    const int* positions, const int* token_seq, const int* seq_slot, void* out, long ldo,
                                    float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
                                    int head_dim, int window, float scale, int split_len, int n_splits, int* status,
-                                   int* counters, int fresh_positions, void* stream)
+                                   int* counters, int fresh_positions, int store_new, int write_pages,
+                                   const float* cos_sin, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (split_len < 0 || n_splits <= 0) return FX_ERR_SIZE;
@@ -382,11 +387,11 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
                           seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, status, counters, fresh_positions, s);
+                          split_len, n_splits, status, counters, fresh_positions, store_new, write_pages, cos_sin, s);
     if (dtype == FX_BF16)
         return run<bf16>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
                          seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, status, counters, fresh_positions, s);
+                         split_len, n_splits, status, counters, fresh_positions, store_new, write_pages, cos_sin, s);
     return FX_ERR_DTYPE;
 }
 
@@ -441,10 +446,10 @@ extern "C" int fx_decode_attention_noalloc(const void* q, long ldq, const void* 
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                           out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, nullptr, nullptr, 0, s);
+                          split_len, n_splits, nullptr, nullptr, 0, 0, 0, nullptr, s);
     if (dtype == FX_BF16)
         return run<bf16>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                          out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, nullptr, nullptr, 0, s);
+                         split_len, n_splits, nullptr, nullptr, 0, 0, 0, nullptr, s);
     return FX_ERR_DTYPE;
 }

@@ -56,6 +56,14 @@ struct DecArgs {
     // last key range merges all of them into `out`; without, the caller runs the merge kernel.  A single key range a
     // token is written to `out` at once if that is given.
     bf16* out; long ldo; int* counters;
+    // store_new: the rows of q are the fused [q | k | v] rows of the step as the projection left them, one token a
+    // request.  The kernel then rotates the queries itself (split-half pairs over the whole head, cos and sin from
+    // cos_sin [tokens][head_dim / 2][2]; null: no rotation), and the block that holds a token's own position rotates
+    // that token's key, puts it and the value into its copy of their tile, and (one block per kv head, if
+    // write_pages) into the cache pages: the work of the rotary kernel without its launch.
+    int store_new, write_pages;
+    const float* cos_sin;
+    bf16* k_pages; bf16* v_pages;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -169,6 +177,42 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
         fx_pdl_wait();
         const int g = lane >> 2, t4 = lane & 3;
         const int chunks_row = head_dim / 8;                   // 16-byte chunks per row
+        const int half_d = head_dim >> 1;
+        // store_new: the warp whose 16 keys of the last tile hold the token's own position prepares that key and value
+        const bool owns_new = a.store_new && pos >= k_begin && pos < k_end && warp == ((pos % TK) >> 4);
+        bf16 new_k[DMAX / 32], new_v[DMAX / 32];   // elements lane + 32 u of the row
+        if (owns_new) {
+            const bf16* krow = a.q + (long)tkn * a.ldq + (long)(n_heads + kvh) * head_dim;
+            const bf16* vrow = krow + (long)n_kv_heads * head_dim;
+#pragma unroll
+            for (int u = 0; u < DMAX / 32; ++u) {
+                const int e = lane + 32 * u;
+                if (e < head_dim) {
+                    new_v[u] = vrow[e];
+                    float x = __bfloat162float(krow[e]);
+                    if (a.cos_sin) {
+                        // element e pairs with e +- head_dim / 2; the same arithmetic as the rotary kernel's
+                        const int i = e < half_d ? e : e - half_d;
+                        const float2 cs = *reinterpret_cast<const float2*>(a.cos_sin + ((long)tkn * half_d + i) * 2);
+                        const float other = __bfloat162float(krow[e < half_d ? e + half_d : e - half_d]);
+                        x = e < half_d ? x * cs.x - other * cs.y : other * cs.y + x * cs.x;
+                    }
+                    new_k[u] = __float2bfloat16_rn(x);
+                }
+            }
+            if (a.write_pages && blockIdx.x % chunks == 0) {
+                const int page = a.block_table[(long)a.seq_slot[seq] * a.table_width + pos / a.page_size];
+                if (page < 0) { if (lane == 0 && a.status) atomicExch(a.status, 2); }
+                else {
+                    const long at = (((long)page * n_kv_heads + kvh) * a.page_size + pos % a.page_size) * head_dim;
+#pragma unroll
+                    for (int u = 0; u < DMAX / 32; ++u) {
+                        const int e = lane + 32 * u;
+                        if (e < head_dim) { a.k_pages[at + e] = new_k[u]; a.v_pages[at + e] = new_v[u]; }
+                    }
+                }
+            }
+        }
         // query rows of this block (zero beyond the group)
         for (int c = threadIdx.x; c < 16 * chunks_row; c += NCONSUMERS) {
             const int r = c / chunks_row, ch = c - r * chunks_row;
@@ -178,6 +222,19 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         consumers_sync();
+        if (a.store_new && a.cos_sin) {
+            // the queries as projected: rotate them where they lie (pairs i, i + head_dim / 2 of every head)
+            bf16* q_s = reinterpret_cast<bf16*>(smem_raw + (q_u - smem_u32(smem_raw)));
+            for (int idx = threadIdx.x; idx < nq * half_d; idx += NCONSUMERS) {
+                const int r = idx / half_d, i = idx - r * half_d;
+                const float2 cs = *reinterpret_cast<const float2*>(a.cos_sin + ((long)tkn * half_d + i) * 2);
+                bf16* row = q_s + (long)r * (pitch / 2);
+                const float x = __bfloat162float(row[i]), y = __bfloat162float(row[i + half_d]);
+                row[i] = __float2bfloat16_rn(x * cs.x - y * cs.y);
+                row[i + half_d] = __float2bfloat16_rn(x * cs.y + y * cs.x);
+            }
+            consumers_sync();
+        }
 
         constexpr int KS = DMAX / 16, ON = DMAX / 8;
         const int ks_n = head_dim / 16;
@@ -195,6 +252,21 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j % stages;
             if (!mbar_wait(full(s), (j / stages) & 1, abort_flag)) break;
+            if (owns_new && j == n_tiles - 1) {
+                // the token's own key and value into this block's copy of their tile (only this warp reads the row)
+                const int r = pos % TK;
+                const uint32_t ku = ring + s * stage_bytes, vu = ku + halves * PIECE;
+#pragma unroll
+                for (int u = 0; u < DMAX / 32; ++u) {
+                    const int e = lane + 32 * u;
+                    if (e < head_dim) {
+                        const uint32_t off = (uint32_t)((e >> 6) * PIECE) + swz(r, (e & 63) >> 3) + (uint32_t)((e & 7) * 2);
+                        asm volatile("st.shared.b16 [%0], %1;" ::"r"(ku + off), "h"(*reinterpret_cast<const uint16_t*>(&new_k[u])) : "memory");
+                        asm volatile("st.shared.b16 [%0], %1;" ::"r"(vu + off), "h"(*reinterpret_cast<const uint16_t*>(&new_v[u])) : "memory");
+                    }
+                }
+                __syncwarp();
+            }
             const int key0 = (first_tile + j) * TK + kw;            // this warp's first key
             if (page_ok_s[s] && key0 < k_end && key0 + 16 > k_begin) {
                 const uint32_t ku = ring + s * stage_bytes, vu = ku + halves * PIECE;
@@ -395,7 +467,7 @@ extern "C" int fx_decode_split_tma(const void* q, long ldq, const void* k_pages,
                                    const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml,
                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                    int split_len, int n_splits, int* status, void* out, long ldo, int* counters,
-                                   int fresh_positions, void* stream)
+                                   int fresh_positions, int store_new, int write_pages, const float* cos_sin, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (counters && (n_splits > 32 || !out || ldo % 2)) return FX_ERR_SIZE;
@@ -425,6 +497,8 @@ extern "C" int fx_decode_split_tma(const void* q, long ldq, const void* k_pages,
     a.scale_log2e = scale * 1.4426950408889634f; a.scale = scale;
     a.split_len = split_len; a.n_splits = n_splits; a.stages = stages; a.status = status;
     a.fresh = fresh_positions;
+    a.store_new = store_new; a.write_pages = write_pages; a.cos_sin = cos_sin;
+    a.k_pages = (bf16*)const_cast<void*>(k_pages); a.v_pages = (bf16*)const_cast<void*>(v_pages);
     a.out = (bf16*)out; a.ldo = ldo; a.counters = counters;
     if (n_splits > 1 && !counters) a.out = nullptr;   // partial results only
     cudaStream_t s = (cudaStream_t)stream;

@@ -57,7 +57,7 @@ _SIGNATURES = {
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "fx_decode_attention": [_P, _L, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                            _I, _P, _P, _I, _P],
+                            _I, _P, _P, _I, _I, _I, _P, _P],
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
     "fx_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "fx_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
@@ -550,14 +550,25 @@ def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int, block
     return 0, best
 
 
+def decode_store_ok(qkv, k_pages, head_dim: int, page_size: int) -> bool:
+    """Whether :func:`decode_attention` can rotate and store the step's own keys and values itself (``store_new``):
+    where the kernel that streams pages by TMA runs."""
+    return (decode_tma_blocks_per_sm(qkv.dtype, head_dim, page_size) > 0 and k_pages.dtype == torch.bfloat16
+            and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and k_pages.data_ptr() % 16 == 0)
+
+
 def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,
                      n_kv_heads, head_dim, window, scale, split_len, n_splits, part_acc, part_ml, status=None,
-                     counters=None, stream=None, fresh_positions=0):
+                     counters=None, stream=None, fresh_positions=0, store_new=False, write_pages=True, cos_sin=None):
     """``counters``: zeroed int32 scratch that the call leaves zeroed, at least tokens x ceil(group / 16) x kv heads;
     with it the kernel that streams pages by TMA merges the key ranges itself (one kernel instead of two).
     ``fresh_positions``: 0 assumes nothing about the kernel launched just before on the stream.  N > 0 promises that
     that kernel wrote, of all this call reads, only the queries and the keys and values of at most the last N
-    positions of each request; older keys are then fetched while it still runs (a false promise reads stale keys)."""
+    positions of each request; older keys are then fetched while it still runs (a false promise reads stale keys).
+    ``store_new`` (one token a request; see :func:`decode_store_ok`): ``q`` is the fused [q | k | v] rows as the
+    projection left them and the kernel does the rotary kernel's work itself: queries and each token's own key
+    rotated (split-half pairs over the whole head, ``cos_sin`` from :func:`rope_table`; None: no rotation), key and
+    value put where the attention reads them and, if ``write_pages``, into the pages."""
     global _launches
     T = q.shape[0]
     per_sm = decode_tma_blocks_per_sm(q.dtype, head_dim, page_size)
@@ -572,8 +583,8 @@ def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, tok
     call("fx_decode_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], code(q),
          _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(out), _rows(out), _ptr(part_acc), _ptr(part_ml), T, n_heads, n_kv_heads, head_dim, int(window or 0),
-         float(scale), split_len, n_splits, _ptr(status), _ptr(counters), int(fresh_positions),
-         stream if stream is not None else stream_ptr())
+         float(scale), split_len, n_splits, _ptr(status), _ptr(counters), int(fresh_positions), int(store_new),
+         int(write_pages), _ptr(cos_sin), stream if stream is not None else stream_ptr())
     return out
 
 

@@ -25,6 +25,10 @@ from .specs import NoPositionSpec
 
 RANGE_COUNTERS = 16384            # (token, block of heads) pairs of a decode step whose key ranges one kernel merges
 DECODE_ATTENTION_MAX_NEW = 8  # entries that bring at most this many tokens use the split-key kernel
+# A decode step of up to this many requests leaves the rotary kernel's work to the attention kernel (measured on a
+# B200, 16 heads of 128: 2 us a layer gained at 1 request, 4 at 8, 1.5 lost at 64, where every one of a thousand
+# blocks pays for what one short kernel did).
+ROTARY_IN_DECODE_KERNEL_MAX_TOKENS = 32
 
 
 def _common_dtype(tensors):
@@ -130,7 +134,14 @@ class GqaAttention(Mixer):
         T = x.shape[0]
         qkv = self.rt.empty(T, self.q_size + 2 * self.kv_size)
         ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, status=batch.status, stream=batch.stream)
-        self.position.rotate_and_store(qkv, batch, cache, s.n_heads, s.n_kv_heads, s.head_dim)
+        # A decode step of one token a request: where the attention kernel can, it rotates the queries and rotates and
+        # stores the keys and values itself (one launch less on every layer's path); else the position part does.
+        in_kernel = None
+        if (batch.max_new == 1 and T <= ROTARY_IN_DECODE_KERNEL_MAX_TOKENS
+                and ops.decode_store_ok(qkv, cache.k, s.head_dim, cache.page_size)):
+            in_kernel = self.position.in_decode_kernel(batch, s.head_dim)
+        if in_kernel is None:
+            self.position.rotate_and_store(qkv, batch, cache, s.n_heads, s.n_kv_heads, s.head_dim)
         attn = self.rt.empty(T, self.q_size)
         if batch.max_new <= DECODE_ATTENTION_MAX_NEW:
             # few query tokens: split each request's keys over many blocks
@@ -146,9 +157,10 @@ class GqaAttention(Mixer):
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, split_len, n_splits,
                 part_acc, part_ml, status=batch.status, counters=self._range_counters, stream=batch.stream,
-                # the kernel just before (the position part's) wrote these rows' q and the k, v of the step's own
-                # positions, at most max_new of a request
+                # the kernel just before (the position part's, or the projection) wrote these rows' q and at most the
+                # k, v of the step's own positions, max_new of a request
                 fresh_positions=batch.max_new,
+                store_new=in_kernel is not None, write_pages=cache.writes, cos_sin=in_kernel[0] if in_kernel else None,
             )
         elif ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
             # prompt portions: tiles of 256 queries (long ones cut into runs of key blocks), tcgen05

@@ -24,6 +24,13 @@ class PositionEncoding(Part):
     def rotate_and_store(self, qkv, batch, cache, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
         raise NotImplementedError  # pragma: no cover - interface
 
+    def in_decode_kernel(self, batch, head_dim: int):
+        """Optional.  A decode step of one token a request can leave this part's work to the attention kernel
+        (``ops.decode_attention(store_new=True)``: split-half rotation over the whole head from a table of cos and
+        sin, or none).  A part whose encoding is of that form returns the one-element tuple (table or None); any
+        other returns None (the default) and is asked to :meth:`rotate_and_store` as always."""
+        return None
+
 
 class RotaryEncoding(PositionEncoding):
     """Rotation of element pairs by pos * inv_freq[i]: a frequency table, a pairing rule and a rotary width.
@@ -57,6 +64,11 @@ class RotaryEncoding(PositionEncoding):
             batch.shared[self._table_key] = t
         return t
 
+    def in_decode_kernel(self, batch, head_dim):
+        if self.pairing != ops.PAIR_HALVES or self.rotary_dim != head_dim:
+            return None
+        return (self.table(batch),)
+
     def rotate_and_store(self, qkv, batch, cache, n_heads, n_kv_heads, head_dim):
         if self.rotary_dim > head_dim:
             raise ValueError(f"rotary_dim={self.rotary_dim} exceeds head_dim={head_dim}")
@@ -75,6 +87,9 @@ class NoPosition(PositionEncoding):
     """No position encoding: keys and queries are stored as projected."""
 
     graph_safe = True
+
+    def in_decode_kernel(self, batch, head_dim):
+        return (None,)
 
     def rotate_and_store(self, qkv, batch, cache, n_heads, n_kv_heads, head_dim):
         ops.rope_kv_write(

@@ -939,3 +939,70 @@ def test_decode_attention_waits_for_a_write_of_many_positions(page_size, d):
         for i in (0, 1, 37, n_new - 1):
             want = plain_attention(x[L0 + i, :nh * d].reshape(nh, d), k, v, L0 + i, 0, scale)
             assert rel(out[i].float().cpu().reshape(nh, d), want) < 1e-2, (trial, i)
+
+
+# ------------------------------------------------------------------ decode attention that rotates and stores itself
+@pytest.mark.parametrize("nh,nkv,d,ps,window,lens", [
+    (16, 16, 128, 64, 0, [300, 64, 65, 1]),
+    (28, 4, 128, 64, 100, [130, 517]),
+    (40, 2, 64, 128, 0, [150, 260, 129]),       # 20 query heads a kv head: two blocks of heads share a key's tile
+    (6, 2, 192, 128, 150, [318, 70]),
+    (4, 4, 256, 64, 33, [140, 64]),
+])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_decode_attention_does_the_rotary_kernels_work_itself(nh, nkv, d, ps, window, lens, rotate):
+    """One new token a request: the decode attention given the fused rows as projected (store_new) against the
+    rotary kernel followed by the decode attention: the same pages bit for bit, the same output within rounding;
+    with one and with several key ranges, merged by the kernel and by the merge kernel; and against plain."""
+    o, dt = ops(), torch.bfloat16
+    assert o.decode_tma_blocks_per_sm(dt, d, ps) > 0
+    kp0, vp0, table, ks, vs = build_cache(dt, lens, nkv, d, ps, n_pages=sum(-(-L // ps) for L in lens) + 3, seed=9)
+    B = len(lens)
+    positions = torch.tensor([L - 1 for L in lens], dtype=torch.int32, device=DEV)     # the new token is each request's last
+    token_seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    seq_slot = torch.tensor([s + 1 for s in range(B)], dtype=torch.int32, device=DEV)
+    qkv0 = rnd(B, (nh + 2 * nkv) * d + 8, dtype=dt, seed=d)[:, :(nh + 2 * nkv) * d]
+    inv_freq = (1.0 / torch.pow(torch.tensor(1e4), torch.arange(0, d // 2).float() * 2 / d)).to(DEV) if rotate else None
+    cos_sin = None
+    if rotate:
+        cos_sin = torch.empty(B, d // 2, 2, device=DEV)
+        o.rope_table(positions, inv_freq, cos_sin)
+    scale = 1 / math.sqrt(d)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    # the two-kernel way
+    qkv_a, kp_a, vp_a = qkv0.clone(), kp0.clone(), vp0.clone()
+    o.rope_kv_write(qkv_a, positions, token_seq, seq_slot, inv_freq, d if rotate else 0, kp_a, vp_a, table, ps, nh, nkv, d,
+                    True, status, cos_sin=cos_sin)
+    for n_splits, with_counters in ((1, False), (3, False), (2, True), (5, True)):
+        pa, pm = torch.empty(B, nh, n_splits, d, device=DEV), torch.empty(B, nh, n_splits, 2, device=DEV)
+        counters = torch.zeros(B * nkv * -(-(nh // nkv) // 16), dtype=torch.int32, device=DEV) if with_counters else None
+        want = torch.zeros(B, nh * d, dtype=dt, device=DEV)
+        o.decode_attention(qkv_a, kp_a, vp_a, table, ps, positions, token_seq, seq_slot, want, nh, nkv, d, window, scale,
+                           0, n_splits, pa, pm, status=status, counters=counters)
+        qkv_b, kp_b, vp_b = qkv0.clone(), kp0.clone(), vp0.clone()
+        got = torch.zeros_like(want)
+        o.decode_attention(qkv_b, kp_b, vp_b, table, ps, positions, token_seq, seq_slot, got, nh, nkv, d, window, scale,
+                           0, n_splits, torch.empty_like(pa), torch.empty_like(pm), status=status, counters=counters,
+                           store_new=True, write_pages=True, cos_sin=cos_sin, fresh_positions=1)
+        assert int(status) == 0
+        assert torch.equal(kp_b, kp_a) and torch.equal(vp_b, vp_a), n_splits       # the pages hold the same bits
+        assert torch.equal(qkv_b, qkv0)                                            # the rows stay as projected
+        assert rel(got, want) < 4e-3, n_splits
+        # a layer that reads another layer's cache: nothing is stored, the token's own key still counts
+        kp_c, vp_c = kp0.clone(), vp0.clone()
+        got_c = torch.zeros_like(want)
+        o.decode_attention(qkv0.clone(), kp_c, vp_c, table, ps, positions, token_seq, seq_slot, got_c, nh, nkv, d, window,
+                           scale, 0, n_splits, torch.empty_like(pa), torch.empty_like(pm), status=status, counters=counters,
+                           store_new=True, write_pages=False, cos_sin=cos_sin)
+        assert torch.equal(kp_c, kp0) and torch.equal(got_c, got)
+    # and against the plain statement, with the new key and value in their places
+    x = qkv_a.float().cpu()
+    for s, L in enumerate(lens):
+        ks[s][L - 1] = x[s, nh * d:(nh + nkv) * d].reshape(nkv, d)
+        vs[s][L - 1] = x[s, (nh + nkv) * d:].reshape(nkv, d)
+        ref = plain_attention(x[s, :nh * d].reshape(nh, d), ks[s], vs[s], L - 1, window, scale)
+        assert rel(got[s].float().cpu().reshape(nh, d), ref) < 1e-2, s
+    # what the kernel cannot do itself is refused, not approximated
+    with pytest.raises(o.KernelError):
+        o.decode_attention(qkv0.float(), kp0.float(), vp0.float(), table, ps, positions, token_seq, seq_slot,
+                           torch.zeros(B, nh * d, device=DEV), nh, nkv, d, window, scale, 0, 1, pa, pm, store_new=True)
