@@ -238,6 +238,25 @@ def main() -> int:
                "flops": pre_flops, "runs_ms": pre_runs,
                "spread_pct": 100.0 * (max(pre_runs) - min(pre_runs)) / pre_ms}
 
+    # ---- the same prompt in portions of 256 tokens (a small token budget: every portion but the first sits behind
+    # a cached prefix, which the prompt attention cuts into runs of key blocks) ------------------------------------
+    def portions_once(portion=256):
+        slot = eng.open_request()
+        toks = random_prompt(PREFILL_TOKENS)
+        for i in range(0, PREFILL_TOKENS, portion):
+            last = i + portion >= PREFILL_TOKENS
+            eng.step([StepEntry(slot, toks[i:i + portion], want=[len(toks[i:i + portion]) - 1] if last else [])], check=False)
+        return slot
+
+    eng.close_request(portions_once())
+    por_runs = []
+    for _ in range(3):
+        por_runs.append(timed(lambda: holder.__setitem__("s", portions_once())))
+        eng.close_request(holder["s"])
+    por_ms = statistics.median(por_runs)
+    prefill["portions_of_256"] = {"value": PREFILL_TOKENS / (por_ms / 1e3), "ms": por_ms, "steps": PREFILL_TOKENS // 256,
+                                  "runs_ms": por_runs}
+
     # ---- decode ------------------------------------------------------------------
     def decode_run(batch, steps, warmup, repeats, sample_clocks=False):
         """``repeats`` timed regions of ``steps`` decode steps each, back to back on the same requests.  Returns the
