@@ -83,6 +83,9 @@ class Sampler:
         temp = torch.tensor([p.temperature if not p.greedy else 1.0 for p in params], dtype=torch.float32, device=dev)
         top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=dev)
         top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32, device=dev)
+        # (the reference draws only once the filtered mass has turned out positive, sampling.rs:160-168: a request
+        # whose candidates were all filtered away gets its generator's state back below)
+        before = [r.state for r in rngs]
         draws = [r.next_f32() if not p.greedy else 0.0 for p, r in zip(params, rngs)]
         draw = torch.tensor(draws, dtype=torch.float32, device=dev)
         sampled = torch.empty(n, dtype=torch.int32, device=dev)
@@ -95,7 +98,8 @@ class Sampler:
                 result.append(greedy_ids[i])
             elif sampled[i] >= 0:
                 result.append(sampled[i])
-            else:  # every candidate filtered away: greedy on the untouched logits (sampling.rs:160-165)
+            else:  # every candidate filtered away: greedy on the untouched logits (sampling.rs:160-165), no draw used
+                rngs[i].state = before[i]
                 if fallback is None:
                     fallback = ops.argmax(logits, torch.empty(n, dtype=torch.int32, device=dev)).tolist()
                 result.append(fallback[i])
