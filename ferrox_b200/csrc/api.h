@@ -70,6 +70,9 @@ int fx_route(const float* logits, long ld, int n_tokens, int n_experts, int top_
              int* scratch, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
 int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
                    int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
+int fx_route_fused(const void* X, long ldx, const void* W, long ldw, int n_tokens, int n_route, int n_experts, int hidden,
+                   int top_k, int renorm, float* logits, long ldl, int* ids, float* weights, int* offsets, int* src_token,
+                   int* inv_perm, int* active, int n_slots, void* xp_out, long ldxp, void* stream);
 int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin, void* stream);
 int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, long ldw, long w_group_stride,
                    const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int n_tokens,

@@ -63,21 +63,19 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, in
 
 // Routing and bookkeeping of a small step in ONE block: top-k per token (a warp
 // each), then counts, offsets, the list of experts that got rows, and the placement
-// of every (token, rank) pair, all in shared memory.
-constexpr int SMALL_WARPS = 32;
-__global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
-    const float* __restrict__ logits, long ld, int n_tokens, int n_experts, int top_k, int renorm,
-    int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ src_token, int* __restrict__ inv_perm,
-    int* __restrict__ active, int n_slots)
+// of every (token, rank) pair, all in shared memory.  `p_scratch`: [warps][n_experts]
+// floats, `counts`: 2 * n_experts + 1 ints, both in shared memory.
+__device__ __forceinline__ void route_in_block(const float* lg, long ld, float* p_scratch, int* counts, int n_warps,
+                                               int n_tokens, int n_experts, int top_k, int renorm,
+                                               int* __restrict__ ids, float* __restrict__ weights,
+                                               int* __restrict__ offsets, int* __restrict__ src_token,
+                                               int* __restrict__ inv_perm, int* __restrict__ active, int n_slots)
 {
-    extern __shared__ float smem[];  // [SMALL_WARPS][n_experts] floats, then 2 * n_experts + 1 ints
-    fx_pdl_wait();
-    int* counts = reinterpret_cast<int*>(smem + (long)SMALL_WARPS * n_experts);
     int* offs = counts + n_experts;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
-    for (int t = warp; t < n_tokens; t += SMALL_WARPS) {
-        route_token(logits + (long)t * ld, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
+    for (int t = warp; t < n_tokens; t += n_warps) {
+        route_token(lg + (long)t * ld, p_scratch + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
                     weights);
         __syncwarp();
     }
@@ -101,6 +99,130 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
         const int r = offs[e] + atomicAdd(&counts[e], 1);
         src_token[r] = i / top_k;
         inv_perm[i] = r;
+    }
+}
+
+constexpr int SMALL_WARPS = 32;
+__global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
+    const float* __restrict__ logits, long ld, int n_tokens, int n_experts, int top_k, int renorm,
+    int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ src_token, int* __restrict__ inv_perm,
+    int* __restrict__ active, int n_slots)
+{
+    extern __shared__ float smem[];  // [SMALL_WARPS][n_experts] floats, then 2 * n_experts + 1 ints
+    fx_pdl_wait();
+    int* counts = reinterpret_cast<int*>(smem + (long)SMALL_WARPS * n_experts);
+    route_in_block(logits, ld, smem, counts, SMALL_WARPS, n_tokens, n_experts, top_k, renorm, ids, weights, offsets,
+                   src_token, inv_perm, active, n_slots);
+}
+
+// What stands between the norm and the experts in a decode step of a few tokens, in ONE launch of one cluster of
+// FUSED_CTAS blocks instead of three dependent launches (each costs a few microseconds of waiting for the one before):
+//   1. the router's product: the blocks share the rows of W (a warp a row: its dot products with every token, 32-bit
+//      sums); every warp puts its logits into the first block's shared memory (DSMEM) and into logits_out, which
+//      later kernels read for rows beyond the experts' (a gate's logit);
+//   2. after the cluster's barrier the first block routes as route_small_kernel does;
+//   3. (optional) and copies each (token, rank) pair's row of x into expert order (xp_out), for kernels that want
+//      an expert's rows side by side.
+// n_route >= n_experts rows of W; the first n_experts are routed over.  (The norm before it was taken in as well,
+// measured and left out: the shared expert, which needs only the normed rows, would wait for the whole kernel.)
+struct FusedArgs {
+    const bf16* X; long ldx;                 // the tokens' rows
+    const bf16* W; long ldw;
+    int n_tokens, n_route, n_experts, hidden, top_k, renorm;
+    float* logits_out; long ldl;
+    int* ids; float* weights; int* offsets; int* src_token; int* inv_perm; int* active; int n_slots;
+    bf16* xp_out; long ldxp;                 // rows in expert order (may be null)
+};
+
+constexpr int FUSED_CTAS = 8, FUSED_WARPS = 8, FUSED_PASS = 8;   // a pass: 8 x 16 bytes a lane = 2,048 elements a warp
+template <int NT>
+__global__ void __launch_bounds__(FUSED_WARPS * 32) route_fused_kernel(FusedArgs a)
+{
+    // every block: the tokens' rows [NT][hidden] bfloat16; the first block behind them: logits [NT][n_route],
+    // p [FUSED_WARPS][n_experts], 2 n_experts + 1 ints
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* x_s = reinterpret_cast<bf16*>(smem_raw);
+    float* lg_s = reinterpret_cast<float*>(smem_raw + (size_t)NT * a.hidden * sizeof(bf16));
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hidden = a.hidden, n_route = a.n_route, n_tokens = a.n_tokens;
+    const int rows_per_cta = (n_route + FUSED_CTAS - 1) / FUSED_CTAS;
+    const int row_begin = rank * rows_per_cta, row_end = min(n_route, row_begin + rows_per_cta);
+    const int n_vec = hidden >> 3;                       // 16-byte pieces of a row
+    // the first block's logits as every block of the cluster addresses them
+    uint32_t lg_remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(lg_remote) : "r"((uint32_t)__cvta_generic_to_shared(lg_s)), "r"(0));
+
+    uint4 wv[FUSED_PASS];
+    auto load_w = [&](int row, int v0) {
+#pragma unroll
+        for (int u = 0; u < FUSED_PASS; ++u) {
+            const int v = v0 + u * 32 + lane;
+            wv[u] = v < n_vec ? *reinterpret_cast<const uint4*>(a.W + (long)row * a.ldw + (long)v * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    // the weights do not depend on the kernel before this one: the first pass is on its way before the wait
+    if (row_begin + warp < row_end) load_w(row_begin + warp, 0);
+    fx_pdl_wait();
+    // the tokens' rows into shared memory, all loads of a thread in flight together (rows beyond the step's: zeros)
+    for (int i = threadIdx.x; i < NT * n_vec; i += FUSED_WARPS * 32) {
+        const int t = i / n_vec, v = i - t * n_vec;
+        reinterpret_cast<uint4*>(x_s)[i] = t < n_tokens ? *reinterpret_cast<const uint4*>(a.X + (long)t * a.ldx + (long)v * 8)
+                                                        : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    for (int row = row_begin + warp; row < row_end; row += FUSED_WARPS) {
+        float acc[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) acc[t] = 0.f;
+        for (int v0 = 0; v0 < n_vec; v0 += FUSED_PASS * 32) {
+            if (!(row == row_begin + warp && v0 == 0)) load_w(row, v0);
+#pragma unroll
+            for (int u = 0; u < FUSED_PASS; ++u) {
+                const int v = min(v0 + u * 32 + lane, n_vec - 1);   // (beyond the row the weights are zeros)
+                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
+                float2 wf[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) wf[i] = __bfloat1622float2(w2[i]);
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const uint4 xv = reinterpret_cast<const uint4*>(x_s)[t * n_vec + v];
+                    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 b = __bfloat1622float2(x2[i]);
+                        acc[t] = fmaf(wf[i].x, b.x, acc[t]);
+                        acc[t] = fmaf(wf[i].y, b.y, acc[t]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const float v = warp_sum(acc[t]);
+            if (lane == 0 && t < n_tokens) {
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(lg_remote + 4u * (uint32_t)(t * n_route + row)), "f"(v) : "memory");
+                a.logits_out[(long)t * a.ldl + row] = v;
+            }
+        }
+    }
+    // every block's logits are in the first block's shared memory after the cluster's barrier
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank != 0) return;
+    float* p_scratch = lg_s + (long)NT * n_route;
+    int* counts = reinterpret_cast<int*>(p_scratch + (long)FUSED_WARPS * a.n_experts);
+    route_in_block(lg_s, n_route, p_scratch, counts, FUSED_WARPS, n_tokens, a.n_experts, a.top_k, a.renorm, a.ids, a.weights,
+                   a.offsets, a.src_token, a.inv_perm, a.active, a.n_slots);
+    if (a.xp_out) {
+        // the rows in expert order, out of shared memory (src_token was written by this block: visible after a barrier)
+        __syncthreads();
+        const int n = n_tokens * a.top_k;
+        for (int i = threadIdx.x; i < n * n_vec; i += FUSED_WARPS * 32) {
+            const int r = i / n_vec, v = i - r * n_vec;
+            *reinterpret_cast<uint4*>(a.xp_out + (long)r * a.ldxp + v * 8) = reinterpret_cast<const uint4*>(x_s)[a.src_token[r] * n_vec + v];
+        }
     }
 }
 
@@ -236,6 +358,63 @@ extern "C" int fx_route_small(const float* logits, long ld, int n_tokens, int n_
     fx_launch_pdl(route_small_kernel, 1, SMALL_WARPS * 32, smem, (cudaStream_t)stream,
         logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active, n_slots);
     return fx_launch_status();
+}
+
+template <int NT>
+static int launch_route_fused(size_t smem, cudaStream_t s, const FusedArgs& a)
+{
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(route_fused_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(FUSED_CTAS);
+    cfg.blockDim = dim3(FUSED_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = FUSED_CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_fx_pdl_enabled ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, route_fused_kernel<NT>, a);
+    return fx_launch_status();
+}
+
+// One launch for what stands between the norm and the experts in a step of at most 8 tokens (see route_fused_kernel).
+// X [n_tokens, hidden] and W [n_route, hidden] bfloat16; logits [n_tokens, n_route] 32-bit; the routing outputs as
+// fx_route_small; xp_out (optional) [n_tokens * top_k, hidden] the rows in expert order.  Rows of a multiple of 8
+// elements, 16-byte aligned.  Refuses other sizes (FX_ERR_SIZE / FX_ERR_ALIGN): the caller then runs the separate kernels.
+extern "C" int fx_route_fused(const void* X, long ldx, const void* W, long ldw, int n_tokens, int n_route,
+                              int n_experts, int hidden, int top_k, int renorm, float* logits, long ldl, int* ids,
+                              float* weights, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots,
+                              void* xp_out, long ldxp, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (n_tokens > 8 || top_k <= 0 || top_k > n_experts || n_experts > n_route || n_route > 1024 || hidden <= 0)
+        return FX_ERR_SIZE;
+    if (hidden % 8 || ldw % 8 || (uintptr_t)W % 16 || ldx % 8 || (uintptr_t)X % 16) return FX_ERR_ALIGN;
+    if (xp_out && (ldxp % 8 || (uintptr_t)xp_out % 16)) return FX_ERR_ALIGN;
+    const int nt = n_tokens <= 1 ? 1 : n_tokens <= 2 ? 2 : n_tokens <= 4 ? 4 : 8;
+    const size_t smem = (size_t)nt * hidden * sizeof(bf16) + ((size_t)nt * n_route + (size_t)FUSED_WARPS * n_experts) * sizeof(float) +
+                        (2 * (size_t)n_experts + 1) * sizeof(int);
+    if (smem > 200 * 1024) return FX_ERR_SIZE;
+    FusedArgs a;
+    a.X = (const bf16*)X; a.ldx = ldx; a.W = (const bf16*)W; a.ldw = ldw;
+    a.n_tokens = n_tokens; a.n_route = n_route; a.n_experts = n_experts; a.hidden = hidden; a.top_k = top_k; a.renorm = renorm;
+    a.logits_out = logits; a.ldl = ldl; a.ids = ids; a.weights = weights; a.offsets = offsets; a.src_token = src_token;
+    a.inv_perm = inv_perm; a.active = active; a.n_slots = n_slots; a.xp_out = (bf16*)xp_out; a.ldxp = ldxp;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (nt) {
+        case 1: return launch_route_fused<1>(smem, s, a);
+        case 2: return launch_route_fused<2>(smem, s, a);
+        case 4: return launch_route_fused<4>(smem, s, a);
+        default: return launch_route_fused<8>(smem, s, a);
+    }
 }
 
 // scratch: 2 * n_experts ints (counts, cursors).  Outputs: offsets [E+1],

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
     "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P],
+    "fx_route_fused": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P],
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P],
     "fx_moe_combine_norm": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P, _I, _F, _P, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
@@ -295,6 +296,36 @@ def route_small(logits, top_k, renorm, ids, weights, offsets, src_token, inv_per
     T, E = logits.shape[0], (n_experts or logits.shape[1])
     call("fx_route_small", _ptr(logits), _rows(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights), _ptr(offsets),
          _ptr(src_token), _ptr(inv_perm), _ptr(active), active.numel() if active is not None else 0,
+         stream if stream is not None else stream_ptr())
+
+
+ROUTE_FUSED_MAX_TOKENS = 8     # the kernel keeps a sum per token in registers
+ROUTE_FUSED_MAX_ROWS = 1024
+
+
+def route_fused_ok(x, w_route, n_experts: int) -> bool:
+    """Whether :func:`route_fused` takes these operands."""
+    T, H = x.shape
+    R = w_route.shape[0]
+    smem = 8 * H * 2 + (8 * R + 8 * n_experts) * 4 + (2 * n_experts + 1) * 4
+    return (T <= ROUTE_FUSED_MAX_TOKENS and x.dtype == torch.bfloat16 and w_route.dtype == torch.bfloat16
+            and w_route.dim() == 2 and R <= ROUTE_FUSED_MAX_ROWS and smem <= 200 * 1024 and H % 8 == 0
+            and w_route.shape[1] == H and x.stride(0) % 8 == 0 and w_route.stride(0) % 8 == 0 and x.stride(1) == 1
+            and w_route.stride(1) == 1 and x.data_ptr() % 16 == 0 and w_route.data_ptr() % 16 == 0)
+
+
+def route_fused(x, w_route, logits, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active=None, n_experts=None,
+                xp_out=None, stream=None):
+    """What stands between the norm and the experts in a step of a few tokens, in one launch of one thread-block
+    cluster (see :func:`route_fused_ok`): the router's product logits = x . w_route^T (32-bit sums; ``w_route`` may carry
+    rows beyond the experts', whose logits later kernels read), :func:`route_small` on the first ``n_experts`` columns
+    and, with ``xp_out`` [tokens * top_k, hidden], the rows of ``x`` copied into expert order."""
+    T, H = x.shape
+    R = w_route.shape[0]
+    E = n_experts or R
+    call("fx_route_fused", _ptr(x), _rows(x), _ptr(w_route), _rows(w_route), T, R, E, H, top_k, int(renorm), _ptr(logits),
+         _rows(logits), _ptr(ids), _ptr(weights), _ptr(offsets), _ptr(src_token), _ptr(inv_perm), _ptr(active),
+         active.numel() if active is not None else 0, _ptr(xp_out), _rows(xp_out) if xp_out is not None else 0,
          stream if stream is not None else stream_ptr())
 
 

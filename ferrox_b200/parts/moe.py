@@ -106,10 +106,21 @@ class SoftmaxTopkMoe(FeedForward):
         ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
         return shared
 
+    def _shared_on_side(self, x, batch):
+        """The shared expert's two products on the second stream, from the point the fork event marks."""
+        self._side.wait_event(self._fork)
+        with torch.cuda.stream(self._side):
+            out = self._shared_expert(x, batch, self._side.cuda_stream)
+            self._join.record(self._side)
+        return out
+
     def forward_add(self, x, h, batch, then_norm=None):
         s, rt, st = self.spec, self.rt, batch.stream
         T, E, K, I, H = x.shape[0], s.n_experts, s.top_k, s.expert_intermediate, s.hidden
         i32 = torch.int32
+        # A decode step of a few tokens: the router's product, the routing and the rows in expert order come from ONE
+        # kernel (three dependent launches otherwise, each a few microseconds of waiting for the one before).
+        fused = ops.route_fused_ok(x, self.w_route, E)
         tc = ops.tc_ok(x, self.w_gu) and I % 8 == 0 and E <= ops.TC_MAX_GROUPS
         tiles = expert_tile_tokens(T, K, E) if tc and T >= SWAP_MIN_TOKENS and E <= ops.TC_SWAP_MAX_GROUPS else None
         small = tiles is None and T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
@@ -121,25 +132,35 @@ class SoftmaxTopkMoe(FeedForward):
         # B200: 3 to 10 % of a decode step of 8 to 64 tokens, 14 % of a prompt portion of 256 tokens, 4 % at 2,048.
         shared = None
         overlap = self.w_shared_gu is not None
+
         if overlap:
             main = torch.cuda.current_stream()
-            self._fork.record(main)
-            self._side.wait_event(self._fork)
-            with torch.cuda.stream(self._side):
-                shared = self._shared_expert(x, batch, self._side.cuda_stream)
-                self._join.record(self._side)
+            self._fork.record(main)          # the shared expert may start from here on
+            if not fused:
+                shared = self._shared_on_side(x, batch)
         logits = rt.empty(T, n_route, dtype=torch.float32)
-        ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
         ids = rt.empty(T, K, dtype=i32)
         weights = rt.empty(T, K, dtype=torch.float32)
         offsets = rt.empty(E + 1, dtype=i32)
         src_token = rt.empty(T * K, dtype=i32)
         inv_perm = rt.empty(T * K, dtype=i32)
         active = rt.empty(min(E, T * K), dtype=i32) if small else None
-        if T <= ops.ROUTE_SMALL_MAX_TOKENS and E <= ops.ROUTE_SMALL_MAX_EXPERTS:
+        xp = None
+        if fused:
+            # The cluster's kernel goes first: it needs eight free SMs of one GPC at once, which it finds now and would
+            # not find once the shared expert's weight-streaming kernels (enqueued right after it, waiting only for what
+            # was before it) fill every SM.
+            xp = rt.empty(T * K, H) if tiles is not None else None
+            ops.route_fused(x, self.w_route, logits, K, s.norm_topk_prob, ids, weights, offsets, src_token, inv_perm, active,
+                            n_experts=E, xp_out=xp, stream=st)
+            if overlap:
+                shared = self._shared_on_side(x, batch)
+        elif T <= ops.ROUTE_SMALL_MAX_TOKENS and E <= ops.ROUTE_SMALL_MAX_EXPERTS:
+            ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
             ops.route_small(logits, K, s.norm_topk_prob, ids, weights, offsets, src_token, inv_perm, active,
                             n_experts=E, stream=st)
         else:
+            ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
             ops.route(logits, K, s.norm_topk_prob, ids, weights, self._scratch, offsets, src_token, inv_perm, active,
                       n_experts=E, stream=st)
 
@@ -148,11 +169,13 @@ class SoftmaxTopkMoe(FeedForward):
         if tiles is not None:
             # a few rows for each expert: rows in expert order, then features in the lanes of the tensor-core tiles
             # and the expert's rows in their columns
-            xp = rt.empty(T * K, H)
-            ops.gather_rows(x, src_token, xp, stream=st)
-            # (the offsets were written by the routing, before the gather: both products may fetch weights early)
+            if xp is None:
+                xp = rt.empty(T * K, H)
+                ops.gather_rows(x, src_token, xp, stream=st)
+            # (the offsets were written by the routing, before the gather: both products may fetch weights early;
+            # when one kernel did both, the first product waits for it before it reads the offsets)
             ops.gemm_tc_swap(xp, self.w_gu, act, gated=True, group_offsets=offsets, tokens_per_tile=tiles[0],
-                             weights_first=True, status=batch.status, stream=st)
+                             weights_first=not fused, status=batch.status, stream=st)
             ops.gemm_tc_swap(act, self.w_down, y, group_offsets=offsets, tokens_per_tile=tiles[1],
                              weights_first=True, status=batch.status, stream=st)
         elif small:

@@ -1006,3 +1006,41 @@ def test_decode_attention_does_the_rotary_kernels_work_itself(nh, nkv, d, ps, wi
     with pytest.raises(o.KernelError):
         o.decode_attention(qkv0.float(), kp0.float(), vp0.float(), table, ps, positions, token_seq, seq_slot,
                            torch.zeros(B, nh * d, device=DEV), nh, nkv, d, window, scale, 0, 1, pa, pm, store_new=True)
+
+
+# ------------------------------------------------------------------ router product, routing and gather in one launch
+@pytest.mark.parametrize("T,E,K,H,extra", [(1, 60, 4, 2048, 1), (8, 60, 4, 2048, 1), (3, 5, 1, 80, 0), (7, 64, 8, 3584, 0),
+                                           (2, 131, 6, 520, 1), (5, 8, 3, 128, 1)])
+def test_route_fused_is_product_routing_and_gather(T, E, K, H, extra):
+    """One cluster does what three kernels do: logits = x . w^T (E router rows and `extra` further rows, 32-bit sums),
+    the routing over the first E, and the rows in expert order.  The logits against a 32-bit product, everything else
+    equal to route_small run on those very logits, the gathered rows equal to the rows they copy."""
+    o = ops()
+    x = rnd(T + 1, H + 8, dtype=torch.bfloat16, seed=T)[1:, :H]        # a strided view
+    w = rnd(E + extra, H, dtype=torch.bfloat16, scale=0.3, seed=E)
+    assert o.route_fused_ok(x, w, E)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    R = E + extra
+    for renorm in (False, True):
+        for gather in (True, False):
+            logits = torch.full((T, R), float("nan"), device=DEV)
+            ids_a, w_a = torch.empty(T, K, **i32), torch.empty(T, K, device=DEV)
+            offsets, src, inv = torch.empty(E + 1, **i32), torch.empty(T * K, **i32), torch.empty(T * K, **i32)
+            active = torch.empty(min(E, T * K), **i32)
+            xp = torch.full((T * K, H), float("nan"), dtype=torch.bfloat16, device=DEV) if gather else None
+            o.route_fused(x, w, logits, K, renorm, ids_a, w_a, offsets, src, inv, active, n_experts=E, xp_out=xp)
+            assert rel(logits, x.float() @ w.float().T) < 3e-6
+            ids_b, w_b = torch.empty(T, K, **i32), torch.empty(T, K, device=DEV)
+            off_b, src_b, inv_b = torch.empty(E + 1, **i32), torch.empty(T * K, **i32), torch.empty(T * K, **i32)
+            act_b = torch.empty(min(E, T * K), **i32)
+            o.route_small(logits, K, renorm, ids_b, w_b, off_b, src_b, inv_b, act_b, n_experts=E)
+            assert torch.equal(ids_a, ids_b) and torch.equal(w_a, w_b) and torch.equal(offsets, off_b)
+            assert torch.equal(active, act_b)
+            flat = ids_a.flatten().tolist()
+            assert sorted(inv.tolist()) == list(range(T * K))
+            for i, r in enumerate(inv.tolist()):
+                assert int(offsets[flat[i]]) <= r < int(offsets[flat[i] + 1]) and int(src[r]) == i // K
+            if gather:
+                assert torch.equal(xp, x[src.long()])
+    # what it does not take is said beforehand
+    assert not o.route_fused_ok(rnd(9, H, dtype=torch.bfloat16), w, E) and not o.route_fused_ok(x.float(), w, E)
