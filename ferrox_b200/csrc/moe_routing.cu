@@ -16,7 +16,7 @@ namespace {
 // warp reductions instead of two chains of shuffles.  `counts` (optional): counts[e] += 1 for each kept expert.
 __device__ __forceinline__ void route_token(const float* __restrict__ lg, float* p, int lane, int t, int n_experts,
                                             int top_k, int renorm, int* __restrict__ ids, float* __restrict__ weights,
-                                            int* __restrict__ counts = nullptr)
+                                            int* __restrict__ counts = nullptr, int* ids_shared = nullptr)
 {
     uint32_t* pb = reinterpret_cast<uint32_t*>(p);
     float mx = -INFINITY;
@@ -26,7 +26,10 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
     for (int e = lane; e < n_experts; e += 32) { const float v = expf(lg[e] - mx); pb[e] = __float_as_uint(v) + 1u; sum += v; }
     sum = warp_sum(sum);
     __syncwarp();
-    float kept = 0.f;
+    // up to 32 kept experts stay in registers (lane k holds the k-th) and are written once, side by side
+    const bool in_regs = top_k <= 32;
+    float kept = 0.f, mine_w = 0.f;
+    int mine_e = 0;
     for (int k = 0; k < top_k; ++k) {
         uint32_t best = 0u; int best_e = 0x7fffffff;
         for (int e = lane; e < n_experts; e += 32) {
@@ -37,13 +40,25 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
         const int win = __reduce_min_sync(0xffffffffu, best == top ? best_e : 0x7fffffff);
         const float w = __uint_as_float(top - 1u) / sum;
         if (lane == 0) {
-            ids[(long)t * top_k + k] = win; weights[(long)t * top_k + k] = w; pb[win] = 0u;
-            if (counts) atomicAdd(&counts[win], 1);
+            pb[win] = 0u;
+            if (!in_regs) {
+                ids[(long)t * top_k + k] = win; weights[(long)t * top_k + k] = w;
+                if (ids_shared) ids_shared[t * top_k + k] = win;
+                if (counts) atomicAdd(&counts[win], 1);
+            }
         }
+        if (lane == k) { mine_w = w; mine_e = win; }
         kept += w;
         __syncwarp();
     }
-    if (renorm) {
+    if (in_regs) {
+        if (lane < top_k) {
+            ids[(long)t * top_k + lane] = mine_e;
+            weights[(long)t * top_k + lane] = renorm ? mine_w / kept : mine_w;
+            if (ids_shared) ids_shared[t * top_k + lane] = mine_e;
+            if (counts) atomicAdd(&counts[mine_e], 1);
+        }
+    } else if (renorm) {
         __syncwarp();
         for (int k = lane; k < top_k; k += 32) weights[(long)t * top_k + k] /= kept;
     }
@@ -69,35 +84,51 @@ __device__ __forceinline__ void route_in_block(const float* lg, long ld, float* 
                                                int n_tokens, int n_experts, int top_k, int renorm,
                                                int* __restrict__ ids, float* __restrict__ weights,
                                                int* __restrict__ offsets, int* __restrict__ src_token,
-                                               int* __restrict__ inv_perm, int* __restrict__ active, int n_slots)
+                                               int* __restrict__ inv_perm, int* __restrict__ active, int n_slots,
+                                               int* ids_s = nullptr, int* src_s = nullptr)
 {
+    // ids_s, src_s (optional, shared memory, n_tokens * top_k ints each): the block keeps what it chose and where it
+    // put it beside the copies in global memory, so that it (and its caller) need not read those back
     int* offs = counts + n_experts;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
     for (int t = warp; t < n_tokens; t += n_warps) {
         route_token(lg + (long)t * ld, p_scratch + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
-                    weights);
+                    weights, counts, ids_s);
         __syncwarp();
     }
     __syncthreads();  // ids written by this block are visible to it after the barrier
+    const int* ids_r = ids_s ? ids_s : ids;
     const int n = n_tokens * top_k;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&counts[ids[i]], 1);
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    if (warp == 0) {
+        // offsets = running sum of the counts, 32 experts a pass; the experts with rows, in ascending order
         int run = 0, n_active = 0;
-        for (int e = 0; e < n_experts; ++e) {
-            offs[e] = run; offsets[e] = run; run += counts[e];
-            if (active && counts[e] > 0 && n_active < n_slots) active[n_active++] = e;
-            counts[e] = 0;  // becomes the cursor
+        for (int e0 = 0; e0 < n_experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < n_experts ? counts[e] : 0;
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+            const int off = run + incl - c;
+            if (e < n_experts) { offs[e] = off; offsets[e] = off; counts[e] = 0; }  // the count becomes the cursor
+            const unsigned has = __ballot_sync(0xffffffffu, c > 0);
+            if (active && c > 0) {
+                const int slot = n_active + __popc(has & ((1u << lane) - 1u));
+                if (slot < n_slots) active[slot] = e;
+            }
+            n_active += __popc(has);
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        offsets[n_experts] = run;
-        if (active) for (int i = n_active; i < n_slots; ++i) active[i] = -1;
+        if (lane == 0) offsets[n_experts] = run;
+        if (active) for (int i = min(n_active, n_slots) + lane; i < n_slots; i += 32) active[i] = -1;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int e = ids[i];
+        const int e = ids_r[i];
         const int r = offs[e] + atomicAdd(&counts[e], 1);
         src_token[r] = i / top_k;
+        if (src_s) src_s[r] = i / top_k;
         inv_perm[i] = r;
     }
 }
@@ -213,15 +244,19 @@ __global__ void __launch_bounds__(FUSED_WARPS * 32) route_fused_kernel(FusedArgs
     if (rank != 0) return;
     float* p_scratch = lg_s + (long)NT * n_route;
     int* counts = reinterpret_cast<int*>(p_scratch + (long)FUSED_WARPS * a.n_experts);
+    int* ids_s = counts + 2 * a.n_experts + 1;      // [NT * top_k], then src_s [NT * top_k]
+    int* src_s = ids_s + NT * a.top_k;
     route_in_block(lg_s, n_route, p_scratch, counts, FUSED_WARPS, n_tokens, a.n_experts, a.top_k, a.renorm, a.ids, a.weights,
-                   a.offsets, a.src_token, a.inv_perm, a.active, a.n_slots);
+                   a.offsets, a.src_token, a.inv_perm, a.active, a.n_slots, ids_s, src_s);
     if (a.xp_out) {
-        // the rows in expert order, out of shared memory (src_token was written by this block: visible after a barrier)
+        // the rows in expert order, out of shared memory: a warp a row, 16 bytes a lane and pass
         __syncthreads();
         const int n = n_tokens * a.top_k;
-        for (int i = threadIdx.x; i < n * n_vec; i += FUSED_WARPS * 32) {
-            const int r = i / n_vec, v = i - r * n_vec;
-            *reinterpret_cast<uint4*>(a.xp_out + (long)r * a.ldxp + v * 8) = reinterpret_cast<const uint4*>(x_s)[a.src_token[r] * n_vec + v];
+        for (int r = warp; r < n; r += FUSED_WARPS) {
+            const uint4* src = reinterpret_cast<const uint4*>(x_s) + (long)src_s[r] * n_vec;
+            uint4* dst = reinterpret_cast<uint4*>(a.xp_out + (long)r * a.ldxp);
+#pragma unroll 4
+            for (int v = lane; v < n_vec; v += 32) dst[v] = src[v];
         }
     }
 }
@@ -395,13 +430,13 @@ extern "C" int fx_route_fused(const void* X, long ldx, const void* W, long ldw, 
                               void* xp_out, long ldxp, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
-    if (n_tokens > 8 || top_k <= 0 || top_k > n_experts || n_experts > n_route || n_route > 1024 || hidden <= 0)
+    if (n_tokens > 8 || top_k <= 0 || top_k > n_experts || top_k > 64 || n_experts > n_route || n_route > 1024 || hidden <= 0)
         return FX_ERR_SIZE;
     if (hidden % 8 || ldw % 8 || (uintptr_t)W % 16 || ldx % 8 || (uintptr_t)X % 16) return FX_ERR_ALIGN;
     if (xp_out && (ldxp % 8 || (uintptr_t)xp_out % 16)) return FX_ERR_ALIGN;
     const int nt = n_tokens <= 1 ? 1 : n_tokens <= 2 ? 2 : n_tokens <= 4 ? 4 : 8;
     const size_t smem = (size_t)nt * hidden * sizeof(bf16) + ((size_t)nt * n_route + (size_t)FUSED_WARPS * n_experts) * sizeof(float) +
-                        (2 * (size_t)n_experts + 1) * sizeof(int);
+                        (2 * (size_t)n_experts + 1 + 2 * (size_t)nt * top_k) * sizeof(int);
     if (smem > 200 * 1024) return FX_ERR_SIZE;
     FusedArgs a;
     a.X = (const bf16*)X; a.ldx = ldx; a.W = (const bf16*)W; a.ldw = ldw;

@@ -303,12 +303,12 @@ ROUTE_FUSED_MAX_TOKENS = 8     # the kernel keeps a sum per token in registers
 ROUTE_FUSED_MAX_ROWS = 1024
 
 
-def route_fused_ok(x, w_route, n_experts: int) -> bool:
+def route_fused_ok(x, w_route, n_experts: int, top_k: int = 1) -> bool:
     """Whether :func:`route_fused` takes these operands."""
     T, H = x.shape
     R = w_route.shape[0]
-    smem = 8 * H * 2 + (8 * R + 8 * n_experts) * 4 + (2 * n_experts + 1) * 4
-    return (T <= ROUTE_FUSED_MAX_TOKENS and x.dtype == torch.bfloat16 and w_route.dtype == torch.bfloat16
+    smem = 8 * H * 2 + (8 * R + 8 * n_experts) * 4 + (2 * n_experts + 1 + 16 * top_k) * 4
+    return (T <= ROUTE_FUSED_MAX_TOKENS and top_k <= 64 and x.dtype == torch.bfloat16 and w_route.dtype == torch.bfloat16
             and w_route.dim() == 2 and R <= ROUTE_FUSED_MAX_ROWS and smem <= 200 * 1024 and H % 8 == 0
             and w_route.shape[1] == H and x.stride(0) % 8 == 0 and w_route.stride(0) % 8 == 0 and x.stride(1) == 1
             and w_route.stride(1) == 1 and x.data_ptr() % 16 == 0 and w_route.data_ptr() % 16 == 0)

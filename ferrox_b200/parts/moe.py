@@ -120,7 +120,7 @@ class SoftmaxTopkMoe(FeedForward):
         i32 = torch.int32
         # A decode step of a few tokens: the router's product, the routing and the rows in expert order come from ONE
         # kernel (three dependent launches otherwise, each a few microseconds of waiting for the one before).
-        fused = ops.route_fused_ok(x, self.w_route, E)
+        fused = ops.route_fused_ok(x, self.w_route, E, K)
         tc = ops.tc_ok(x, self.w_gu) and I % 8 == 0 and E <= ops.TC_MAX_GROUPS
         tiles = expert_tile_tokens(T, K, E) if tc and T >= SWAP_MIN_TOKENS and E <= ops.TC_SWAP_MAX_GROUPS else None
         small = tiles is None and T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
