@@ -153,8 +153,10 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
                 const int page = page_next;
                 if (j + 1 < n_tiles) page_next = table[(key0 + TK) / a.page_size];
                 // The kernel before this one wrote the keys and values of the step's own positions (the last
-                // a.fresh of a request at most); a tile that ends before them may be asked for at once.
-                if (!waited && key0 + TK > pos + 1 - a.fresh) { fx_pdl_wait(); waited = true; }
+                // a.fresh of a request at most); a tile that ends before them may be asked for at once.  With
+                // store_new it wrote no key at all: this kernel puts the token's own row into its copy of the tile
+                // after the tile has arrived, whatever the page held.
+                if (!waited && !a.store_new && key0 + TK > pos + 1 - a.fresh) { fx_pdl_wait(); waited = true; }
                 if (j >= stages && !mbar_wait(empty(s), ((j / stages) - 1) & 1, abort_flag)) break;
                 page_ok_s[s] = page >= 0;
                 if (page >= 0) {
@@ -174,12 +176,27 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
         }
     } else {
         // ---------------- four scoring warps ----------------
-        fx_pdl_wait();
         const int g = lane >> 2, t4 = lane & 3;
         const int chunks_row = head_dim / 8;                   // 16-byte chunks per row
         const int half_d = head_dim >> 1;
         // store_new: the warp whose 16 keys of the last tile hold the token's own position prepares that key and value
         const bool owns_new = a.store_new && pos >= k_begin && pos < k_end && warp == ((pos % TK) >> 4);
+        const bool writes_page = owns_new && a.write_pages && blockIdx.x % chunks == 0;
+        // (the table is not the work of the kernel before this one: the page is looked up before the wait for it)
+        const int new_page = writes_page ? a.block_table[(long)a.seq_slot[seq] * a.table_width + pos / a.page_size] : -1;
+        fx_pdl_wait();
+        // query rows of this block (zero beyond the group): on their way while the new key is prepared
+        for (int c = threadIdx.x; c < 16 * chunks_row; c += NCONSUMERS) {
+            const int r = c / chunks_row, ch = c - r * chunks_row;
+            const bf16* src = a.q + (long)tkn * a.ldq + (long)(h0 + min(r, nq - 1)) * head_dim + ch * 8;
+            cp_async16(q_u + r * pitch + ch * 16, src, r < nq ? 16 : 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // cos and sin of this thread's first pair of the queries' rotation, asked for beside the queries
+        const bool rotates_q = a.store_new && a.cos_sin;
+        float2 cs_first = make_float2(1.f, 0.f);
+        if (rotates_q && (int)threadIdx.x < nq * half_d)
+            cs_first = *reinterpret_cast<const float2*>(a.cos_sin + ((long)tkn * half_d + (int)threadIdx.x % half_d) * 2);
         bf16 new_k[DMAX / 32], new_v[DMAX / 32];   // elements lane + 32 u of the row
         if (owns_new) {
             const bf16* krow = a.q + (long)tkn * a.ldq + (long)(n_heads + kvh) * head_dim;
@@ -200,11 +217,10 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
                     new_k[u] = __float2bfloat16_rn(x);
                 }
             }
-            if (a.write_pages && blockIdx.x % chunks == 0) {
-                const int page = a.block_table[(long)a.seq_slot[seq] * a.table_width + pos / a.page_size];
-                if (page < 0) { if (lane == 0 && a.status) atomicExch(a.status, 2); }
+            if (writes_page) {
+                if (new_page < 0) { if (lane == 0 && a.status) atomicExch(a.status, 2); }
                 else {
-                    const long at = (((long)page * n_kv_heads + kvh) * a.page_size + pos % a.page_size) * head_dim;
+                    const long at = (((long)new_page * n_kv_heads + kvh) * a.page_size + pos % a.page_size) * head_dim;
 #pragma unroll
                     for (int u = 0; u < DMAX / 32; ++u) {
                         const int e = lane + 32 * u;
@@ -213,21 +229,15 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
                 }
             }
         }
-        // query rows of this block (zero beyond the group)
-        for (int c = threadIdx.x; c < 16 * chunks_row; c += NCONSUMERS) {
-            const int r = c / chunks_row, ch = c - r * chunks_row;
-            const bf16* src = a.q + (long)tkn * a.ldq + (long)(h0 + min(r, nq - 1)) * head_dim + ch * 8;
-            cp_async16(q_u + r * pitch + ch * 16, src, r < nq ? 16 : 0);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         consumers_sync();
-        if (a.store_new && a.cos_sin) {
+        if (rotates_q) {
             // the queries as projected: rotate them where they lie (pairs i, i + head_dim / 2 of every head)
             bf16* q_s = reinterpret_cast<bf16*>(smem_raw + (q_u - smem_u32(smem_raw)));
             for (int idx = threadIdx.x; idx < nq * half_d; idx += NCONSUMERS) {
                 const int r = idx / half_d, i = idx - r * half_d;
-                const float2 cs = *reinterpret_cast<const float2*>(a.cos_sin + ((long)tkn * half_d + i) * 2);
+                const float2 cs = idx == (int)threadIdx.x ? cs_first
+                                                          : *reinterpret_cast<const float2*>(a.cos_sin + ((long)tkn * half_d + i) * 2);
                 bf16* row = q_s + (long)r * (pitch / 2);
                 const float x = __bfloat162float(row[i]), y = __bfloat162float(row[i + half_d]);
                 row[i] = __float2bfloat16_rn(x * cs.x - y * cs.y);
@@ -377,37 +387,59 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
                 // ---- the block that finishes a token's last key range merges them, in range order ----
                 __threadfence();                       // this block's partial result is visible before it is counted
                 consumers_sync();
-                if (threadIdx.x == 0) {
-                    uint32_t with_keys = 0;            // ranges without visible keys never ran (n_splits <= 32 here)
-                    for (int s2 = 0; s2 < a.n_splits; ++s2) {
-                        int b, e;
-                        fx_split_range(pos, lo, s2, a.n_splits, a.split_len, b, e);
-                        if (b < e) with_keys |= 1u << s2;
+                if (warp == 0) {
+                    // ranges without visible keys never ran (n_splits <= 32 here): lane s2 looks at range s2
+                    int b = 0, e = 0;
+                    if (lane < a.n_splits) fx_split_range(pos, lo, lane, a.n_splits, a.split_len, b, e);
+                    const uint32_t with_keys = __ballot_sync(0xffffffffu, b < e);
+                    if (lane == 0) {
+                        ranges_with_keys_s = with_keys;
+                        int* counter = a.counters + (long)tkn * gridDim.x + blockIdx.x;
+                        const int before = atomicAdd(counter, 1);
+                        last_block_s = before == __popc(with_keys) - 1;
+                        if (last_block_s) *counter = 0;    // every other block of this token has counted: ready for the next launch
                     }
-                    ranges_with_keys_s = with_keys;
-                    int* counter = a.counters + (long)tkn * gridDim.x + blockIdx.x;
-                    const int before = atomicAdd(counter, 1);
-                    last_block_s = before == __popc(with_keys) - 1;
-                    if (last_block_s) *counter = 0;    // every other block of this token has counted: ready for the next launch
                 }
                 consumers_sync();
                 if (last_block_s) {
                     __threadfence();
                     const uint32_t with_keys = ranges_with_keys_s;
+                    const int n_splits = a.n_splits;
+                    // every range's (max, sum) of this block's heads into shared memory, all loads in flight together
+                    // (the ring is free: every thread has read its part of acc_s before the barrier above);
+                    // a range without keys counts as one whose maximum is -inf
+                    float* ml2 = acc_s;                // [nq][n_splits][2]
+                    for (int i = threadIdx.x; i < nq * n_splits; i += NCONSUMERS) {
+                        const int h = i / n_splits, s2 = i - h * n_splits;
+                        float2 v = make_float2(-INFINITY, 0.f);
+                        if (with_keys >> s2 & 1)
+                            v = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (((long)tkn * n_heads + (h0 + h)) * n_splits + s2) * 2));
+                        ml2[2 * i] = v.x; ml2[2 * i + 1] = v.y;
+                    }
+                    consumers_sync();
+                    constexpr int MERGE_AHEAD = 8;     // partial sums asked for together; added up in range order
                     for (int idx = threadIdx.x; idx < nq * head_dim; idx += NCONSUMERS) {
                         const int h = idx / head_dim, e = idx - h * head_dim;
-                        const long base = ((long)tkn * n_heads + (h0 + h)) * a.n_splits;
+                        const long base = ((long)tkn * n_heads + (h0 + h)) * n_splits;
+                        const float* ml_h = ml2 + (long)h * n_splits * 2;
                         float mm = -INFINITY;
-                        for (int s2 = 0; s2 < a.n_splits; ++s2)
-                            if (with_keys >> s2 & 1) mm = fmaxf(mm, __ldcg(a.part_ml + (base + s2) * 2));
+                        for (int s2 = 0; s2 < n_splits; ++s2) mm = fmaxf(mm, ml_h[s2 * 2]);
                         float ll = 0.f, acc = 0.f;
-                        for (int s2 = 0; s2 < a.n_splits; ++s2) {
-                            if (!(with_keys >> s2 & 1)) continue;
-                            const float ms = __ldcg(a.part_ml + (base + s2) * 2);
-                            if (ms == -INFINITY) continue;
-                            const float wgt = __expf(ms - mm);
-                            ll += __ldcg(a.part_ml + (base + s2) * 2 + 1) * wgt;
-                            acc += __ldcg(a.part_acc + (base + s2) * head_dim + e) * wgt;
+                        for (int s0 = 0; s0 < n_splits; s0 += MERGE_AHEAD) {
+                            float part[MERGE_AHEAD], ms[MERGE_AHEAD];
+#pragma unroll
+                            for (int u = 0; u < MERGE_AHEAD; ++u) {
+                                const int s2 = s0 + u;
+                                ms[u] = s2 < n_splits ? ml_h[s2 * 2] : -INFINITY;
+                                part[u] = ms[u] == -INFINITY ? 0.f : __ldcg(a.part_acc + (base + s2) * head_dim + e);
+                            }
+#pragma unroll
+                            for (int u = 0; u < MERGE_AHEAD; ++u) {
+                                if (ms[u] == -INFINITY) continue;
+                                const float wgt = __expf(ms[u] - mm);
+                                ll += ml_h[(s0 + u) * 2 + 1] * wgt;
+                                acc += part[u] * wgt;
+                            }
                         }
                         a.out[(long)tkn * a.ldo + (long)(h0 + h) * head_dim + e] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
                     }
