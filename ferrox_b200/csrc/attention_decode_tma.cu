@@ -345,16 +345,18 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
 
         // ---- merge the four warps, in warp order, and write the partial result ------------
         consumers_sync();                            // every warp has left the ring (all its tiles have arrived)
-        float* acc_s = reinterpret_cast<float*>(smem_raw + (ring - smem_u32(smem_raw)));   // [4][16][head_dim]
+        // [4][16][head_dim + 8]: rows 8 floats longer than a head, so that the 8-byte stores of a quarter warp
+        // (rows g, columns 2 t4) fall into different banks; only the rows of real heads are written
+        float* acc_s = reinterpret_cast<float*>(smem_raw + (ring - smem_u32(smem_raw)));
+        const int acc_pitch = head_dim + 8;
         if (t4 == 0) { m_s[warp][g] = m0; m_s[warp][g + 8] = m1; l_s[warp][g] = l0; l_s[warp][g + 8] = l1; }
         if (threadIdx.x == 0) complete_s = !abort_flag_s;   // one reading for all: the barriers below are taken by all or none
 #pragma unroll
         for (int i = 0; i < ON; ++i) {
             const int col = i * 8 + 2 * t4;
             if (col < head_dim) {
-                float* a0 = acc_s + ((long)warp * 16 + g) * head_dim + col;
-                float* a1 = acc_s + ((long)warp * 16 + g + 8) * head_dim + col;
-                a0[0] = o[i][0]; a0[1] = o[i][1]; a1[0] = o[i][2]; a1[1] = o[i][3];
+                if (g < nq) *reinterpret_cast<float2*>(acc_s + ((long)warp * 16 + g) * acc_pitch + col) = make_float2(o[i][0], o[i][1]);
+                if (g + 8 < nq) *reinterpret_cast<float2*>(acc_s + ((long)warp * 16 + g + 8) * acc_pitch + col) = make_float2(o[i][2], o[i][3]);
             }
         }
         consumers_sync();
@@ -370,7 +372,7 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
                     for (int w = 0; w < 4; ++w) {
                         const float wgt = m_s[w][h] == -INFINITY ? 0.f : exp2f((m_s[w][h] - mm) * a.scale_log2e);
                         ll += l_s[w][h] * wgt;
-                        acc += acc_s[((long)w * 16 + h) * head_dim + e] * wgt;
+                        acc += acc_s[((long)w * 16 + h) * acc_pitch + e] * wgt;
                     }
                 }
                 if (a.n_splits == 1 && a.out) {
@@ -385,7 +387,9 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
             }
             if (a.counters && a.n_splits > 1) {
                 // ---- the block that finishes a token's last key range merges them, in range order ----
-                __threadfence();                       // this block's partial result is visible before it is counted
+                // Every thread's partial sums are written before the barrier; the one thread that counts does so with
+                // release and acquire at the scope of the GPU, which orders the block's writes (cumulative through the
+                // barrier) before the count and the count before what the last block reads: no fence in every thread.
                 consumers_sync();
                 if (warp == 0) {
                     // ranges without visible keys never ran (n_splits <= 32 here): lane s2 looks at range s2
@@ -395,19 +399,32 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
                     if (lane == 0) {
                         ranges_with_keys_s = with_keys;
                         int* counter = a.counters + (long)tkn * gridDim.x + blockIdx.x;
-                        const int before = atomicAdd(counter, 1);
+                        int before;
+                        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(before) : "l"(counter) : "memory");
                         last_block_s = before == __popc(with_keys) - 1;
                         if (last_block_s) *counter = 0;    // every other block of this token has counted: ready for the next launch
                     }
                 }
                 consumers_sync();
                 if (last_block_s) {
-                    __threadfence();
                     const uint32_t with_keys = ranges_with_keys_s;
                     const int n_splits = a.n_splits;
-                    // every range's (max, sum) of this block's heads into shared memory, all loads in flight together
-                    // (the ring is free: every thread has read its part of acc_s before the barrier above);
-                    // a range without keys counts as one whose maximum is -inf
+                    // The partial sums of this thread's first element and every range's (max, sum) of the block's heads
+                    // are asked for together: one trip to the L2 instead of three.  (The ring is free: every thread
+                    // has read its part of acc_s before the barriers above.)  A range without keys was never
+                    // written and counts as one whose maximum is -inf.
+                    constexpr int MERGE_AHEAD = 16;    // partial sums asked for together; added up in range order
+                    float part[MERGE_AHEAD];
+                    auto load_parts = [&](int idx, int s0) {
+                        const int h = idx / head_dim, e = idx - h * head_dim;
+                        const long base = ((long)tkn * n_heads + (h0 + h)) * n_splits;
+#pragma unroll
+                        for (int u = 0; u < MERGE_AHEAD; ++u) {
+                            const int s2 = s0 + u;
+                            part[u] = (s2 < n_splits && (with_keys >> s2 & 1)) ? __ldcg(a.part_acc + (base + s2) * head_dim + e) : 0.f;
+                        }
+                    };
+                    if ((int)threadIdx.x < nq * head_dim) load_parts(threadIdx.x, 0);
                     float* ml2 = acc_s;                // [nq][n_splits][2]
                     for (int i = threadIdx.x; i < nq * n_splits; i += NCONSUMERS) {
                         const int h = i / n_splits, s2 = i - h * n_splits;
@@ -417,26 +434,19 @@ __global__ void __launch_bounds__(NTHREADS, DMAX <= 128 ? 2 : 1) decode_tma_kern
                         ml2[2 * i] = v.x; ml2[2 * i + 1] = v.y;
                     }
                     consumers_sync();
-                    constexpr int MERGE_AHEAD = 8;     // partial sums asked for together; added up in range order
                     for (int idx = threadIdx.x; idx < nq * head_dim; idx += NCONSUMERS) {
                         const int h = idx / head_dim, e = idx - h * head_dim;
-                        const long base = ((long)tkn * n_heads + (h0 + h)) * n_splits;
                         const float* ml_h = ml2 + (long)h * n_splits * 2;
                         float mm = -INFINITY;
                         for (int s2 = 0; s2 < n_splits; ++s2) mm = fmaxf(mm, ml_h[s2 * 2]);
                         float ll = 0.f, acc = 0.f;
                         for (int s0 = 0; s0 < n_splits; s0 += MERGE_AHEAD) {
-                            float part[MERGE_AHEAD], ms[MERGE_AHEAD];
+                            if (idx != (int)threadIdx.x || s0 != 0) load_parts(idx, s0);
 #pragma unroll
                             for (int u = 0; u < MERGE_AHEAD; ++u) {
-                                const int s2 = s0 + u;
-                                ms[u] = s2 < n_splits ? ml_h[s2 * 2] : -INFINITY;
-                                part[u] = ms[u] == -INFINITY ? 0.f : __ldcg(a.part_acc + (base + s2) * head_dim + e);
-                            }
-#pragma unroll
-                            for (int u = 0; u < MERGE_AHEAD; ++u) {
-                                if (ms[u] == -INFINITY) continue;
-                                const float wgt = __expf(ms[u] - mm);
+                                const float ms = s0 + u < n_splits ? ml_h[(s0 + u) * 2] : -INFINITY;
+                                if (ms == -INFINITY) continue;
+                                const float wgt = __expf(ms - mm);
                                 ll += ml_h[(s0 + u) * 2 + 1] * wgt;
                                 acc += part[u] * wgt;
                             }
@@ -485,7 +495,7 @@ static int tma_ring(int head_dim, size_t* smem)
     int stages = (96 * 1024) / stage_bytes;             // two blocks an SM up to head size 128
     if (stages < 3) stages = 3;                         // head size 192, 256: one block an SM
     if (stages > MAX_STAGES) stages = MAX_STAGES;
-    const size_t merge = (size_t)4 * 16 * head_dim * sizeof(float);
+    const size_t merge = (size_t)4 * 16 * (head_dim + 8) * sizeof(float);
     size_t ring = (size_t)stages * stage_bytes;
     if (ring < merge) ring = merge;
     *smem = 1024 + ring + (size_t)16 * (head_dim * 2 + 16);
@@ -503,13 +513,14 @@ extern "C" int fx_decode_split_tma(const void* q, long ldq, const void* k_pages,
 {
     if (n_tokens <= 0) return FX_OK;
     if (counters && (n_splits > 32 || !out || ldo % 2)) return FX_ERR_SIZE;
-    size_t smem = 0;
-    const int stages = tma_ring(head_dim, &smem);
-    if (stages == 0 || n_pages <= 0 || page_size < TK || page_size % TK || n_kv_heads <= 0 || n_heads % n_kv_heads)
+    if (head_dim <= 0 || n_pages <= 0 || page_size < TK || page_size % TK || n_kv_heads <= 0 || n_heads % n_kv_heads)
         return FX_ERR_SIZE;
     if (ldq % 8 || (uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16) return FX_ERR_ALIGN;
     const int group = n_heads / n_kv_heads;
     const int chunks = (group + MAXQ - 1) / MAXQ;
+    size_t smem = 0;
+    const int stages = tma_ring(head_dim, &smem);
+    if (stages == 0) return FX_ERR_SIZE;
     dim3 grid(n_kv_heads * chunks, n_tokens, n_splits);
     if (grid.y > 65535u || grid.z > 65535u) return FX_ERR_SIZE;
     CUtensorMap mk, mv;

@@ -555,7 +555,7 @@ def decode_tma_blocks_per_sm(dtype, head_dim: int, page_size: int) -> int:
         return 0
     stage = 2 * (head_dim // 64) * 8192
     stages = max(3, min(8, (96 * 1024) // stage))
-    smem = 1024 + max(stages * stage, 4 * 16 * head_dim * 4) + 16 * (head_dim * 2 + 16)
+    smem = 1024 + max(stages * stage, 4 * 16 * (head_dim + 8) * 4) + 16 * (head_dim * 2 + 16)
     return min(2, (227 * 1024) // (smem + 1024))
 
 
