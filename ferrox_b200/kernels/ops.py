@@ -545,6 +545,7 @@ DECODE_BLOCK_OVERHEAD = 128       # start and end of a block, in keys' worth of 
 DECODE_MERGE_COST = 256           # the merge of the key ranges, in the same unit
 DECODE_BLOCKS_TO_SATURATE = 160   # blocks streaming at the same time that draw the machine's whole bandwidth
 DECODE_MAX_SPLITS = 16
+DECODE_RUN_LATENCY = 0.15         # share of a run's length that a block's own chain of tiles adds
 
 
 def decode_tma_blocks_per_sm(dtype, head_dim: int, page_size: int) -> int:
@@ -560,22 +561,28 @@ def decode_tma_blocks_per_sm(dtype, head_dim: int, page_size: int) -> int:
 
 
 def decode_split_plan(n_tokens: int, n_kv_blocks: int, max_positions: int, blocks_per_sm: int = 3,
-                      single_is_final: bool = False):
+                      single_is_final: bool = False, run_latency: float = 0.0):
     """(split_len, n_splits) for :func:`decode_attention`.  split_len 0: every token's visible keys are cut
     into n_splits runs of equal length, so that all blocks have work whatever the context length is.
     n_splits is a function of the step's size and the context limit only (a CUDA graph keeps its grid).  The cost
     of n runs, in the time one block takes for a key: the keys stream at the rate of the whole machine
     (DECODE_BLOCKS_TO_SATURATE blocks' worth) or, with few or unevenly many blocks, at the rate of the blocks of a
-    wave one after the other; every wave pays a block's start and end; more than one run pays the merge
-    (``single_is_final``: a kernel that writes a single run's result itself, so only n > 1 pays it).  Measured
-    on a B200 with 16 kv heads of 128: 64 requests 178 us with one run and 189 us with two, 8 requests 35 and 29."""
+    wave one after the other; every wave pays a block's start and end and a share of a run's length (a block's own
+    chain of tiles, which nothing hides at its start and its end); more than one run pays the merge
+    (``single_is_final``: a kernel that writes a single run's result itself, so only n > 1 pays it).
+    ``run_latency``: the share of a run's length counted once more per wave; the kernel that streams pages by TMA is
+    planned with DECODE_RUN_LATENCY.  Measured with it on a B200 with 16 kv heads of 128, context 2,048 of 4,096, 8
+    layers' step in microseconds: 3 requests 864 with 4 runs and 848 with 6; 4 requests 956 with 3 and 936 with 4;
+    5 requests 1,081 with 2 and 1,046 with 3; 6 requests 1,167 with 2 and 1,133 with 3; 8 requests 1,258 with 2 and
+    1,357 with 3 (384 blocks where 296 fit); 9 requests 1,482 with 1, 1,376 with 2, 1,464 with 3."""
     blocks = max(1, n_tokens * n_kv_blocks)
     slots = sm_count() * blocks_per_sm
     best, best_cost = 1, None
     for n in range(1, min(DECODE_MAX_SPLITS, max(1, -(-max_positions // 64))) + 1):
         waves = -(-blocks * n // slots)
         stream = max(blocks * max_positions / DECODE_BLOCKS_TO_SATURATE, waves * max_positions / n)
-        cost = stream + waves * DECODE_BLOCK_OVERHEAD + (DECODE_MERGE_COST if n > 1 or not single_is_final else 0)
+        cost = (stream + waves * (DECODE_BLOCK_OVERHEAD + run_latency * max_positions / n)
+                + (DECODE_MERGE_COST if n > 1 or not single_is_final else 0))
         if best_cost is None or cost < best_cost * 0.98:   # more runs only for a clear gain
             best, best_cost = n, cost
     return 0, best

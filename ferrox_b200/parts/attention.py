@@ -149,8 +149,9 @@ class GqaAttention(Mixer):
             per_sm = ops.decode_tma_blocks_per_sm(qkv.dtype, s.head_dim, cache.page_size)
             # blocks per token: the tensor-core kernels take 16 query heads of a kv head at a time, the CUDA-core one 8
             kv_blocks = s.n_kv_heads * -(-group // (16 if qkv.dtype == torch.bfloat16 else 8))
-            split_len, n_splits = ops.decode_split_plan(T, kv_blocks, cache.block_table.shape[1] * cache.page_size,
-                                                        per_sm or 3, single_is_final=per_sm > 0)
+            split_len, n_splits = ops.decode_split_plan(
+                T, kv_blocks, cache.block_table.shape[1] * cache.page_size, per_sm or 3, single_is_final=per_sm > 0,
+                run_latency=ops.DECODE_RUN_LATENCY if per_sm else 0.0)
             part_acc = self.rt.empty(T, s.n_heads, n_splits, s.head_dim, dtype=torch.float32)
             part_ml = self.rt.empty(T, s.n_heads, n_splits, 2, dtype=torch.float32)
             ops.decode_attention(
