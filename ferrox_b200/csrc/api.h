@@ -74,6 +74,13 @@ int fx_route_fused(const void* X, long ldx, const void* W, long ldw, int n_token
                    int top_k, int renorm, float* logits, long ldl, int* ids, float* weights, int* offsets, int* src_token,
                    int* inv_perm, int* active, int n_slots, void* xp_out, long ldxp, void* stream);
 int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin, void* stream);
+// A few tokens against a plain matrix that fits the shared memory of all SMs together (gemm_slab.cu): every block asks
+// for its whole slab of W before it waits for the kernel before it on the stream, which therefore must not have written W.
+// C[t, n] (+)= sum_k X[t, k] W[n, k] (+ bias[n]); bfloat16 X and W, K a multiple of 128, C bfloat16 or float32.
+int fx_gemm_slab_ok(int N, int K);
+int fx_gemm_slab(const void* X, long ldx, const void* W, long ldw, const void* bias, int bias_dtype, void* C,
+                 int c_dtype, long ldc, int accumulate, int n_tokens, int N, int K, int* status, void* stream);
+
 int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, long ldw, long w_group_stride,
                    const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int n_tokens,
                    int N, int K, int gated, int gate_up_offset, const int* group_offsets, const int* active_groups,

@@ -133,7 +133,8 @@ class GqaAttention(Mixer):
         s = self.spec
         T = x.shape[0]
         qkv = self.rt.empty(T, self.q_size + 2 * self.kv_size)
-        ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, status=batch.status, stream=batch.stream)
+        # (what runs before a block's first product is a norm or the combination before it: short kernels)
+        ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, status=batch.status, stream=batch.stream, after_short_kernel=True)
         # A decode step of one token a request: where the attention kernel can, it rotates the queries and rotates and
         # stores the keys and values itself (one launch less on every layer's path); else the position part does.
         in_kernel = None
@@ -188,7 +189,8 @@ class GqaAttention(Mixer):
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
             )
-        ops.linear(attn, self.w_o, h, accumulate=True, status=batch.status, stream=batch.stream)
+        # (the attention's last blocks only add up key ranges: the memory system is idle under them)
+        ops.linear(attn, self.w_o, h, accumulate=True, status=batch.status, stream=batch.stream, after_short_kernel=True)
 
 
 register_part("gqa_attention", GqaAttention, replace=True)

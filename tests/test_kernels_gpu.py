@@ -94,6 +94,52 @@ def test_gemm_skinny(T, N, K):
         assert rel(got, gate / (1 + torch.exp(-gate)) * up) < 2e-5
 
 
+@pytest.mark.parametrize("T", [1, 5, 8, 13, 32])
+@pytest.mark.parametrize("N,K", [(6144, 2048), (1000, 384), (2048, 2048), (61, 128), (7, 1408), (3001, 1024)])
+def test_gemm_slab_holds_its_rows_of_the_matrix_in_shared_memory(T, N, K):
+    """The product for a few tokens that asks for the whole matrix before it waits for the kernel before it:
+    against the 32-bit product, with a bias, added to a 32-bit result, rows of x wider than K, after a kernel
+    that is still running when it starts (the same stream: its wait is what orders them)."""
+    o = ops()
+    xw = rnd(T, K + 24, dtype=torch.bfloat16)
+    x = xw[:, :K]
+    w, bias = rnd(N, K, dtype=torch.bfloat16, scale=0.1), rnd(N)
+    assert o.slab_ok(x, w)
+    want = x.float() @ w.float().T
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    o.gemm_slab(x, w, out, bias=bias)
+    assert rel(out, want + bias) < TOL["bfloat16"]
+    acc = rnd(T, N, seed=3)
+    base = acc.clone()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.gemm_slab(x, w, acc, accumulate=True, status=status)
+    assert rel(acc, base + want) < 2e-5 and int(status) == 0
+    # x written by the kernel just before it on the stream
+    x2 = torch.empty_like(xw)
+    out2 = torch.empty(T, N, dtype=torch.float32, device=DEV)
+    o.residual_add(acc, out)                      # some kernel of the library: the product's wait is for it
+    x2.copy_(xw)
+    o.gemm_slab(x2[:, :K], w, out2)
+    assert rel(out2, want) < 2e-5
+    # each token's result does not depend on the others
+    if T > 1:
+        one = torch.empty(1, N, dtype=torch.float32, device=DEV)
+        o.gemm_slab(x[T - 1:T], w, one)
+        assert torch.equal(one[0], out2[T - 1])
+
+
+def test_gemm_slab_refuses_what_does_not_fit():
+    o = ops()
+    big = torch.empty(40000, 2048, dtype=torch.bfloat16, device=DEV)      # 164 MB: no SM's share fits
+    x = rnd(4, 2048, dtype=torch.bfloat16)
+    assert not o.slab_ok(x, big)
+    assert not o.slab_ok(rnd(4, 96, dtype=torch.bfloat16), rnd(64, 96, dtype=torch.bfloat16))      # K no multiple of 128
+    assert not o.slab_ok(rnd(40, 128, dtype=torch.bfloat16), rnd(64, 128, dtype=torch.bfloat16))   # too many tokens
+    assert not o.slab_ok(rnd(4, 128), rnd(64, 128))                                                  # 32-bit
+    with pytest.raises(o.KernelError):
+        o.gemm_slab(x, big, torch.empty(4, 40000, dtype=torch.float32, device=DEV))
+
+
 @pytest.mark.parametrize("T,K_top", [(1, 2), (8, 4), (33, 3)])
 def test_gemm_skinny_grouped_against_routing(T, K_top):
     o = ops()
