@@ -77,7 +77,7 @@ int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int
 // A few tokens against a plain matrix that fits the shared memory of all SMs together (gemm_slab.cu): every block asks
 // for its whole slab of W before it waits for the kernel before it on the stream, which therefore must not have written W.
 // C[t, n] (+)= sum_k X[t, k] W[n, k] (+ bias[n]); bfloat16 X and W, K a multiple of 128, C bfloat16 or float32.
-int fx_gemm_slab_ok(int N, int K);
+int fx_gemm_slab_ok(int N, int K, int n_tokens);
 int fx_gemm_slab(const void* X, long ldx, const void* W, long ldw, const void* bias, int bias_dtype, void* C,
                  int c_dtype, long ldc, int accumulate, int n_tokens, int N, int K, int* status, void* stream);
 

@@ -84,8 +84,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) slab_kernel(SlabArgs a)
     const int row_tiles = a.rows_pad / 16;
     bool have_w = false;
     for (int t0 = 0; t0 < a.n_tokens; t0 += TOKENS) {
-        // this pass's tokens (rows beyond the step's: zeros)
-        for (int i = threadIdx.x; i < TOKENS * (K / 8); i += NTHREADS) {
+        // this pass's tokens; a step of fewer than 8 keeps only its own rows (the tensor cores read the last of them
+        // again in place of the missing ones, and those columns of the result are not used)
+        const int kept = min(TOKENS, a.n_tokens);
+        for (int i = threadIdx.x; i < kept * (K / 8); i += NTHREADS) {
             const int t = i / (K / 8), c = i - t * (K / 8);
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (t0 + t < a.n_tokens) v = *reinterpret_cast<const uint4*>(a.X + (long)(t0 + t) * a.ldx + c * 8);
@@ -103,7 +105,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) slab_kernel(SlabArgs a)
 #pragma unroll
         for (int ks = 0; ks < KSTEPS_MAX; ++ks)
             if (ks < ksteps)
-                ldsm2(x_u + (uint32_t)(lane & 7) * pitch + (uint32_t)(k_begin + ks * 16 + ((lane >> 3) & 1) * 8) * 2, xb[ks][0], xb[ks][1]);
+                ldsm2(x_u + (uint32_t)min(lane & 7, kept - 1) * pitch + (uint32_t)(k_begin + ks * 16 + ((lane >> 3) & 1) * 8) * 2, xb[ks][0], xb[ks][1]);
         __syncthreads();                   // the tokens' rows are in registers: their place is free for the sums
         for (int rt = 0; rt < row_tiles; ++rt) {
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -151,14 +153,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) slab_kernel(SlabArgs a)
 constexpr size_t SLAB_SMEM_MAX = 220 * 1024;
 
 // rows a block and bytes of shared memory; false where the matrix does not fit
-bool slab_plan(int N, int K, int* rows_per_block, int* rows_pad, size_t* smem)
+bool slab_plan(int N, int K, int n_tokens, int* rows_per_block, int* rows_pad, size_t* smem)
 {
     if (N <= 0 || K <= 0 || K % 128 || K / 128 > 64) return false;
     const int sms = fx_sm_count();
     const int r = (int)fx_cdiv(N, sms);
     const int pad = (r + 15) & ~15;
     const size_t pitch = (size_t)K * 2 + 16;
-    const size_t tokens = (size_t)TOKENS * pitch, sums = (size_t)WARPS * pad * TOKENS * sizeof(float);
+    const size_t tokens = (size_t)(n_tokens < TOKENS ? n_tokens : TOKENS) * pitch, sums = (size_t)WARPS * pad * TOKENS * sizeof(float);
     const size_t bytes = (size_t)r * pitch + (tokens > sums ? tokens : sums);
     if (bytes > SLAB_SMEM_MAX) return false;
     *rows_per_block = r; *rows_pad = pad; *smem = bytes;
@@ -182,10 +184,10 @@ int launch(const SlabArgs& a, unsigned blocks, size_t smem, cudaStream_t s)
 }  // namespace
 
 // 1 where fx_gemm_slab takes the sizes (the whole matrix fits the SMs' shared memory, one slab of rows a block).
-extern "C" int fx_gemm_slab_ok(int N, int K)
+extern "C" int fx_gemm_slab_ok(int N, int K, int n_tokens)
 {
     int r, pad; size_t smem;
-    return slab_plan(N, K, &r, &pad, &smem) ? 1 : 0;
+    return slab_plan(N, K, n_tokens, &r, &pad, &smem) ? 1 : 0;
 }
 
 // C[t, n] (+)= sum_k X[t, k] W[n, k] (+ bias[n]).  X [n_tokens, K] and W [N, K] bfloat16 (rows 16-byte aligned);
@@ -197,7 +199,7 @@ extern "C" int fx_gemm_slab(const void* X, long ldx, const void* W, long ldw, co
     if (n_tokens <= 0 || N <= 0) return FX_OK;
     SlabArgs a;
     size_t smem = 0;
-    if (!slab_plan(N, K, &a.rows_per_block, &a.rows_pad, &smem)) return FX_ERR_SIZE;
+    if (!slab_plan(N, K, n_tokens, &a.rows_per_block, &a.rows_pad, &smem)) return FX_ERR_SIZE;
     if (ldw % 8 || ldx % 8 || (uintptr_t)W % 16 || (uintptr_t)X % 16) return FX_ERR_ALIGN;
     if (c_dtype != FX_F32 && c_dtype != FX_BF16) return FX_ERR_DTYPE;
     if (bias && bias_dtype != FX_F32 && bias_dtype != FX_BF16) return FX_ERR_DTYPE;

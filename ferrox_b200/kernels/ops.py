@@ -56,7 +56,7 @@ _SIGNATURES = {
                                 _P, _I, _P],
     "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P],
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
-    "fx_gemm_slab_ok": [_I, _I],
+    "fx_gemm_slab_ok": [_I, _I, _I],
     "fx_gemm_slab": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "fx_decode_attention": [_P, _L, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
@@ -556,7 +556,7 @@ def slab_ok(x, w) -> bool:
         return False
     if x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or x.stride(1) != 1 or w.stride(1) != 1:
         return False
-    return bool(_get("fx_gemm_slab_ok")(w.shape[0], w.shape[1]))
+    return bool(_get("fx_gemm_slab_ok")(w.shape[0], w.shape[1], x.shape[0]))
 
 
 def gemm_slab(x, w, out, *, bias=None, accumulate=False, status=None, stream=None):
