@@ -26,6 +26,7 @@
 // crates/ferrox-core/src/weight_matrix.rs:1115-1122); the product itself is
 // crates/ferrox-core/src/matmul.rs:18-58, experts crates/ferrox-moe/src/lib.rs:619-659.
 #include "tc_common.cuh"
+#include "tc_epilogue.cuh"
 #include "api.h"
 
 namespace {
@@ -40,7 +41,8 @@ template <int BN> struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ +
+                                4 * fxtc::EPI_WARP_BYTES /* the epilogue warps' staging tiles */;
     static_assert(2 * BN <= 512, "two accumulators must fit the 512 columns of tensor memory");
 };
 
@@ -231,7 +233,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
             // Accumulating into 32-bit rows: the values already there are fetched one chunk ahead, the first chunk
             // before the wait for the accumulator, so that their latency hides behind the products.
             const bool row_ok = row < tc.row_end;
-            const bool acc_ahead = !GATED && a.accumulate && a.c_dtype == FX_F32 && a.ldc % 4 == 0 && row_ok;
+            // whole tiles of aligned rows go out through the warp's staging tile in whole 128-byte lines (tc_epilogue.cuh)
+            const bool fast = tc.n0 + OUT_N <= a.N && (uintptr_t)a.C % 16 == 0 &&
+                              (a.c_dtype == FX_F32 ? a.ldc % 4 == 0 : (a.ldc % 8 == 0 && !a.accumulate));
+            uint8_t* stage = smem_raw + (bar_base + 256u - smem_u32(smem_raw)) + quad * EPI_WARP_BYTES;
+            const int rows_ok = min(32, max(0, tc.row_end - (tc.m0 + quad * 32)));
+            const bool acc_ahead = !fast && !GATED && a.accumulate && a.c_dtype == FX_F32 && a.ldc % 4 == 0 && row_ok;
             float4 pre[8], nxt[8];
             auto fetch_c = [&](int c, float4* buf4) {
                 const int nb = tc.n0 + c * 32;
@@ -241,7 +248,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                     for (int j = 0; j < 8; ++j) buf4[j] = cp[j];
                 }
             };
-            fetch_c(0, pre);
+            if (acc_ahead) fetch_c(0, pre);
             const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (uint32_t)((it >> 1) & 1), abort_flag));
             if (!ok) break;
             tc_fence_after();
@@ -251,7 +258,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                 uint32_t r[32], u[32];
                 tc_ld32(lane_addr + c * 32, r);
                 if (GATED) tc_ld32(lane_addr + BN / 2 + c * 32, u);
-                fetch_c(c + 1, nxt);
+                if (acc_ahead) fetch_c(c + 1, nxt);
                 tc_ld_wait();
                 if (c == OUT_N / 32 - 1) {
                     // everything of this accumulator is in registers: hand it back to the tensor cores
@@ -260,14 +267,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                     if (lane == 0) mbar_arrive(acc_empty_bar(buf));
                 }
                 const int nb = tc.n0 + c * 32;
-                if (!row_ok || nb >= a.N) continue;
+                if (!fast && (!row_ok || nb >= a.N)) continue;
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     float x = __uint_as_float(r[j]);
                     if (a.bias) x += bias_s[quad][c * 32 + j];
-                    if (GATED) x = x / (1.0f + __expf(-x)) * __uint_as_float(u[j]);
+                    if (GATED) x = __fdividef(x, 1.0f + __expf(-x)) * __uint_as_float(u[j]);
                     v[j] = x;
+                }
+                if (fast) {
+                    const long row0 = tc.m0 + quad * 32;
+                    if (a.c_dtype == FX_F32) {
+                        epi_stage_f32(stage, lane, v);
+                        __syncwarp();
+                        epi_flush(stage, lane, reinterpret_cast<uint8_t*>(a.C) + (row0 * a.ldc + nb) * 4, a.ldc * 4, rows_ok, a.accumulate != 0);
+                        __syncwarp();
+                    } else {
+                        epi_stage_bf16(stage, lane, c & 1, v);
+                        if (c & 1) {
+                            __syncwarp();
+                            epi_flush(stage, lane, reinterpret_cast<uint8_t*>(a.C) + (row0 * a.ldc + nb - 32) * 2, a.ldc * 2, rows_ok, false);
+                            __syncwarp();
+                        }
+                    }
+                    continue;
                 }
                 const bool full = nb + 32 <= a.N;
                 if (a.c_dtype == FX_F32) {
@@ -304,8 +328,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                             cp[j] = __float2bfloat16_rn(a.accumulate ? __bfloat162float(cp[j]) + v[j] : v[j]);
                     }
                 }
+                if (acc_ahead) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) pre[j] = nxt[j];
+                    for (int j = 0; j < 8; ++j) pre[j] = nxt[j];
+                }
             }
         }
     }

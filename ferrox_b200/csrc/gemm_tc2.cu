@@ -19,6 +19,7 @@
 #include <cooperative_groups.h>
 
 #include "tc_common.cuh"
+#include "tc_epilogue.cuh"
 #include "api.h"
 
 namespace {
@@ -31,7 +32,7 @@ constexpr int BK = 64;
 constexpr int NTHREADS = 192;
 constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256 + 4 * EPI_WARP_BYTES;   // ring, alignment slack, barriers, the epilogue warps' staging tiles
 constexpr int ACC_COLS = 2 * BNH;            // columns of one accumulator: both halves of W
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // a shared::cluster address with this bit cleared names the pair's first CTA
 
@@ -75,6 +76,9 @@ __device__ __forceinline__ void arrive_on_first_cta(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & PEER_MASK) : "memory");
 }
 
+// GATED as a template argument: with a run-time flag the compiler evaluates the gate's exponential and division for
+// every element of plain products too (a select instead of a branch).
+template <bool GATED>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b, Tc2Args a)
 {
@@ -85,7 +89,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();            // 0: the CTA that issues the tensor-core instructions
-    const int out_n = a.gated ? BNH : 2 * BNH;       // output features of a pair's tile
+    const int out_n = GATED ? BNH : 2 * BNH;       // output features of a pair's tile
     const int n_tiles = (a.N + out_n - 1) / out_n;
     const int m_tiles = (a.M + 2 * BM - 1) / (2 * BM);
     const int total = m_tiles * n_tiles;
@@ -129,7 +133,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
                 const int n0 = (id / m_tiles) * out_n;
                 // this CTA's rows of W: plain: its half of the tile's features; gated: the gate rows (first CTA) or
                 // the up rows (second CTA) of the tile's features
-                const int w0 = a.gated ? (rank ? a.gate_up_offset + n0 : n0) : n0 + (int)rank * BNH;
+                const int w0 = GATED ? (rank ? a.gate_up_offset + n0 : n0) : n0 + (int)rank * BNH;
                 for (int kb = 0; kb < k_blocks; ++kb, ++issued) {
                     const int s = (int)(issued % STAGES);
                     const uint32_t parity = (uint32_t)((issued / STAGES) & 1) ^ 1u;
@@ -196,7 +200,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
             // before the wait for the accumulator (as in gemm_tc.cu).
             const bool row_ok = row < a.M;
             const int chunks = out_n / 32;
-            const bool acc_ahead = !a.gated && a.accumulate && a.c_dtype == FX_F32 && a.ldc % 4 == 0 && row_ok;
+            // whole tiles of aligned rows go out through the warp's staging tile in whole 128-byte lines (tc_epilogue.cuh)
+            const bool fast = n0 + out_n <= a.N && (uintptr_t)a.C % 16 == 0 &&
+                              (a.c_dtype == FX_F32 ? a.ldc % 4 == 0 : (a.ldc % 8 == 0 && !a.accumulate));
+            uint8_t* stage = smem_raw + (bar_base + 256u - smem_u32(smem_raw)) + quad * EPI_WARP_BYTES;
+            const int rows_ok = min(32, max(0, a.M - (m0 + quad * 32)));
+            const bool acc_ahead = !fast && !GATED && a.accumulate && a.c_dtype == FX_F32 && a.ldc % 4 == 0 && row_ok;
             float4 pre[8], nxt[8];
             auto fetch_c = [&](int c, float4* buf4) {
                 const int nb = n0 + c * 32;
@@ -215,7 +224,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
             for (int c = 0; c < chunks; ++c) {
                 uint32_t r[32], u[32];
                 tc_ld32(lane_addr + c * 32, r);
-                if (a.gated) tc_ld32(lane_addr + BNH + c * 32, u);
+                if (GATED) tc_ld32(lane_addr + BNH + c * 32, u);
                 fetch_c(c + 1, nxt);
                 tc_ld_wait();
                 if (c == chunks - 1) {
@@ -224,14 +233,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
                     if (lane == 0) arrive_on_first_cta(acc_empty_bar(buf));
                 }
                 const int nb = n0 + c * 32;
-                if (!row_ok || nb >= a.N) continue;
+                if (!fast && (!row_ok || nb >= a.N)) continue;
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     float x = __uint_as_float(r[j]);
                     if (a.bias) x += bias_s[quad][c * 32 + j];
-                    if (a.gated) x = x / (1.0f + __expf(-x)) * __uint_as_float(u[j]);
+                    if (GATED) x = __fdividef(x, 1.0f + __expf(-x)) * __uint_as_float(u[j]);
                     v[j] = x;
+                }
+                if (fast) {
+                    const long row0 = m0 + quad * 32;
+                    if (a.c_dtype == FX_F32) {
+                        epi_stage_f32(stage, lane, v);
+                        __syncwarp();
+                        epi_flush(stage, lane, reinterpret_cast<uint8_t*>(a.C) + (row0 * a.ldc + nb) * 4, a.ldc * 4, rows_ok, a.accumulate != 0);
+                        __syncwarp();
+                    } else {
+                        epi_stage_bf16(stage, lane, c & 1, v);
+                        if (c & 1) {
+                            __syncwarp();
+                            epi_flush(stage, lane, reinterpret_cast<uint8_t*>(a.C) + (row0 * a.ldc + nb - 32) * 2, a.ldc * 2, rows_ok, false);
+                            __syncwarp();
+                        }
+                    }
+                    continue;
                 }
                 const bool full = nb + 32 <= a.N;
                 if (a.c_dtype == FX_F32) {
@@ -319,7 +345,8 @@ extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int
     if (!make_map(&mb, W, (uint64_t)K, (uint64_t)w_rows, (uint64_t)ldw, BNH)) return FX_ERR_SIZE;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -339,7 +366,7 @@ extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_fx_pdl_enabled ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, ma, mb, a);
+    cudaError_t e = gated ? cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<true>, ma, mb, a) : cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<false>, ma, mb, a);
     if (e != cudaSuccess) return (int)e;
     return fx_launch_status();
 }
