@@ -81,7 +81,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -89,9 +89,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, begin=None, end=None):
+        """The samples taken between ``begin`` and ``end`` (time.monotonic() of the host; all samples if none fell there)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -101,7 +102,8 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        inside = [r for t, r in self.rows if begin is not None and begin <= t <= end]
+        for r in inside or [r for _, r in self.rows]:
             if len(r) < 6:
                 continue
             try:
@@ -296,20 +298,24 @@ def main() -> int:
             run.close()
             run_ids[0] = last
 
-        for _ in range(warmup):
-            one_step()
-        run_ids[0] = ids
+        # (the sampler runs from before the warm-up, so that it is up when the timed regions begin; only samples
+        # taken during them count)
         clocks = ClockSampler()
         if sample_clocks:
             clocks.start()
+        for _ in range(warmup):
+            one_step()
+        run_ids[0] = ids
         regions, launches = [], 0
+        torch.cuda.synchronize()
+        t_begin = time.monotonic()
         for r in range(repeats):
             before = ops.launch_count()
             ms = timed(k_steps)
             launches = ops.launch_count() - before
             ids = run_ids[0]
             regions.append((ms / steps, PREFILL_TOKENS + warmup + r * steps + steps // 2))
-        clk = clocks.stop() if sample_clocks else None
+        clk = clocks.stop(t_begin, time.monotonic()) if sample_clocks else None
         for s in slots:
             eng.close_request(s)
         return regions, launches, clk
