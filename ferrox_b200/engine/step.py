@@ -60,8 +60,12 @@ def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True, grap
     if logits is None:
         batch = flatten(entries, model.rt.device, status, ops.stream_ptr())
         last_h2d_bytes = batch.h2d_bytes
-        with ops.stream_scope(batch.stream):
-            logits = model.forward(batch, lambda entry: cache.layer_cache(entry.cache, entry.writes_cache))
+        model.rt.begin_step(batch.n_tokens)      # small eager steps keep their buffers from step to step
+        try:
+            with ops.stream_scope(batch.stream):
+                logits = model.forward(batch, lambda entry: cache.layer_cache(entry.cache, entry.writes_cache))
+        finally:
+            model.rt.end_step()
     if check:
         code = int(status.item())
         if code:

@@ -27,13 +27,59 @@ import torch
 from ..weights.loader import TensorDecl
 
 
+# A step of few tokens costs the host more than the device (a launch takes the GPU a few microseconds and Python as
+# long again to prepare); a sixth of that is the caching allocator, asked some 15 times a layer for buffers of the
+# same shapes as in the step before.  Steps of up to REUSE_MAX_TOKENS tokens that are not captured into a graph keep
+# their buffers instead: the n-th request of a step gets the n-th buffer of the step before if shape and type agree.
+# What a step hands to its caller (the logits) never comes from there.
+REUSE_MAX_TOKENS = 512
+REUSE_MAX_BYTES = 1 << 30
+
+
 @dataclass
 class Runtime:
     device: torch.device
     dtype: torch.dtype  # compute dtype: torch.float32 or torch.bfloat16
 
-    def empty(self, *shape, dtype=None) -> torch.Tensor:
-        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+    def __post_init__(self):
+        self._kept = []          # buffers of the last small step, in the order they were asked for
+        self._next = -1          # index of the next request; -1: buffers are not kept
+        self._kept_bytes = 0
+
+    def begin_step(self, n_tokens: int) -> None:
+        """An eager step begins (never inside a graph capture: a graph owns its memory)."""
+        self._next = 0 if 0 < n_tokens <= REUSE_MAX_TOKENS and self.device.type == "cuda" else -1
+
+    def end_step(self) -> None:
+        self._next = -1
+
+    def empty(self, *shape, dtype=None, fresh: bool = False) -> torch.Tensor:
+        """``fresh``: a buffer of the caller's own, for what outlives the step."""
+        dt = dtype or self.dtype
+        i = self._next
+        if i < 0 or fresh:
+            return torch.empty(shape, dtype=dt, device=self.device)
+        self._next = i + 1
+        kept = self._kept
+        if i < len(kept):
+            t = kept[i]
+            if t is not None and t.shape == shape and t.dtype == dt:
+                return t
+        t = torch.empty(shape, dtype=dt, device=self.device)
+        n = t.numel() * t.element_size()
+        if i < len(kept):
+            old = kept[i]
+            if old is not None:
+                self._kept_bytes -= old.numel() * old.element_size()
+            kept[i] = None
+        if self._kept_bytes + n <= REUSE_MAX_BYTES:
+            if i < len(kept):
+                kept[i] = t
+            else:
+                kept.extend([None] * (i - len(kept)))
+                kept.append(t)
+            self._kept_bytes += n
+        return t
 
 
 class Part:

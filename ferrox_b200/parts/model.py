@@ -105,9 +105,9 @@ class DecoderModel(Part):
             then = nxt.norm1 if nxt is not None and nxt.passes_norm else None
             x = block.forward(h, batch, caches(entry), x=x, then_norm=then)
         if batch.n_want == 0:
-            return rt.empty(0, s.vocab_size, dtype=torch.float32)
+            return rt.empty(0, s.vocab_size, dtype=torch.float32, fresh=True)
         with ops.trace_scope("head"):
             x = self.final_norm.forward(h, rows=batch.want_rows)
-            logits = rt.empty(batch.n_want, s.vocab_size, dtype=torch.float32)
+            logits = rt.empty(batch.n_want, s.vocab_size, dtype=torch.float32, fresh=True)   # the caller's
             ops.linear(x, self.head, logits, status=batch.status, stream=batch.stream)
         return logits
