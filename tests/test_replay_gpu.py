@@ -173,6 +173,26 @@ def test_the_same_trace_twice_gives_the_same_bits(folders, dtype):
         assert torch.equal(runs[0][rid], runs[1][rid]) and torch.equal(runs[0][rid], runs[2][rid])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_logits_of_a_step_outlive_the_steps_after_it(folders, expected, dtype):
+    """Small eager steps keep their buffers from one step to the next; what a step returns is not one of them: the
+    logits of every step, kept on the device without a copy and read only at the end, are the plain ones."""
+    from ferrox_b200 import StepEntry
+
+    eng = engine(folders["A"], dtype, page_size=16, n_pages=12, max_slots=2)
+    toks = prompts_for("A")["r2"]
+    slot = eng.open_request()
+    kept = []
+    for i in range(0, len(toks), 3):                 # the same shapes step after step
+        part = toks[i:i + 3]
+        kept.append(eng.step([StepEntry(slot, part, want=list(range(len(part))))]))
+    assert len({t.data_ptr() for t in kept}) == len(kept)
+    got = {"r2": torch.cat([t.cpu() for t in kept])}
+    compare(got, _Only(expected["A"], "r2"), TOL[dtype], f"kept-logits/A/{dtype}")
+    eng.close_request(slot)
+    eng.cache.check_invariants()
+
+
 def test_a_fault_leaves_the_requests_where_they_were(folders, expected):
     """A step whose kernels raised the status word (here: set by hand, no kernel is made to fault) counts as not
     run: StepFault, the requests' lengths unchanged, the decode attention's merge counters zeroed again, and the
